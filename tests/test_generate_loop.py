@@ -1,0 +1,132 @@
+"""The generation loop's decisions, with a scripted backend (CPU)."""
+import pytest
+
+from vlrf_b200.engine.generate import GenerationError, Request, generate, plan_batches, tokens_needed
+from vlrf_b200.sampling import SamplingParams
+
+
+class ScriptedBackend:
+    """Every sequence 'generates' prompt[0]+1, +2, …; records what the loop asks for."""
+
+    def __init__(self, max_tokens=1024, n_slots=4, max_seq_len=64):
+        self.lim = (max_tokens, n_slots, 64, max_seq_len)
+        self.free = list(range(n_slots))
+        self.log = []
+        self.batches = 0
+
+    def limits(self):
+        return self.lim
+
+    def open_batch(self, requests):
+        self.batches += 1
+        slots = [self.free.pop(0) for _ in requests]
+        return {"slots": slots, "next": [r.prompt[0] for r in requests], "fed": [0] * len(requests), "open": set(range(len(requests)))}
+
+    def run(self, h, rows, tokens):
+        self.log.append(("run", [h["slots"][r] for r in rows], [len(t) for t in tokens]))
+        out = []
+        for r, t in zip(rows, tokens):
+            assert r in h["open"]
+            h["fed"][r] += len(t)
+            h["next"][r] += 1
+            out.append(h["next"][r])
+        return out
+
+    def close_row(self, h, row):
+        assert row in h["open"], "a row is closed twice"
+        h["open"].remove(row)
+        self.free.append(h["slots"][row])
+        self.log.append(("close", h["slots"][row]))
+
+
+def greedy(n, **kw):
+    return SamplingParams(max_new_tokens=n, do_sample=False, **kw)
+
+
+def test_first_token_comes_from_the_prompt_step_and_the_last_is_not_fed_back():
+    b = ScriptedBackend()
+    (r,) = generate(b, [[10, 11, 12]], greedy(4))
+    assert r.new_tokens == [11, 12, 13, 14] and r.finish_reason == "length" and r.token_ids == [10, 11, 12, 11, 12, 13, 14]
+    runs = [e for e in b.log if e[0] == "run"]
+    assert [e[2] for e in runs] == [[3], [1], [1], [1]]          # prompt once, then 3 single tokens: 4 samples
+    assert b.free == [1, 2, 3, 0]
+
+
+def test_stop_tokens_end_sequences_early_and_the_batch_shrinks():
+    b = ScriptedBackend()
+    params = [greedy(10, stop_token_ids=(13,)), greedy(10), greedy(2)]
+    res = generate(b, [[10], [20, 21], [30]], params, eos_token_id=99)
+    assert res[0].new_tokens == [11, 12, 13] and res[0].finish_reason == "stop" and res[0].hit_eos
+    assert res[1].tokens_generated == 10 and res[1].finish_reason == "length"
+    assert res[2].new_tokens == [31, 32] and res[2].finish_reason == "length"
+    widths = [len(e[1]) for e in b.log if e[0] == "run"]
+    assert widths == [3, 3, 2, 1, 1, 1, 1, 1, 1, 1]
+    assert sorted(b.free) == [0, 1, 2, 3]
+
+
+def test_default_stop_is_the_models_eos():
+    b = ScriptedBackend()
+    (r,) = generate(b, [[5]], greedy(10), eos_token_id=8)
+    assert r.new_tokens == [6, 7, 8] and r.finish_reason == "stop"
+
+
+def test_context_full_ends_a_sequence():
+    b = ScriptedBackend(max_seq_len=8)
+    (r,) = generate(b, [[1, 2, 3, 4, 5]], greedy(100))
+    assert len(r.token_ids) == 8 and r.finish_reason == "context"
+    (r,) = generate(b, [[1] * 8], greedy(5))
+    assert r.new_tokens == [] and r.finish_reason == "context"
+    with pytest.raises(GenerationError, match="exceeds"):
+        generate(b, [[1] * 9], greedy(5))
+
+
+def test_empty_prompt_starts_from_bos():
+    b = ScriptedBackend()
+    (r,) = generate(b, [[]], greedy(2), bos_token_id=40)
+    assert r.prompt == [40] and r.new_tokens == [41, 42]
+    with pytest.raises(GenerationError, match="bos_token_id"):
+        generate(b, [[]], greedy(2))
+
+
+def test_zero_new_tokens_runs_nothing():
+    b = ScriptedBackend()
+    (r,) = generate(b, [[1, 2]], greedy(0))
+    assert r.new_tokens == [] and r.finish_reason == "length" and b.log == []
+
+
+def test_requests_are_cut_into_batches_that_fit_and_slots_are_reused():
+    b = ScriptedBackend(max_tokens=256, n_slots=2)
+    res = generate(b, [[i] for i in range(5)], greedy(3))
+    assert [r.new_tokens for r in res] == [[i + 1, i + 2, i + 3] for i in range(5)]
+    assert b.batches == 3 and sorted(b.free) == [0, 1]
+    # tokens, not only slots, bound a batch: 100-token prompts + 100 new → 256 tokens each
+    reqs = [Request([0] * 100, greedy(100), i) for i in range(3)]
+    assert tokens_needed(reqs[0], 64, 1024) == 256
+    assert [len(x) for x in plan_batches(reqs, 512, 8, 64, 1024)] == [2, 1]
+    with pytest.raises(GenerationError, match="cache holds"):
+        plan_batches(reqs, 128, 8, 64, 1024)
+
+
+def test_callback_can_stop_a_sequence():
+    b = ScriptedBackend()
+    seen = []
+
+    def on_token(index, tok):
+        seen.append((index, tok))
+        return tok != 12
+
+    (r,) = generate(b, [[10]], greedy(10), on_token=on_token)
+    assert r.new_tokens == [11, 12] and r.finish_reason == "stop" and seen == [(0, 11), (0, 12)]
+
+
+def test_an_error_in_a_step_gives_the_slots_back():
+    class Failing(ScriptedBackend):
+        def run(self, h, rows, tokens):
+            if len(self.log) >= 2:
+                raise RuntimeError("boom")
+            return super().run(h, rows, tokens)
+
+    b = Failing()
+    with pytest.raises(RuntimeError, match="boom"):
+        generate(b, [[1], [2]], greedy(5))
+    assert sorted(b.free) == [0, 1, 2, 3]

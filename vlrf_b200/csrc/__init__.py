@@ -1,0 +1,81 @@
+"""The CUDA kernels of the framework, loaded as one shared library through ctypes.
+
+There is no other execution path: if the library cannot be compiled or loaded, or no CUDA device is
+present, every operation raises `KernelError`.  The functions of `vlrf_b200.csrc.ops` take torch
+tensors on the device, check them, and call the `extern "C"` entry points with raw pointers and the
+current CUDA stream.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+
+from .build import ensure_built
+
+
+class KernelError(RuntimeError):
+    """A kernel refused its arguments, or the kernel library is unavailable."""
+
+
+_lib = None
+_lock = threading.Lock()
+
+_c_int, _c_float, _c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
+
+#: name -> argument types; every function returns int (0 = ok) unless noted
+_SIGNATURES = {
+    "vlrf_device_info": [ctypes.POINTER(_c_int)] * 4,
+    "vlrf_embed": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
+                   _c_void_p, _c_void_p],
+    "vlrf_layernorm": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float,
+                       _c_void_p],
+    "vlrf_gemm_simt": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
+                       _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "vlrf_kv_append": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
+                       _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+    "vlrf_attn_generic": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
+                          _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
+                          _c_void_p, _c_void_p],
+    "vlrf_sample": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                    _c_void_p, _c_void_p],
+    "vlrf_apply_penalties": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
+                             _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+}
+
+
+def library() -> ctypes.CDLL:
+    """The loaded kernel library; built on first use.  Raises KernelError if that is impossible."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        try:
+            path = ensure_built()
+            lib = ctypes.CDLL(str(path))
+        except Exception as exc:  # noqa: BLE001 - reported as the one error of this layer
+            raise KernelError(f"the CUDA kernel library is unavailable: {exc}") from exc
+        lib.vlrf_last_error.restype = ctypes.c_char_p
+        lib.vlrf_last_error.argtypes = []
+        for name, argtypes in _SIGNATURES.items():
+            try:
+                fn = getattr(lib, name)
+            except AttributeError as exc:
+                raise KernelError(f"the kernel library lacks the symbol {name}") from exc
+            fn.argtypes = argtypes
+            fn.restype = _c_int
+        _lib = lib
+        return lib
+
+
+def register_signatures(extra: dict) -> None:
+    """Add entry points (used by source files that join the library later)."""
+    _SIGNATURES.update(extra)
+
+
+def call(name: str, *args) -> None:
+    lib = library()
+    status = getattr(lib, name)(*args)
+    if status != 0:
+        raise KernelError(f"{name}: {lib.vlrf_last_error().decode('utf-8', 'replace')} (status {status})")

@@ -1,0 +1,77 @@
+// Shared declarations of the sm_100a kernels: status codes, the last-error
+// string, element types and small device helpers.  Every exported function is
+// `extern "C"`, takes raw device pointers and the stream to launch on, checks
+// its sizes on the host before launching anything, and returns 0 or a status
+// whose text `vlrf_last_error()` gives.  Nothing here allocates device memory.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+#include <cstdio>
+#include <cstdarg>
+
+#define VLRF_OK 0
+#define VLRF_ERR_INVALID_ARG 1   // same numbering idea as the reference's status enum (include/api/vlrf.h:32-41)
+#define VLRF_ERR_UNSUPPORTED 2
+#define VLRF_ERR_CUDA 3
+
+#define VLRF_F32 0
+#define VLRF_BF16 1
+
+#define VLRF_ACT_NONE 0
+#define VLRF_ACT_GELU_TANH 1
+#define VLRF_ACT_GELU_ERF 2
+
+// Bits of the device-side error word that kernels set instead of faulting.
+#define VLRF_DEVERR_TOKEN_RANGE 1     // a token id outside the vocabulary was clamped
+#define VLRF_DEVERR_POSITION_RANGE 2  // a position outside the table was clamped
+#define VLRF_DEVERR_NO_BLOCK 4        // a token's cache block was not mapped; the token was skipped
+#define VLRF_DEVERR_WAIT_TIMEOUT 8    // a bounded wait on a barrier gave up
+
+extern "C" const char* vlrf_last_error();
+int vlrf_fail(int code, const char* fmt, ...);
+int vlrf_check_launch(const char* what);
+
+#define VLRF_REQUIRE(cond, ...) \
+    do { if (!(cond)) return vlrf_fail(VLRF_ERR_INVALID_ARG, __VA_ARGS__); } while (0)
+
+template <typename T> struct ElemIO;
+template <> struct ElemIO<float> {
+    static __device__ __forceinline__ float load(const float* p) { return *p; }
+    static __device__ __forceinline__ void store(float* p, float v) { *p = v; }
+};
+template <> struct ElemIO<__nv_bfloat16> {
+    static __device__ __forceinline__ float load(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// GELU as the reference computes it (tanh form, include/model/ops.hpp:390-403)
+// and the exact erf form for activation_function "gelu".
+__device__ __forceinline__ float gelu_tanh_f(float x) {
+    const float c1 = 0.7978845608028654f, c2 = 0.044715f;
+    return 0.5f * x * (1.f + tanhf(c1 * (x + c2 * x * x * x)));
+}
+__device__ __forceinline__ float gelu_erf_f(float x) {
+    return 0.5f * x * (1.f + erff(x * 0.70710678118654752440f));
+}
+template <int ACT> __device__ __forceinline__ float apply_act(float x) {
+    if (ACT == VLRF_ACT_GELU_TANH) return gelu_tanh_f(x);
+    if (ACT == VLRF_ACT_GELU_ERF) return gelu_erf_f(x);
+    return x;
+}
+__device__ __forceinline__ float apply_act_rt(float x, int act) {
+    if (act == VLRF_ACT_GELU_TANH) return gelu_tanh_f(x);
+    if (act == VLRF_ACT_GELU_ERF) return gelu_erf_f(x);
+    return x;
+}

@@ -1,0 +1,310 @@
+// Sampling on the device: one block per row of float32 logits.
+//
+// Order of operations as in the reference's sampler (include/model/transformer.hpp:124-182):
+// temperature ≤ 0 (or a greedy row) → first maximal index (:43-47); else logits/temperature → softmax →
+// keep the top_k most probable → walk by descending probability and cut the first token whose running
+// mass exceeds top_p together with all after it, the most probable always staying (:159-165) →
+// renormalise → draw the first index whose cumulative probability reaches the uniform number u (:175-181).
+// Penalties on generated tokens and the n-gram block (:54-120) are a kernel of their own that edits the
+// logits first.
+//
+// Nothing is sorted.  The cut is found by a radix select over the float bits of the unnormalised
+// probabilities e_i = exp((l_i − max)/T), 8 bits a pass, with per-bin counts and masses; masses are
+// summed as 32.32 fixed-point integers so that every sum is exact and independent of the order in which
+// threads add — the same seed gives the same token on every run.  Equal probabilities at the cut are kept
+// in index order (the reference leaves their order to std::sort / std::partial_sort).
+//
+// The uniform number of a row is a counter-based hash of (rng_key[row], rng_ctr[row]); the counter
+// advances by one per draw, so a request's stream depends on nothing but its key and how many tokens it
+// drew.
+#include "common.cuh"
+
+namespace {
+constexpr int ST = 1024;  // threads per row
+
+__device__ __forceinline__ unsigned long long mix64(unsigned long long x) {
+    x ^= x >> 30; x *= 0xBF58476D1CE4E5B9ull;
+    x ^= x >> 27; x *= 0x94D049BB133111EBull;
+    x ^= x >> 31;
+    return x;
+}
+// u in [0,1) with 24 bits
+__device__ __forceinline__ float uniform01(unsigned long long key, unsigned int ctr) {
+    const unsigned long long x = mix64(key + 0x9E3779B97F4A7C15ull * (unsigned long long)(ctr + 1u));
+    return (float)(x >> 40) * (1.0f / 16777216.0f);
+}
+
+struct ArgMax { float v; int i; };
+__device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {
+    if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+    return a;
+}
+__device__ ArgMax block_argmax(ArgMax a, ArgMax* sm /*32*/) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ArgMax b;
+        b.v = __shfl_xor_sync(0xffffffffu, a.v, o);
+        b.i = __shfl_xor_sync(0xffffffffu, a.i, o);
+        a = better(a, b);
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) sm[warp] = a;
+    __syncthreads();
+    ArgMax r = sm[0];
+    for (int w = 1; w < ST / 32; ++w) r = better(r, sm[w]);
+    return r;
+}
+
+// exclusive block scan; returns this thread's prefix and writes the total
+template <typename T>
+__device__ T block_excl_scan(T v, T* sm /*32*/, T* total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    T inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        T n = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += n;
+    }
+    __syncthreads();
+    if (lane == 31) sm[warp] = inc;
+    __syncthreads();
+    T base = 0, tot = 0;
+    for (int w = 0; w < ST / 32; ++w) {
+        if (w < warp) base += sm[w];
+        tot += sm[w];
+    }
+    *total = tot;
+    return base + inc - v;
+}
+
+__device__ __forceinline__ float unnorm_prob(float logit, float mx, float inv_t) {
+    return expf((logit - mx) * inv_t);
+}
+__device__ __forceinline__ unsigned long long to_fixed(float e) {  // e in [0,1] → 32.32
+    return (unsigned long long)((double)e * 4294967296.0);
+}
+
+__global__ void __launch_bounds__(ST)
+sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __restrict__ temperature,
+              const int* __restrict__ top_k, const float* __restrict__ top_p,
+              const unsigned long long* __restrict__ rng_key, unsigned int* __restrict__ rng_ctr,
+              int* __restrict__ out_token) {
+    __shared__ ArgMax sm_am[32];
+    __shared__ unsigned long long sm_u64[32];
+    __shared__ int sm_i32[32];
+    __shared__ unsigned int h_cnt[256];
+    __shared__ unsigned long long h_mass[256];
+    __shared__ unsigned int s_prefix;
+    __shared__ unsigned int s_cnt_above;
+    __shared__ unsigned long long s_mass_above;
+    __shared__ int s_hit;
+    __shared__ int s_choice;
+
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const float* lg = logits + (size_t)row * ld;
+
+    ArgMax am{-INFINITY, 0x7fffffff};
+    for (int i = tid; i < V; i += ST) {
+        const float v = lg[i];
+        if (v > am.v) { am.v = v; am.i = i; }
+    }
+    am = block_argmax(am, sm_am);
+    if (am.i == 0x7fffffff) am.i = 0;  // a row of NaNs or −inf: defined answer
+    const float temp = temperature ? temperature[row] : 0.f;
+    if (!(temp > 0.f)) {
+        if (tid == 0) out_token[row] = am.i;
+        return;
+    }
+    const float mx = am.v, inv_t = 1.f / temp;
+
+    // total unnormalised mass
+    unsigned long long part = 0;
+    for (int i = tid; i < V; i += ST) part += to_fixed(unnorm_prob(lg[i], mx, inv_t));
+    unsigned long long total = 0;
+    block_excl_scan<unsigned long long>(part, sm_u64, &total);
+
+    const int k_in = top_k ? top_k[row] : 0;
+    const unsigned int k_eff = (k_in > 0 && k_in < V) ? (unsigned int)k_in : (unsigned int)V;
+    const float tp = top_p ? top_p[row] : 1.f;
+    const bool use_p = tp < 1.f;
+    const unsigned long long thresh =
+        use_p ? (unsigned long long)((double)fmaxf(tp, 0.f) * (double)total) : ~0ull;
+
+    // ---- radix select of the cut value -------------------------------------------------------
+    bool keep_all = (k_eff >= (unsigned int)V) && !use_p;
+    unsigned int cut_bits = 0, ties_kept = 0;
+    if (!keep_all) {
+        if (tid == 0) { s_prefix = 0; s_cnt_above = 0; s_mass_above = 0; }
+        unsigned int mask = 0;
+        for (int shift = 24; shift >= 0; shift -= 8) {
+            for (int b = tid; b < 256; b += ST) { h_cnt[b] = 0; h_mass[b] = 0; }
+            __syncthreads();
+            const unsigned int prefix = s_prefix;
+            for (int i = tid; i < V; i += ST) {
+                const float e = unnorm_prob(lg[i], mx, inv_t);
+                const unsigned int bits = __float_as_uint(e);
+                if ((bits & mask) == prefix) {
+                    const unsigned int bin = (bits >> shift) & 255u;
+                    atomicAdd(&h_cnt[bin], 1u);
+                    atomicAdd(&h_mass[bin], to_fixed(e));
+                }
+            }
+            __syncthreads();
+            if (tid == 0) {
+                unsigned int c = s_cnt_above;
+                unsigned long long ms = s_mass_above;
+                int hit = 0;
+                for (int b = 255; b >= 0; --b) {
+                    if (h_cnt[b] == 0) continue;
+                    const unsigned int c2 = c + h_cnt[b];
+                    const unsigned long long ms2 = ms + h_mass[b];
+                    if (c2 >= k_eff || ms2 > thresh) {
+                        s_prefix = prefix | ((unsigned int)b << shift);
+                        hit = 1;
+                        break;
+                    }
+                    c = c2; ms = ms2;
+                }
+                s_cnt_above = c; s_mass_above = ms; s_hit = hit;
+            }
+            __syncthreads();
+            if (!s_hit) { keep_all = true; break; }  // uniform: read from shared memory
+            mask |= 255u << shift;
+        }
+        if (!keep_all) {
+            cut_bits = s_prefix;
+            const unsigned int above = s_cnt_above;
+            const unsigned long long e_cut = to_fixed(__uint_as_float(cut_bits));
+            unsigned long long by_p = ~0ull;
+            if (use_p && e_cut > 0) by_p = (thresh >= s_mass_above) ? (thresh - s_mass_above) / e_cut : 0ull;
+            if (above == 0 && by_p == 0) by_p = 1;  // the most probable token always stays
+            unsigned long long by_k = (unsigned long long)(k_eff - above);  // above < k_eff by construction
+            ties_kept = (unsigned int)min(by_p, by_k);
+        }
+    }
+
+    // ---- draw in index order over what is kept ---------------------------------------------------
+    const int chunk = (V + ST - 1) / ST;
+    const int i0 = min(V, tid * chunk), i1 = min(V, i0 + chunk);
+    int my_ties = 0;
+    if (!keep_all)
+        for (int i = i0; i < i1; ++i)
+            my_ties += (__float_as_uint(unnorm_prob(lg[i], mx, inv_t)) == cut_bits);
+    int ties_total = 0;
+    const int tie_base = block_excl_scan<int>(my_ties, sm_i32, &ties_total);
+
+    unsigned long long my_mass = 0;
+    {
+        int seen = tie_base;
+        for (int i = i0; i < i1; ++i) {
+            const float e = unnorm_prob(lg[i], mx, inv_t);
+            bool keep = true;
+            if (!keep_all) {
+                const unsigned int bits = __float_as_uint(e);
+                if (bits == cut_bits) { keep = (unsigned int)seen < ties_kept; ++seen; }
+                else keep = bits > cut_bits;
+            }
+            if (keep) my_mass += to_fixed(e);
+        }
+    }
+    unsigned long long kept_total = 0;
+    const unsigned long long mass_base = block_excl_scan<unsigned long long>(my_mass, sm_u64, &kept_total);
+    if (tid == 0) s_choice = -1;
+    __syncthreads();
+    if (kept_total == 0) {  // nothing left to draw from (:169-172): the maximal logit
+        if (tid == 0) out_token[row] = am.i;
+    } else {
+        const unsigned int ctr = rng_ctr[row];
+        const float u = uniform01(rng_key[row], ctr);
+        unsigned long long tgt = (unsigned long long)((double)u * (double)kept_total) + 1ull;
+        if (tgt > kept_total) tgt = kept_total;
+        if (my_mass > 0 && mass_base < tgt && tgt <= mass_base + my_mass) {
+            unsigned long long cum = mass_base;
+            int seen = tie_base;
+            for (int i = i0; i < i1; ++i) {
+                const float e = unnorm_prob(lg[i], mx, inv_t);
+                bool keep = true;
+                if (!keep_all) {
+                    const unsigned int bits = __float_as_uint(e);
+                    if (bits == cut_bits) { keep = (unsigned int)seen < ties_kept; ++seen; }
+                    else keep = bits > cut_bits;
+                }
+                if (keep) {
+                    cum += to_fixed(e);
+                    if (cum >= tgt) { s_choice = i; break; }
+                }
+            }
+        }
+        __syncthreads();
+        if (tid == 0) out_token[row] = (s_choice >= 0) ? s_choice : am.i;
+    }
+    __syncthreads();
+    if (tid == 0) rng_ctr[row] = rng_ctr[row] + 1u;
+}
+
+// Penalties over the tokens a request generated so far, and the n-gram block
+// (include/model/transformer.hpp:54-120).  One block per row; thread j looks at generated token j.
+__global__ void penalties_kernel(float* __restrict__ logits, int ld, int V, const int* __restrict__ gen,
+                                 int gen_ld, const int* __restrict__ gen_len,
+                                 const float* __restrict__ rep, const float* __restrict__ freq,
+                                 const float* __restrict__ pres, const int* __restrict__ ngram) {
+    const int row = blockIdx.x;
+    const int n = gen_len[row];
+    if (n <= 0) return;
+    const int* g = gen + (size_t)row * gen_ld;
+    float* lg = logits + (size_t)row * ld;
+    const float r = rep ? rep[row] : 1.f, f = freq ? freq[row] : 0.f, p = pres ? pres[row] : 0.f;
+    if (r != 1.f || f != 0.f || p != 0.f) {
+        for (int j = threadIdx.x; j < n; j += blockDim.x) {
+            const int tok = g[j];
+            if (tok < 0 || tok >= V) continue;
+            bool first = true;
+            for (int i = 0; i < j; ++i)
+                if (g[i] == tok) { first = false; break; }
+            if (!first) continue;  // the first occurrence speaks for all
+            int count = 1;
+            for (int i = j + 1; i < n; ++i) count += (g[i] == tok);
+            float v = lg[tok];
+            if (r != 1.f) v = (v > 0.f) ? v / r : v * r;
+            if (f != 0.f) v -= f * (float)count;
+            if (p != 0.f) v -= p;
+            lg[tok] = v;
+        }
+    }
+    __syncthreads();
+    const int ng = ngram ? ngram[row] : 0;
+    if (ng > 1 && n >= ng - 1) {
+        const int* suffix = g + n - (ng - 1);
+        for (int start = threadIdx.x; start + ng <= n; start += blockDim.x) {
+            bool match = true;
+            for (int k = 0; k < ng - 1; ++k)
+                if (g[start + k] != suffix[k]) { match = false; break; }
+            if (match) {
+                const int forbidden = g[start + ng - 1];
+                if (forbidden >= 0 && forbidden < V) lg[forbidden] = -INFINITY;
+            }
+        }
+    }
+}
+}  // namespace
+
+extern "C" int vlrf_sample(const float* logits, int ld, int n_rows, int V, const float* temperature,
+                           const int* top_k, const float* top_p, const unsigned long long* rng_key,
+                           unsigned int* rng_ctr, int* out_token, cudaStream_t stream) {
+    VLRF_REQUIRE(n_rows >= 0 && V > 0 && ld >= V, "sample: bad sizes rows=%d V=%d ld=%d", n_rows, V, ld);
+    VLRF_REQUIRE(temperature == nullptr || (rng_key != nullptr && rng_ctr != nullptr),
+                 "sample: temperature sampling needs the rows' random keys and counters");
+    if (n_rows == 0) return VLRF_OK;
+    sample_kernel<<<n_rows, ST, 0, stream>>>(logits, ld, V, temperature, top_k, top_p, rng_key, rng_ctr, out_token);
+    return vlrf_check_launch("sample");
+}
+
+extern "C" int vlrf_apply_penalties(float* logits, int ld, int n_rows, int V, const int* gen, int gen_ld,
+                                    const int* gen_len, const float* rep, const float* freq,
+                                    const float* pres, const int* ngram, cudaStream_t stream) {
+    VLRF_REQUIRE(n_rows >= 0 && V > 0 && ld >= V && gen_ld >= 0, "penalties: bad sizes");
+    if (n_rows == 0) return VLRF_OK;
+    penalties_kernel<<<n_rows, 256, 0, stream>>>(logits, ld, V, gen, gen_ld, gen_len, rep, freq, pres, ngram);
+    return vlrf_check_launch("penalties");
+}

@@ -1,0 +1,29 @@
+"""From a model folder to a model on the device."""
+from __future__ import annotations
+
+import torch
+
+from ..weights.model_dir import open_model_dir
+from .model import BuildOptions, DecoderModel
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+
+
+def parse_dtype(name) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        if name not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"the engine computes in bfloat16 or float32, not {name}")
+        return name
+    try:
+        return DTYPES[str(name)]
+    except KeyError:
+        raise ValueError(f"unknown dtype '{name}'; choose bfloat16 or float32") from None
+
+
+def load_model(model_dir, dtype="bfloat16", device="cuda:0") -> DecoderModel:
+    """Read config.json, pick the architecture it names, check model.safetensors against that
+    architecture's tensor list and assemble the model on the device."""
+    import vlrf_b200.models  # noqa: F401  (registers the architectures)
+    arch, cfg, weights = open_model_dir(model_dir)
+    options = BuildOptions(dtype=parse_dtype(dtype), device=torch.device(device))
+    return arch.build(cfg, weights, options)

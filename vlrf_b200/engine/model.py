@@ -1,0 +1,93 @@
+"""A decoder model as data: parts, layers, and the order in which the layers run.
+
+`DecoderModel` knows no architecture.  An architecture's builder (see `vlrf_b200.models`) makes the
+parts from a configuration and the checked weights and hands them over with a *schedule*: the list of
+layer calls of one forward pass.  A call names the layer to run, so a layer may appear twice, and may
+name an earlier call whose cache it reads instead of keeping one of its own.
+"""
+from __future__ import annotations
+
+import dataclasses
+
+import torch
+
+from ..parts.context import StepContext
+
+
+@dataclasses.dataclass(frozen=True)
+class LayerCall:
+    layer: int                    # index into DecoderModel.layers
+    reads_cache_of: int | None = None   # index of an earlier call in the schedule, or None: own cache
+
+
+@dataclasses.dataclass
+class BuildOptions:
+    dtype: torch.dtype            # torch.bfloat16 (serving kernels) or torch.float32 (everything 32-bit)
+    device: torch.device
+
+
+class DecoderModel:
+    def __init__(self, *, config, embedding, layers, schedule, final_norm, head, options: BuildOptions,
+                 max_seq_len: int):
+        self.config = config
+        self.embedding, self.layers, self.final_norm, self.head = embedding, list(layers), final_norm, head
+        self.schedule = [c if isinstance(c, LayerCall) else LayerCall(int(c)) for c in schedule]
+        self.options = options
+        self.act_dtype = options.dtype
+        self.device = options.device
+        self.max_seq_len = int(max_seq_len)
+        self.width = embedding.width
+        self.vocab_size = head.vocab_size
+        for i, call in enumerate(self.schedule):
+            if not (0 <= call.layer < len(self.layers)):
+                raise ValueError(f"schedule entry {i} names layer {call.layer}, which does not exist")
+            if call.reads_cache_of is not None:
+                j = call.reads_cache_of
+                if not (0 <= j < i) or self.schedule[j].reads_cache_of is not None:
+                    raise ValueError(f"schedule entry {i} must read the cache of an earlier entry that owns one")
+                if self.layers[self.schedule[j].layer].cache_need() != self.layers[call.layer].cache_need():
+                    raise ValueError(f"schedule entry {i} reads a cache whose shape differs from its own need")
+
+    def cache_needs(self) -> list:
+        """For every schedule entry what it keeps per sequence (None for entries that read another's)."""
+        return [None if c.reads_cache_of is not None else self.layers[c.layer].cache_need()
+                for c in self.schedule]
+
+    def weight_bytes(self) -> int:
+        seen, total = set(), 0
+
+        def visit(obj):
+            nonlocal total
+            if isinstance(obj, torch.Tensor):
+                if obj.data_ptr() not in seen:
+                    seen.add(obj.data_ptr())
+                    total += obj.numel() * obj.element_size()
+            elif hasattr(obj, "__dict__"):
+                for v in vars(obj).values():
+                    visit(v)
+            elif isinstance(obj, (list, tuple)):
+                for v in obj:
+                    visit(v)
+
+        for part in (self.embedding, self.layers, self.final_norm, self.head):
+            visit(part)
+        return total
+
+    def forward(self, ctx: StepContext, cache) -> torch.Tensor:
+        """Run the tokens of `ctx` through all scheduled layers; returns float32 logits
+        [ctx.n_logit_rows, vocab] for the rows in ctx.logit_rows
+        (reference: include/model/transformer.hpp:335-424, which keeps the last row only)."""
+        x = ctx.ws.get("residual", ctx.n_tokens, self.width, torch.float32)
+        self.embedding(ctx, x)
+        for i, call in enumerate(self.schedule):
+            owner = i if call.reads_cache_of is None else call.reads_cache_of
+            view = cache.view(owner) if cache.needs[owner] is not None else None
+            self.layers[call.layer].forward(x, ctx, view, writes_cache=call.reads_cache_of is None)
+        n = ctx.n_logit_rows
+        logits = ctx.ws.get("logits", max(n, 1), self.vocab_size, torch.float32)
+        if n == 0:
+            return logits[:0]
+        hn = ctx.ws.get("final_normed", n, self.width, ctx.act_dtype)
+        self.final_norm(x, hn, ctx.logit_rows)
+        self.head(hn, logits, n)
+        return logits[:n]

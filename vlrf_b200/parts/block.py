@@ -1,0 +1,26 @@
+"""Blocks: how a layer arranges its norm, mixer and feed-forward around the residual stream."""
+from __future__ import annotations
+
+import torch
+
+from .context import StepContext
+from .registry import register_part
+
+
+@register_part("block", "pre_norm")
+class PreNormBlock:
+    """x += mixer(norm1(x)); x += ffn(norm2(x)) (reference: include/model/transformer_block.hpp:149-159).
+    The residual stream x stays float32; the normed rows are in the activation dtype."""
+
+    def __init__(self, norm1, mixer, norm2, feed_forward):
+        self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, view, writes_cache: bool = True) -> None:
+        h = ctx.ws.get("block_normed", ctx.n_tokens, x.shape[1], ctx.act_dtype)
+        self.norm1(x, h)
+        self.mixer.forward(h, x, ctx, view, writes_cache)
+        self.norm2(x, h)
+        self.feed_forward.forward(h, x, ctx)

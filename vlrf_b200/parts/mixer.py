@@ -1,0 +1,74 @@
+"""Mixers: the parts that let a token see other tokens.  Attention is the one this library ships.
+
+Interface of a mixer (what `Block` and the step rely on):
+
+    cache_need() -> KVNeed | StateNeed | None     what it keeps per sequence
+    forward(h, x, ctx, view, writes_cache=True)   x += mix(h), in place.
+        h     [n_tokens, width]  normed input in the activation dtype
+        x     [n_tokens, width]  float32 residual stream
+        ctx   StepContext        tokens' slots and positions, scratch, error word
+        view  CacheView | None   this layer's storage (another layer's when the layer list says so;
+                                 then writes_cache is False and the mixer only reads it)
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache import KVNeed
+from ..csrc import ops
+from .context import StepContext
+from .registry import register_part
+
+
+@register_part("mixer", "causal_self_attention")
+class CausalSelfAttention:
+    """Multi-head causal attention with a fused q/k/v projection over a paged cache.
+
+    q, k, v = h·W_qkvᵀ + b (reference: include/model/attention.hpp:98-105, as one product); k and v
+    are written into the cache first (attention.hpp:127-129); every query attends the keys 0…its
+    position of its own sequence with score·scale, softmax in float32 (attention.hpp:207-309,
+    :373-374); the heads are merged and projected, and the residual is added in the projection's
+    epilogue (attention.hpp:183-184, include/model/transformer_block.hpp:153).
+
+    n_kv_heads < n_heads shares each key/value head among n_heads/n_kv_heads query heads; window > 0
+    limits a query to the last `window` keys.  GPT-2 uses neither.
+    """
+
+    def __init__(self, w_qkv, b_qkv, w_out, b_out, *, n_heads: int, n_kv_heads: int, head_dim: int,
+                 scale: float, window: int = 0, position=None):
+        width_q, width_kv = n_heads * head_dim, n_kv_heads * head_dim
+        if w_qkv.shape[0] != width_q + 2 * width_kv:
+            raise ValueError(f"attention: fused projection has {w_qkv.shape[0]} rows, "
+                             f"{width_q + 2 * width_kv} expected")
+        if w_out.shape[1] != width_q:
+            raise ValueError("attention: output projection does not take the merged heads")
+        if n_heads % n_kv_heads != 0:
+            raise ValueError(f"attention: {n_heads} heads cannot share {n_kv_heads} key/value heads")
+        if position is not None and getattr(position, "where", None) == "qk":
+            raise NotImplementedError("attention: no position encoding acting on q/k is built into this mixer")
+        self.w_qkv, self.b_qkv, self.w_out, self.b_out = w_qkv, b_qkv, w_out, b_out
+        self.n_heads, self.n_kv_heads, self.head_dim = n_heads, n_kv_heads, head_dim
+        self.scale, self.window = float(scale), int(window)
+        self.q_off, self.k_off, self.v_off = 0, width_q, width_q + width_kv
+        self.qkv_width = width_q + 2 * width_kv
+
+    def cache_need(self):
+        if self.window > 0:
+            return KVNeed(self.n_kv_heads, self.head_dim, "window", self.window)
+        return KVNeed(self.n_kv_heads, self.head_dim, "full")
+
+    def forward(self, h: torch.Tensor, x: torch.Tensor, ctx: StepContext, view, writes_cache: bool = True) -> None:
+        T = ctx.n_tokens
+        qkv = ctx.ws.get("attn_qkv", T, self.qkv_width, ctx.act_dtype)
+        ops.linear(h, self.w_qkv, self.b_qkv, qkv)
+        if writes_cache:
+            ops.kv_append(qkv, self.k_off, self.v_off, view.k, view.v, view.block_table, ctx.tok_slot,
+                          ctx.tok_pos, T, self.n_kv_heads, self.head_dim, ctx.dev_err)
+        merged = ctx.ws.get("attn_out", T, self.n_heads * self.head_dim, ctx.act_dtype)
+        self._attend(qkv, view, merged, ctx)
+        ops.linear(merged, self.w_out, self.b_out, x, residual=x)
+
+    def _attend(self, qkv, view, merged, ctx: StepContext) -> None:
+        ops.attention_generic(qkv, self.q_off, view.k, view.v, view.block_table, ctx.tok_slot, ctx.tok_pos,
+                              merged, ctx.n_tokens, self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
+                              self.window, ctx.dev_err)
