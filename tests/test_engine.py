@@ -1,0 +1,129 @@
+"""The engine against the plain implementation: whole requests, the last 32 tokens one by one, batches
+of unequal lengths one after another, long decoding and the first tokens — in 32-bit and in bfloat16."""
+import pytest
+import torch
+
+import plain_gpt2 as plain
+from conftest import TOL_BF16, TOL_F32, random_ids, rel_err
+from engine_drives import drive_batches, drive_tail_one_by_one, drive_whole, poison
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [("float32", TOL_F32), ("bfloat16", TOL_BF16)]
+#: request lengths per model: BASELINE's batches (5/17/31 and 1/9/40/100) with their decode steps added
+LENGTHS = {"tiny_a": [5 + 16, 17 + 16, 31 + 16, 70, 128], "tiny_b": [1 + 24, 9 + 24, 40 + 24, 100 + 24, 200, 256]}
+
+
+@pytest.fixture(scope="module")
+def requests_and_truth(plain_models):
+    out = {}
+    for name, (cfg, w) in plain_models.items():
+        reqs = [random_ids(cfg["vocab_size"], n, 7 + i) for i, n in enumerate(LENGTHS[name])]
+        truth = [plain.logits_all_positions(cfg, w, ids) for ids in reqs]
+        out[name] = (reqs, truth)
+    return out
+
+
+def make_engine(model_dirs, name, dtype, max_tokens):
+    from vlrf_b200.engine import Engine, load_model
+    eng = Engine(load_model(model_dirs[name], dtype), max_tokens=max_tokens)
+    poison(eng)
+    return eng
+
+
+def compare(got, truth, tol, what):
+    worst = 0.0
+    for i, (g, t) in enumerate(zip(got, truth)):
+        assert g.shape == t.shape, f"{what}: request {i} has shape {tuple(g.shape)}, expected {tuple(t.shape)}"
+        assert torch.isfinite(g).all(), f"{what}: request {i} has non-finite logits (something unwritten was read)"
+        scale = float(t.abs().max())
+        err = (g.double() - t).abs().max(dim=1).values / scale
+        bad = (err > tol).nonzero()
+        assert bad.numel() == 0, (f"{what}: request {i} (length {len(t)}) first differs at position {int(bad[0])} "
+                                  f"with error {float(err[bad[0]]):.3e} of the logit scale (tolerance {tol:.0e})")
+        worst = max(worst, float(err.max()))
+    return worst
+
+
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_each_request_alone_and_whole(model_dirs, requests_and_truth, name, dtype, tol):
+    reqs, truth = requests_and_truth[name]
+    eng = make_engine(model_dirs, name, dtype, 256)
+    compare(drive_whole(eng, reqs), truth, tol, "whole")
+    eng.cache.check()
+    assert eng.cache.slots.n_held == 0
+
+
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_last_32_tokens_one_by_one(model_dirs, requests_and_truth, name, dtype, tol):
+    reqs, truth = requests_and_truth[name]
+    eng = make_engine(model_dirs, name, dtype, 256)
+    compare(drive_tail_one_by_one(eng, reqs, 32), truth, tol, "prefix + 32 single tokens")
+
+
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_unequal_batches_one_after_another(model_dirs, requests_and_truth, name, dtype, tol):
+    reqs, truth = requests_and_truth[name]
+    decode = 16 if name == "tiny_a" else 24
+    prompt_lens = [max(1, len(r) - decode) for r in reqs]
+    # a cache just large enough for one batch: the second batch must reuse slots and blocks of the first
+    batch = 3 if name == "tiny_a" else 4
+    need = max(sum((len(r) + 63) // 64 * 64 for r in reqs[b:b + batch]) for b in range(0, len(reqs), batch))
+    eng = make_engine(model_dirs, name, dtype, need)
+    got = drive_batches(eng, reqs, batch, prompt_lens)
+    compare(got, truth, tol, "unequal batches")
+    assert eng.cache.slots.n_held == 0
+    # the same again in another order: every slot and block has been used before
+    order = list(reversed(range(len(reqs))))
+    got2 = drive_batches(eng, [reqs[i] for i in order], batch, [prompt_lens[i] for i in order])
+    compare(got2, [truth[i] for i in order], tol, "unequal batches, reused cache")
+
+
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+def test_long_decoding_from_one_token(model_dirs, plain_models, dtype, tol):
+    cfg, w = plain_models["tiny_b"]
+    ids = random_ids(cfg["vocab_size"], cfg["n_positions"], 99)
+    truth = plain.logits_all_positions(cfg, w, ids)
+    eng = make_engine(model_dirs, "tiny_b", dtype, 256)
+    got = drive_tail_one_by_one(eng, [ids], tail=len(ids) - 1)
+    compare(got, [truth], tol, "decoding all 256 positions")
+
+
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_first_tokens(model_dirs, plain_models, name, dtype, tol):
+    cfg, w = plain_models[name]
+    reqs = [random_ids(cfg["vocab_size"], n, 50 + n) for n in (1, 2, 3, 1)]
+    truth = [plain.logits_all_positions(cfg, w, ids) for ids in reqs]
+    eng = make_engine(model_dirs, name, dtype, 256)
+    compare(drive_whole(eng, reqs), truth, tol, "first tokens, whole")
+    compare(drive_batches(eng, reqs, 4, [1, 1, 1, 1]), truth, tol, "first tokens, batch")
+
+
+def test_step_refuses_what_it_cannot_run(model_dirs):
+    from vlrf_b200.cache import CacheError
+    from vlrf_b200.engine import StepEntry, StepError
+    eng = make_engine(model_dirs, "tiny_a", "float32", 192)
+    s = eng.start_sequence()
+    with pytest.raises(StepError, match="outside the vocabulary"):
+        eng.step([StepEntry(s, [512], [0])])
+    with pytest.raises(StepError, match="at least one token"):
+        eng.step([StepEntry(s, [], [])])
+    with pytest.raises(StepError, match="wanted place"):
+        eng.step([StepEntry(s, [1, 2], [2])])
+    with pytest.raises(StepError, match="exceed"):
+        eng.step([StepEntry(s, [1] * 129, [])])
+    with pytest.raises(StepError, match="twice"):
+        eng.step([StepEntry(s, [1], []), StepEntry(s, [2], [])])
+    with pytest.raises(StepError, match="not held"):
+        eng.step([StepEntry(5, [1], [])])
+    assert eng.length(s) == 0
+    eng.step([StepEntry(s, [1] * 100, [])])
+    s2 = eng.start_sequence()
+    with pytest.raises(CacheError, match="cache full"):
+        eng.step([StepEntry(s2, [1] * 65, [0])])
+    assert eng.step([StepEntry(s2, [1] * 3, [])]).shape == (0, 512)
+    eng.check_device_errors()

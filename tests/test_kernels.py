@@ -1,0 +1,332 @@
+"""Each kernel alone against its plain reference, at sizes other than the engine tests use."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_gpt2 as plain
+from conftest import rel_err
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def g(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+def randn(*shape, seed=0, dtype=torch.float32, scale=1.0):
+    return (torch.randn(*shape, generator=g(seed)) * scale).to(dtype)
+
+
+def err_word():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("d,V,P", [(80, 300, 77), (1600, 1000, 50)])
+def test_embed(dtype, d, V, P):
+    from vlrf_b200.csrc import ops
+    wte, wpe = randn(V, d, seed=1, dtype=dtype), randn(P, d, seed=2, dtype=dtype)
+    tok = torch.randint(0, V, (45,), generator=g(3), dtype=torch.int32)
+    pos = torch.randint(0, P, (45,), generator=g(4), dtype=torch.int32)
+    out = torch.full((45, d), float("nan"), device=DEV)
+    e = err_word()
+    ops.embed(wte.to(DEV), wpe.to(DEV), tok.to(DEV), pos.to(DEV), out, e)
+    want = plain.embed_tokens(wte.double(), tok.tolist()) + wpe.double()[pos.long()]
+    assert rel_err(out.cpu(), want) < 1e-6 and int(e.item()) == 0
+    ops.embed(wte.to(DEV), None, tok.to(DEV), None, out, e)
+    assert torch.equal(out.cpu(), wte.float()[tok.long()])
+    # an id outside the table is clamped and reported, never read out of bounds
+    bad = tok.clone(); bad[7] = V + 5
+    ops.embed(wte.to(DEV), wpe.to(DEV), bad.to(DEV), pos.to(DEV), out, e)
+    assert int(e.item()) == 1
+
+
+@pytest.mark.parametrize("out_dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 5e-3)])
+@pytest.mark.parametrize("d,eps", [(80, 1e-3), (1000, 1e-5), (1600, 1e-6), (16, 1e-5)])
+def test_layernorm(out_dtype, tol, d, eps):
+    from vlrf_b200.csrc import ops
+    x = randn(33, d, seed=5) * 3 + 1.5
+    gamma, beta = randn(d, seed=6) * 0.5 + 1, randn(d, seed=7)
+    want = plain.layer_norm(x.double(), gamma.double(), beta.double(), eps)
+    out = torch.empty(33, d, dtype=out_dtype, device=DEV)
+    ops.layernorm(x.to(DEV), gamma.to(DEV), beta.to(DEV), eps, out)
+    assert rel_err(out.float().cpu(), want) < tol
+    rows = torch.tensor([32, 0, 5, 5], dtype=torch.int32)
+    out2 = torch.empty(4, d, dtype=out_dtype, device=DEV)
+    ops.layernorm(x.to(DEV), gamma.to(DEV), beta.to(DEV), eps, out2, rows.to(DEV))
+    assert rel_err(out2.float().cpu(), want[rows.long()]) < tol
+
+
+def test_layernorm_small_variance_uses_eps():
+    from vlrf_b200.csrc import ops
+    x = torch.full((2, 64), 3.0) + randn(2, 64, seed=8) * 1e-4
+    gamma, beta = torch.ones(64), torch.zeros(64)
+    for eps in (1e-5, 1e-6):
+        out = torch.empty(2, 64, device=DEV)
+        ops.layernorm(x.to(DEV), gamma.to(DEV), beta.to(DEV), eps, out)
+        assert rel_err(out.cpu(), plain.layer_norm(x.double(), gamma.double(), beta.double(), eps)) < 1e-3
+
+
+# ------------------------------------------------------------------------------------------------
+GEMM_SHAPES = [(1, 53, 19), (37, 53, 19), (64, 64, 16), (130, 200, 72), (3, 1000, 96), (257, 96, 320)]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+@pytest.mark.parametrize("in_dtype,out_dtype,tol", [(torch.float32, torch.float32, 2e-6),
+                                                    (torch.bfloat16, torch.float32, 2e-6),
+                                                    (torch.bfloat16, torch.bfloat16, 5e-3)])
+@pytest.mark.parametrize("act", [None, "gelu_tanh", "gelu_erf"])
+def test_linear(M, N, K, in_dtype, out_dtype, tol, act):
+    from vlrf_b200.csrc import ops
+    x, w = randn(M, K, seed=9, dtype=in_dtype), randn(N, K, seed=10, dtype=in_dtype, scale=0.3)
+    bias, res = randn(N, seed=11), randn(M, N, seed=12)
+    want = x.double() @ w.double().T + bias.double()
+    if act == "gelu_tanh":
+        want = plain.gelu_tanh(want)
+    elif act == "gelu_erf":
+        want = plain.gelu_erf(want)
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops.linear(x.to(DEV), w.to(DEV), bias.to(DEV), out, act=act)
+    assert rel_err(out.float().cpu(), want) < tol
+    if out_dtype == torch.float32:   # residual sum in place, as the blocks use it
+        acc = res.clone().to(DEV)
+        ops.linear(x.to(DEV), w.to(DEV), bias.to(DEV), acc, act=act, residual=acc)
+        assert rel_err(acc.cpu(), want + res.double()) < tol
+        nob = torch.empty(M, N, device=DEV)
+        ops.linear(x.to(DEV), w.to(DEV), None, nob)
+        assert rel_err(nob.cpu(), x.double() @ w.double().T) < tol
+
+
+def test_linear_rows_do_not_depend_on_the_batch():
+    from vlrf_b200.csrc import ops
+    x, w, b = randn(70, 96, seed=13), randn(200, 96, seed=14), randn(200, seed=15)
+    full = torch.empty(70, 200, device=DEV)
+    ops.linear(x.to(DEV), w.to(DEV), b.to(DEV), full)
+    one = torch.empty(1, 200, device=DEV)
+    ops.linear(x[41:42].contiguous().to(DEV), w.to(DEV), b.to(DEV), one)
+    assert torch.equal(full[41:42], one)
+
+
+# ------------------------------------------------------------------------------------------------
+def paged(k, v, n_blocks, order_seed, dtype):
+    """Put [H, C, dh] keys and values of one sequence into a pool with scattered blocks; unused pool
+    entries are NaN."""
+    H, C, dh = k.shape
+    nb = (C + 63) // 64
+    perm = torch.randperm(n_blocks, generator=g(order_seed))[:nb]
+    kp = torch.full((n_blocks, H, 64, dh), float("nan"), dtype=dtype)
+    vp = torch.full((n_blocks, H, 64, dh), float("nan"), dtype=dtype)
+    for i, b in enumerate(perm.tolist()):
+        n = min(64, C - 64 * i)
+        kp[b, :, :n] = k[:, 64 * i:64 * i + n].to(dtype)
+        vp[b, :, :n] = v[:, 64 * i:64 * i + n].to(dtype)
+    return kp, vp, perm.to(torch.int32)
+
+
+def run_attention(q, k, v, *, dtype, scale, window=0, past=None, impl="generic"):
+    """q [H, T, dh] are the LAST T positions of a context of C = k.shape[1] tokens."""
+    from vlrf_b200.csrc import ops
+    H, T, dh = q.shape
+    Hkv, C, _ = k.shape
+    kp, vp, blocks = paged(k, v, 12, 21, dtype)
+    table = torch.full((3, 10), -1, dtype=torch.int32)
+    table[1, :blocks.numel()] = blocks
+    qkv = torch.zeros(T, H * dh + 5 * 16, dtype=dtype)          # q sits at an offset inside a wider row
+    qkv[:, 16:16 + H * dh] = q.permute(1, 0, 2).reshape(T, H * dh).to(dtype)
+    out = torch.full((T, H * dh), float("nan"), dtype=dtype, device=DEV)
+    e = err_word()
+    slot = torch.full((T,), 1, dtype=torch.int32)
+    pos = torch.arange(C - T, C, dtype=torch.int32)
+    ops.attention_generic(qkv.to(DEV), 16, kp.to(DEV), vp.to(DEV), table.to(DEV), slot.to(DEV), pos.to(DEV), out, T,
+                          H, Hkv, dh, scale, window, e)
+    assert int(e.item()) == 0
+    return out.float().cpu().reshape(T, H, dh).permute(1, 0, 2)
+
+
+def plain_attention(q, k, v, scale, window=0):
+    H, T, dh = q.shape
+    Hkv, C, _ = k.shape
+    rep = H // Hkv
+    kk, vv = k.repeat_interleave(rep, 0).double(), v.repeat_interleave(rep, 0).double()
+    qq = torch.zeros(H, C, dh, dtype=torch.float64)
+    qq[:, C - T:] = q.double()
+    return plain.causal_attention(qq, kk, vv, scale, window)[:, C - T:]
+
+
+ATT_CASES = [  # H, Hkv, dh, T, C   (tails, decode, continuation — as tests/test_flash_attention.cpp:96-121)
+    (3, 3, 16, 37, 37), (4, 4, 32, 130, 130), (2, 2, 64, 1, 200), (2, 1, 64, 200, 500), (6, 2, 48, 64, 64),
+    (4, 1, 80, 65, 129), (1, 1, 128, 5, 70), (5, 5, 256, 3, 66), (12, 12, 64, 128, 128),
+]
+
+
+@pytest.mark.parametrize("H,Hkv,dh,T,C", ATT_CASES)
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 1.5e-2)])
+def test_attention_generic(H, Hkv, dh, T, C, dtype, tol):
+    q, k, v = randn(H, T, dh, seed=30), randn(Hkv, C, dh, seed=31), randn(Hkv, C, dh, seed=32)
+    if dtype == torch.bfloat16:   # the kernel sees bfloat16 inputs; compare on what it sees
+        q, k, v = (t.to(dtype).float() for t in (q, k, v))
+    scale = 0.7 / math.sqrt(dh)
+    got = run_attention(q, k, v, dtype=dtype, scale=scale)
+    assert rel_err(got, plain_attention(q, k, v, scale)) < tol
+
+
+@pytest.mark.parametrize("window", [1, 31, 32, 33, 64, 100])
+def test_attention_window_edges(window):
+    H, dh, T, C = 2, 32, 150, 150
+    q, k, v = randn(H, T, dh, seed=33), randn(H, C, dh, seed=34), randn(H, C, dh, seed=35)
+    # make the key just outside each query's window the one it would like best
+    for t in range(window, C):
+        k[:, t - window] = 0
+    got = run_attention(q, k, v, dtype=torch.float32, scale=0.2, window=window)
+    assert rel_err(got, plain_attention(q, k, v, 0.2, window)) < 2e-5
+    k2 = k.clone()
+    k2[:, 3] = q[:, 3 + window] * 50 if 3 + window < T else k2[:, 3]   # would dominate if it were seen
+    got2 = run_attention(q, k2, v, dtype=torch.float32, scale=0.2, window=window)
+    assert rel_err(got2[:, 3 + window], plain_attention(q, k2, v, 0.2, window)[:, 3 + window]) < 2e-5
+
+
+@pytest.mark.parametrize("far", [0, 63, 64, 257, 511])
+def test_attention_finds_one_far_key(far):
+    """One key among hundreds carries the whole weight: the output must be that key's value."""
+    H, dh, C = 2, 64, 512
+    q, k, v = randn(H, 1, dh, seed=36), randn(H, C, dh, seed=37) * 0.1, randn(H, C, dh, seed=38)
+    k[:, far] = q[:, 0] * 4.0
+    got = run_attention(q, k, v, dtype=torch.float32, scale=1.0)
+    assert rel_err(got[:, 0], v[:, far]) < 1e-4
+    assert rel_err(got, plain_attention(q, k, v, 1.0)) < 2e-5
+
+
+def test_kv_append_writes_each_token_where_its_slot_says():
+    from vlrf_b200.csrc import ops
+    Hkv, dh, T = 3, 16, 70
+    for dtype in (torch.float32, torch.bfloat16):
+        qkv = randn(T, 5 * Hkv * dh, seed=39, dtype=dtype)
+        kc = torch.zeros(6, Hkv, 64, dh, dtype=dtype, device=DEV)
+        vc = torch.zeros_like(kc)
+        table = torch.tensor([[4, 1, -1], [2, 5, 0]], dtype=torch.int32)
+        slot = torch.tensor([0] * 30 + [1] * 40, dtype=torch.int32)
+        pos = torch.cat([torch.arange(50, 80), torch.arange(100, 140)]).to(torch.int32)
+        e = err_word()
+        ops.kv_append(qkv.to(DEV), 2 * Hkv * dh, 4 * Hkv * dh, kc, vc, table.to(DEV), slot.to(DEV), pos.to(DEV), T, Hkv,
+                      dh, e)
+        assert int(e.item()) == 0
+        for t in range(T):
+            b = int(table[slot[t], pos[t] // 64])
+            assert torch.equal(kc[b, :, pos[t] % 64].cpu().reshape(-1), qkv[t, 2 * Hkv * dh:3 * Hkv * dh])
+            assert torch.equal(vc[b, :, pos[t] % 64].cpu().reshape(-1), qkv[t, 4 * Hkv * dh:5 * Hkv * dh])
+        assert float(kc[3].abs().sum()) == 0          # an unmapped block stays untouched
+        # a token whose block is not mapped is skipped and reported
+        pos2 = pos.clone(); pos2[0] = 130
+        ops.kv_append(qkv.to(DEV), 2 * Hkv * dh, 4 * Hkv * dh, kc, vc, table.to(DEV), slot.to(DEV), pos2.to(DEV), T,
+                      Hkv, dh, e)
+        assert int(e.item()) == 4
+
+
+# ------------------------------------------------------------------------------------------------
+def test_argmax_takes_the_first_maximum():
+    from vlrf_b200.csrc import ops
+    V = 50257
+    lg = randn(5, V, seed=40)
+    lg[0, 777] = lg[0, 40000] = 9.0
+    lg[1, V - 1] = 9.0
+    lg[2, 0] = 9.0
+    out = torch.zeros(5, dtype=torch.int32, device=DEV)
+    ops.sample(lg.to(DEV), 5, out)
+    assert out.tolist() == [777, V - 1, 0, int(lg[3].argmax()), int(lg[4].argmax())]
+
+
+@pytest.mark.parametrize("V", [1000, 50257])
+def test_sampling_matches_the_plain_sampler(V):
+    from vlrf_b200.csrc import ops
+    from vlrf_b200.sampling.rng import as_signed64, request_key, uniform01
+    n = 48
+    lg = randn(n, V, seed=41) * 2.0
+    rs = np.random.RandomState(5)
+    temp = rs.choice([0.0, 0.5, 0.8, 1.0, 1.7], n).astype(np.float32)
+    top_k = rs.choice([0, 1, 5, 50, V, V + 10], n).astype(np.int32)
+    top_p = rs.choice([1.0, 0.9, 0.5, 0.05, 0.999], n).astype(np.float32)
+    keys = [request_key(42, i) for i in range(n)]
+    d = lambda a, dt: torch.tensor(a, dtype=dt, device=DEV)  # noqa: E731
+    ctr = torch.zeros(n, dtype=torch.int32, device=DEV)
+    key_t = d([as_signed64(k) for k in keys], torch.int64)
+    out = torch.zeros(n, dtype=torch.int32, device=DEV)
+    lg_d = lg.to(DEV)
+    for draw in range(3):
+        ops.sample(lg_d, n, out, temperature=d(temp, torch.float32), top_k=d(top_k, torch.int32),
+                   top_p=d(top_p, torch.float32), rng_key=key_t, rng_ctr=ctr)
+        got = out.tolist()
+        mismatches = []
+        for i in range(n):
+            u = uniform01(keys[i], draw)
+            want = plain.sample_token(lg[i].numpy(), float(temp[i]), int(top_k[i]), float(top_p[i]), u)
+            if got[i] != want:
+                # float32 vs float64 may differ where u falls within rounding of a boundary: accept a neighbour
+                # of the boundary only if both candidates are kept tokens with cumulative masses that close
+                p = np.exp((lg[i].numpy().astype(np.float64) - lg[i].numpy().max()) / max(float(temp[i]), 1e-9))
+                mismatches.append((i, got[i], want, p[got[i]] / p.sum(), p[want] / p.sum()))
+        assert len(mismatches) <= 1, mismatches
+    assert (ctr.cpu().numpy() == np.where(temp > 0, 3, 0)).all()   # greedy rows draw nothing
+
+
+def test_sampling_distribution_and_filters():
+    """Many draws of one row: frequencies follow the renormalised kept probabilities."""
+    from vlrf_b200.csrc import ops
+    V, n = 37, 4096
+    base = torch.log(torch.tensor([0.3, 0.2, 0.2, 0.1, 0.1] + [0.1 / 32] * 32))
+    lg = base.repeat(n, 1).contiguous().to(DEV)
+    d = lambda a, dt: torch.tensor(a, dtype=dt, device=DEV)  # noqa: E731
+    keys = torch.arange(1, n + 1, dtype=torch.int64, device=DEV) * 7919
+    out = torch.zeros(n, dtype=torch.int32, device=DEV)
+
+    def draw(k, p):
+        ctr = torch.zeros(n, dtype=torch.int32, device=DEV)
+        ops.sample(lg, n, out, temperature=d([1.0] * n, torch.float32), top_k=d([k] * n, torch.int32),
+                   top_p=d([p] * n, torch.float32), rng_key=keys, rng_ctr=ctr)
+        return np.bincount(out.cpu().numpy(), minlength=V) / n
+
+    f = draw(0, 1.0)
+    assert abs(f[0] - 0.3) < 0.03 and abs(f[1] - 0.2) < 0.03 and abs(f[5:].sum() - 0.1) < 0.02
+    f = draw(3, 1.0)          # ties at the cut (0.2, 0.2) both inside; 0.1s outside
+    assert f[3:].sum() == 0 and abs(f[0] - 0.3 / 0.7) < 0.03
+    f = draw(2, 1.0)          # the cut falls between the two tokens of equal probability: the lower index stays
+    assert f[2:].sum() == 0 and f[1] > 0.3
+    f = draw(0, 0.75)         # cumulative .3 .5 .7 .8>.75 → keep three
+    assert f[3:].sum() == 0 and abs(f[2] - 0.2 / 0.7) < 0.03
+    f = draw(0, 0.1)          # the most probable always stays
+    assert f[0] == 1.0
+
+
+def test_penalties_and_ngram_block():
+    from vlrf_b200.csrc import ops
+    V, n = 300, 6
+    lg = randn(n, V, seed=42)
+    gen = torch.zeros(n, 12, dtype=torch.int32)
+    lens = torch.tensor([0, 5, 5, 12, 7, 3], dtype=torch.int32)
+    rs = np.random.RandomState(9)
+    hist = [list(rs.randint(0, 6, size=int(m))) for m in lens]     # few distinct tokens: repeats are certain
+    for i, h in enumerate(hist):
+        gen[i, :len(h)] = torch.tensor(h, dtype=torch.int32)
+    rep = [1.0, 1.3, 1.0, 2.0, 1.0, 0.8]
+    freq = [0.0, 0.0, 0.7, 0.2, 0.0, 0.1]
+    pres = [0.0, 0.5, 0.0, 0.1, 0.0, 0.0]
+    ngram = [0, 0, 2, 3, 2, 1]
+    d = lambda a, dt: torch.tensor(a, dtype=dt, device=DEV)  # noqa: E731
+    got = lg.clone().to(DEV)
+    ops.apply_penalties(got, n, gen.to(DEV), lens.to(DEV), repetition=d(rep, torch.float32),
+                        frequency=d(freq, torch.float32), presence=d(pres, torch.float32),
+                        no_repeat_ngram=d(ngram, torch.int32))
+    got = got.cpu().numpy()
+    for i in range(n):
+        counts = {}
+        for t in hist[i]:
+            counts[int(t)] = counts.get(int(t), 0) + 1
+        want = plain.apply_penalties(lg[i].numpy(), counts, rep[i], freq[i], pres[i])
+        want = plain.block_repeated_ngrams(want, [int(t) for t in hist[i]], ngram[i])
+        fin = np.isfinite(want)
+        assert (np.isfinite(got[i]) == fin).all()
+        assert np.allclose(got[i][fin], want[fin], rtol=1e-6, atol=1e-6)
+    assert np.array_equal(got[0], lg[0].numpy())      # nothing generated yet: untouched

@@ -147,7 +147,7 @@ class Engine:
             seq_start=views[4], seq_pos0=views[5], max_new=max(p["lens"]),
             max_context=max(a + b for a, b in zip(p["pos0"], p["lens"])), logit_rows=views[6],
             n_logit_rows=n_want, act_dtype=self.model.act_dtype, dev_err=self.dev_err, ws=self.ws,
-            host_seq_lens=p["lens"], host_seq_pos0=p["pos0"])
+            host_seq_slots=[e.slot for e in entries], host_seq_lens=p["lens"], host_seq_pos0=p["pos0"])
         logits = self.model.forward(ctx, self.cache)
         for e in entries:
             self.cache.advance(e.slot, len(e.tokens))

@@ -57,5 +57,6 @@ class StepContext:
     dev_err: torch.Tensor            # int32 [1]: bits that kernels set instead of faulting
     ws: Workspace
     #: host copies for parts that plan on the host (e.g. tiling a prefill)
+    host_seq_slots: list = dataclasses.field(default_factory=list)
     host_seq_lens: list = dataclasses.field(default_factory=list)
     host_seq_pos0: list = dataclasses.field(default_factory=list)
