@@ -71,13 +71,17 @@ def test_unequal_batches_one_after_another(model_dirs, requests_and_truth, name,
     prompt_lens = [max(1, len(r) - decode) for r in reqs]
     # a cache just large enough for one batch: the second batch must reuse slots and blocks of the first
     batch = 3 if name == "tiny_a" else 4
-    need = max(sum((len(r) + 63) // 64 * 64 for r in reqs[b:b + batch]) for b in range(0, len(reqs), batch))
+    order = list(reversed(range(len(reqs))))
+
+    def need_of(rs):
+        return max(sum((len(r) + 63) // 64 * 64 for r in rs[b:b + batch]) for b in range(0, len(rs), batch))
+
+    need = max(need_of(reqs), need_of([reqs[i] for i in order]))
     eng = make_engine(model_dirs, name, dtype, need)
     got = drive_batches(eng, reqs, batch, prompt_lens)
     compare(got, truth, tol, "unequal batches")
     assert eng.cache.slots.n_held == 0
     # the same again in another order: every slot and block has been used before
-    order = list(reversed(range(len(reqs))))
     got2 = drive_batches(eng, [reqs[i] for i in order], batch, [prompt_lens[i] for i in order])
     compare(got2, [truth[i] for i in order], tol, "unequal batches, reused cache")
 
