@@ -74,8 +74,19 @@ def register_signatures(extra: dict) -> None:
     _SIGNATURES.update(extra)
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernel entry points have been called so far (each launches one kernel unless it says
+    otherwise); replays of a captured graph are counted by whoever replays it."""
+    return _launches
+
+
 def call(name: str, *args) -> None:
+    global _launches
     lib = library()
+    _launches += 1
     status = getattr(lib, name)(*args)
     if status != 0:
         raise KernelError(f"{name}: {lib.vlrf_last_error().decode('utf-8', 'replace')} (status {status})")

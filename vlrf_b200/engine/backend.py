@@ -1,10 +1,14 @@
-"""The generation loop's backend on the device: `Engine.step` plus the sampling kernels."""
+"""The generation loop's backend on the device: `Engine.step` for the prompts, a `DecodeSession` for
+the single-token steps, and the sampling kernels."""
 from __future__ import annotations
 
 import dataclasses
 
+import torch
+
 from ..sampling.rng import request_key
 from ..sampling.sampler import RowSampler
+from .decode import DecodeSession
 from .step import Engine, StepEntry
 
 
@@ -12,13 +16,25 @@ from .step import Engine, StepEntry
 class _Batch:
     slots: list
     sampler: RowSampler
+    budget: list                      # most tokens each sequence may come to hold
+    session: DecodeSession | None = None
+    staging: torch.Tensor | None = None   # pinned host int32: the tokens fed at a decode step
+
+
+def _bucket(n: int) -> int:
+    b = 1
+    while b < n:
+        b *= 2
+    return b
 
 
 class DeviceBackend:
-    def __init__(self, engine: Engine):
+    def __init__(self, engine: Engine, *, use_graph: bool = True):
         self.engine = engine
+        self.use_graph = use_graph
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        self.decode_steps = 0
 
     def limits(self):
         c = self.engine.cache
@@ -29,9 +45,22 @@ class DeviceBackend:
         keys = [request_key(r.params.seed, r.index) for r in requests]
         history = max((r.params.max_new_tokens for r in requests), default=1)
         sampler = RowSampler([r.params for r in requests], keys, self.engine.device, history)
-        return _Batch(slots, sampler)
+        most = [min(len(r.prompt) + max(r.params.max_new_tokens - 1, 0), self.engine.model.max_seq_len)
+                for r in requests]
+        return _Batch(slots, sampler, most)
 
     def run(self, batch: _Batch, rows: list, tokens: list) -> list:
+        if batch.session is None and all(len(t) == 1 for t in tokens) and rows == list(range(len(batch.slots))) \
+                and all(self.engine.length(s) > 0 for s in batch.slots):
+            # every sequence of the batch goes on by one token: from here on the steps are replayed
+            batch.session = DecodeSession(self.engine, batch.slots, use_graph=self.use_graph,
+                                          pad_to=_bucket(len(batch.slots)))
+            for s, most in zip(batch.slots, batch.budget):
+                self.engine.cache.reserve(s, most)
+            self.engine.cache.sync_tables()
+            batch.staging = torch.zeros(len(batch.slots), dtype=torch.int32, pin_memory=True)
+        if batch.session is not None:
+            return self._run_decode(batch, rows, tokens)
         entries = [StepEntry(batch.slots[r], toks, [len(toks) - 1]) for r, toks in zip(rows, tokens)]
         logits = self.engine.step(entries)
         out = batch.sampler.sample(logits, rows)
@@ -41,5 +70,22 @@ class DeviceBackend:
         self.engine.check_device_errors()
         return host
 
+    def _run_decode(self, batch: _Batch, rows: list, tokens: list) -> list:
+        sess = batch.session
+        n = len(batch.slots)
+        st = batch.staging
+        for r, toks in zip(rows, tokens):
+            st[r] = toks[0]
+        sess.tokens[:n].copy_(st, non_blocking=True)          # this step's inputs, host → device
+        logits = sess.step()
+        out = batch.sampler.sample(logits[:n], list(range(n)))
+        host = out.tolist()                                    # this step's result, device → host; synchronises
+        self.h2d_bytes += 4 * n
+        self.d2h_bytes += 4 * n
+        self.decode_steps += 1
+        return [host[r] for r in rows]
+
     def close_row(self, batch: _Batch, row: int) -> None:
+        if batch.session is not None:
+            batch.session.end_row(row)
         self.engine.end_sequence(batch.slots[row])

@@ -1,0 +1,109 @@
+"""Decoding a fixed set of sequences one token per step, with the tokens staying on the device.
+
+A `DecodeSession` is the step function specialised to "every sequence goes on by one token": the
+integer tables of the step (token, slot, position per row) are static device tensors, so the step's
+launches can be captured once in a CUDA graph and replayed, and the sampled tokens of one step are
+written straight into the token table of the next.  It runs the same `DecoderModel.forward` on the same
+cache as `Engine.step`; rows of ended sequences become padding (slot −1), which every part skips.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..parts.context import StepContext, Workspace
+from .step import Engine
+
+
+class DecodeSession:
+    def __init__(self, engine: Engine, slots: list, *, use_graph: bool = True, pad_to: int | None = None):
+        self.engine, self.model = engine, engine.model
+        self.slots = list(slots)
+        self.n = len(slots)
+        self.rows = pad_to if pad_to is not None else self.n
+        if self.rows < self.n:
+            raise ValueError("pad_to is smaller than the number of sequences")
+        dev = engine.device
+        self.live = [True] * self.n
+        self.tokens = torch.zeros(self.rows, dtype=torch.int32, device=dev)
+        self.tok_slot = torch.full((self.rows,), -1, dtype=torch.int32, device=dev)
+        self.tok_pos = torch.zeros(self.rows, dtype=torch.int32, device=dev)
+        self.seq_start = torch.arange(self.rows + 1, dtype=torch.int32, device=dev)
+        self.logit_rows = torch.arange(self.rows, dtype=torch.int32, device=dev)
+        self.one = torch.ones(self.rows, dtype=torch.int32, device=dev)
+        self.ws = Workspace(dev)
+        self.use_graph = use_graph
+        self.graph = None
+        self.logits = None
+        self.kernels_per_step = 0
+        self._sync_tables()
+
+    def _sync_tables(self) -> None:
+        c = self.engine.cache
+        slot = [s if live else -1 for s, live in zip(self.slots, self.live)] + [-1] * (self.rows - self.n)
+        pos = [c.lengths[s] if live else 0 for s, live in zip(self.slots, self.live)] + [0] * (self.rows - self.n)
+        self.tok_slot.copy_(torch.tensor(slot, dtype=torch.int32))
+        self.tok_pos.copy_(torch.tensor(pos, dtype=torch.int32))
+
+    def set_tokens(self, tokens) -> None:
+        """The tokens to feed at the next step: a device int32 tensor [n] or a host list."""
+        if isinstance(tokens, torch.Tensor):
+            self.tokens[:self.n].copy_(tokens[:self.n])
+        else:
+            self.tokens[:self.n].copy_(torch.tensor(list(tokens), dtype=torch.int32))
+
+    def end_row(self, row: int) -> None:
+        """The sequence of this row has ended; its row becomes padding.  (The slot is the caller's to free.)"""
+        self.live[row] = False
+        self.tok_slot[row] = -1
+
+    def reserve_ahead(self, n_steps: int) -> None:
+        """Make sure every live sequence has blocks for its next n_steps tokens, so that the replayed
+        steps need no change of the block tables."""
+        c = self.engine.cache
+        for s, live in zip(self.slots, self.live):
+            if live:
+                c.reserve(s, min(c.lengths[s] + n_steps, self.model.max_seq_len))
+        c.sync_tables()
+
+    def _context(self) -> StepContext:
+        c = self.engine.cache
+        most = max([c.lengths[s] + 1 for s, live in zip(self.slots, self.live) if live] or [1])
+        return StepContext(
+            n_tokens=self.rows, tokens=self.tokens, tok_slot=self.tok_slot, tok_pos=self.tok_pos, n_seqs=self.rows,
+            seq_slot=self.tok_slot, seq_start=self.seq_start, seq_pos0=self.tok_pos, max_new=1,
+            max_context=self.model.max_seq_len if self.use_graph else most, logit_rows=self.logit_rows,
+            n_logit_rows=self.rows, act_dtype=self.model.act_dtype, dev_err=self.engine.dev_err, ws=self.ws,
+            host_seq_slots=list(self.slots), host_seq_lens=[1] * self.rows, host_seq_pos0=[])
+
+    def step(self) -> torch.Tensor:
+        """One decode step of all rows from `self.tokens`; returns float32 logits [rows, vocab] (static
+        storage).  Afterwards every live row's position has advanced by one, on the device and in the
+        cache's books."""
+        from ..csrc import launch_count
+        c = self.engine.cache
+        for s, live in zip(self.slots, self.live):
+            if live and c.lengths[s] + 1 > self.model.max_seq_len:
+                raise ValueError(f"slot {s} is at the model's last position")
+        if self.use_graph and self.graph is None:
+            # a warm-up run sizes the workspace; the capture then sees stable addresses
+            before = launch_count()
+            self.logits = self.model.forward(self._context(), c)
+            self.kernels_per_step = launch_count() - before
+            torch.cuda.synchronize()
+            self.ws.frozen = True
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.logits = self.model.forward(self._context(), c)
+            self.graph = g
+        if self.use_graph:
+            self.graph.replay()
+        else:
+            before = launch_count()
+            self.logits = self.model.forward(self._context(), c)
+            self.kernels_per_step = launch_count() - before
+        self.tok_pos.add_(self.one * (self.tok_slot >= 0))
+        for s, live in zip(self.slots, self.live):
+            if live:
+                c.advance(s, 1)
+        self.engine.steps_run += 1
+        return self.logits

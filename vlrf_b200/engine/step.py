@@ -87,9 +87,10 @@ class Engine:
             if self.cache.lengths[e.slot] + len(e.tokens) > self.model.max_seq_len:
                 raise StepError(f"slot {e.slot}: {self.cache.lengths[e.slot]} + {len(e.tokens)} tokens exceed the "
                                 f"{self.model.max_seq_len} positions of the model")
-            for t in e.tokens:
-                if not (0 <= int(t) < vocab):
-                    raise StepError(f"slot {e.slot}: token id {t} lies outside the vocabulary of {vocab}")
+            arr = np.asarray(e.tokens, dtype=np.int64)
+            if arr.min() < 0 or arr.max() >= vocab:
+                bad = int(arr[(arr < 0) | (arr >= vocab)][0])
+                raise StepError(f"slot {e.slot}: token id {bad} lies outside the vocabulary of {vocab}")
             for w in e.want:
                 if not (0 <= int(w) < len(e.tokens)):
                     raise StepError(f"slot {e.slot}: wanted place {w} is not among its {len(e.tokens)} tokens")
