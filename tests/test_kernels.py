@@ -72,7 +72,9 @@ def test_layernorm_small_variance_uses_eps():
 
 
 # ------------------------------------------------------------------------------------------------
-GEMM_SHAPES = [(1, 53, 19), (37, 53, 19), (64, 64, 16), (130, 200, 72), (3, 1000, 96), (257, 96, 320)]
+GEMM_SHAPES = [(1, 53, 19), (37, 53, 19), (64, 64, 16), (130, 200, 72), (3, 1000, 96), (257, 96, 320),
+               # few rows and K a multiple of 32: the weight-streaming kernel of the decode step
+               (8, 2304, 768), (64, 200, 96), (17, 50, 64), (33, 1000, 320), (1, 768, 3072), (9, 17, 32)]
 
 
 @pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
@@ -101,6 +103,52 @@ def test_linear(M, N, K, in_dtype, out_dtype, tol, act):
         assert rel_err(nob.cpu(), x.double() @ w.double().T) < tol
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 96, 64), (8, 2304, 768), (13, 200, 96), (40, 320, 96), (32, 130, 1600), (64, 130, 768)])
+@pytest.mark.parametrize("out_dtype,act", [(torch.bfloat16, None), (torch.bfloat16, "gelu_tanh"), (torch.float32, "gelu_erf")])
+def test_linear_with_fused_layernorm(M, N, K, out_dtype, act):
+    from vlrf_b200.csrc import ops
+    assert ops.can_fuse_layernorm(M, K, torch.bfloat16)
+    x = randn(M, K, seed=16) * 2 + 0.5
+    gamma, beta = randn(K, seed=17) * 0.3 + 1, randn(K, seed=18) * 0.2
+    w, b = randn(N, K, seed=19, dtype=torch.bfloat16, scale=0.2), randn(N, seed=20)
+    eps = 1e-5
+    h = plain.layer_norm(x.double(), gamma.double(), beta.double(), eps)
+    h = h.to(torch.bfloat16).double()       # the kernel rounds the normed rows to bfloat16 for the tensor cores
+    want = h @ w.double().T + b.double()
+    if act:
+        want = (plain.gelu_tanh if act == "gelu_tanh" else plain.gelu_erf)(want)
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops.linear_layernorm(x.to(DEV), gamma.to(DEV), beta.to(DEV), eps, w.to(DEV), b.to(DEV), out, act=act)
+    # a normed value that lies within rounding of a bfloat16 tie may round the other way than float64's
+    assert rel_err(out.float().cpu(), want) < (6e-3 if out_dtype == torch.bfloat16 else 3e-3)
+
+
+def test_fused_projection_writes_keys_and_values_into_the_cache():
+    from vlrf_b200.csrc import ops
+    H, Hkv, dh, K, M = 4, 2, 16, 96, 5
+    N = (H + 2 * Hkv) * dh
+    x = randn(M, K, seed=21)
+    gamma, beta = torch.ones(K), torch.zeros(K)
+    w, b = randn(N, K, seed=22, dtype=torch.bfloat16, scale=0.2), randn(N, seed=23)
+    kc = torch.full((6, Hkv, 64, dh), float("nan"), dtype=torch.bfloat16, device=DEV)
+    vc = torch.full_like(kc, float("nan"))
+    table = torch.tensor([[3, 1], [5, -1], [2, 0]], dtype=torch.int32)
+    slot = torch.tensor([0, 2, -1, 1, 2], dtype=torch.int32)      # row 2 is padding; rows 1 and 4 share slot 2
+    pos = torch.tensor([70, 5, 0, 63, 64], dtype=torch.int32)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    ops.linear_layernorm(x.to(DEV), gamma.to(DEV), beta.to(DEV), 1e-5, w.to(DEV), b.to(DEV), out,
+                         kv_scatter=(kc, vc, table.to(DEV), slot.to(DEV), pos.to(DEV), H * dh, (H + Hkv) * dh, Hkv, dh))
+    o = out.cpu()
+    for m in range(M):
+        if slot[m] < 0:
+            continue
+        blk = int(table[slot[m], pos[m] // 64])
+        assert torch.equal(kc[blk, :, pos[m] % 64].cpu().reshape(-1), o[m, H * dh:(H + Hkv) * dh])
+        assert torch.equal(vc[blk, :, pos[m] % 64].cpu().reshape(-1), o[m, (H + Hkv) * dh:])
+    written = (~torch.isnan(kc.float())).sum().item()
+    assert written == 4 * Hkv * dh                                   # nothing else was touched
+
+
 def test_linear_rows_do_not_depend_on_the_batch():
     from vlrf_b200.csrc import ops
     x, w, b = randn(70, 96, seed=13), randn(200, 96, seed=14), randn(200, seed=15)
@@ -127,7 +175,7 @@ def paged(k, v, n_blocks, order_seed, dtype):
     return kp, vp, perm.to(torch.int32)
 
 
-def run_attention(q, k, v, *, dtype, scale, window=0, past=None, impl="generic"):
+def run_attention(q, k, v, *, dtype, scale, window=0, past=None, impl="generic", n_split=1):
     """q [H, T, dh] are the LAST T positions of a context of C = k.shape[1] tokens."""
     from vlrf_b200.csrc import ops
     H, T, dh = q.shape
@@ -141,8 +189,17 @@ def run_attention(q, k, v, *, dtype, scale, window=0, past=None, impl="generic")
     e = err_word()
     slot = torch.full((T,), 1, dtype=torch.int32)
     pos = torch.arange(C - T, C, dtype=torch.int32)
-    ops.attention_generic(qkv.to(DEV), 16, kp.to(DEV), vp.to(DEV), table.to(DEV), slot.to(DEV), pos.to(DEV), out, T,
-                          H, Hkv, dh, scale, window, e)
+    if impl == "decode":
+        partials = torch.full((T * H * n_split * (dh + 2),), float("nan"), device=DEV)
+        counters = torch.zeros(T * H, dtype=torch.int32, device=DEV)
+        for _ in range(2):       # twice: the counters must be back at zero after a call
+            out.fill_(float("nan"))
+            ops.attention_decode(qkv.to(DEV), 16, kp.to(DEV), vp.to(DEV), table.to(DEV), slot.to(DEV), pos.to(DEV), out,
+                                 T, H, Hkv, dh, scale, window, n_split, partials, counters, e)
+        assert int(counters.abs().sum()) == 0
+    else:
+        ops.attention_generic(qkv.to(DEV), 16, kp.to(DEV), vp.to(DEV), table.to(DEV), slot.to(DEV), pos.to(DEV), out,
+                              T, H, Hkv, dh, scale, window, e)
     assert int(e.item()) == 0
     return out.float().cpu().reshape(T, H, dh).permute(1, 0, 2)
 
@@ -172,6 +229,34 @@ def test_attention_generic(H, Hkv, dh, T, C, dtype, tol):
     scale = 0.7 / math.sqrt(dh)
     got = run_attention(q, k, v, dtype=dtype, scale=scale)
     assert rel_err(got, plain_attention(q, k, v, scale)) < tol
+
+
+@pytest.mark.parametrize("H,Hkv,dh,T,C", ATT_CASES + [(12, 12, 64, 8, 1024 - 400), (25, 25, 64, 2, 33)])
+@pytest.mark.parametrize("n_split", [1, 2, 5, 16])
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 1.5e-2)])
+def test_attention_decode_split_context(H, Hkv, dh, T, C, n_split, dtype, tol):
+    """The decode kernel takes any rows (here the last T positions of one context), any split count."""
+    if T > 40:
+        T = 40
+    q, k, v = randn(H, T, dh, seed=30), randn(Hkv, C, dh, seed=31), randn(Hkv, C, dh, seed=32)
+    if dtype == torch.bfloat16:
+        q, k, v = (t.to(dtype).float() for t in (q, k, v))
+    scale = 0.7 / math.sqrt(dh)
+    got = run_attention(q, k, v, dtype=dtype, scale=scale, impl="decode", n_split=n_split)
+    assert rel_err(got, plain_attention(q, k, v, scale)) < tol
+
+
+@pytest.mark.parametrize("far", [0, 63, 64, 257, 511])
+@pytest.mark.parametrize("n_split", [1, 4])
+def test_attention_decode_finds_one_far_key_and_respects_a_window(far, n_split):
+    H, dh, C = 2, 64, 512
+    q, k, v = randn(H, 1, dh, seed=36), randn(H, C, dh, seed=37) * 0.1, randn(H, C, dh, seed=38)
+    k[:, far] = q[:, 0] * 4.0
+    got = run_attention(q, k, v, dtype=torch.float32, scale=1.0, impl="decode", n_split=n_split)
+    assert rel_err(got[:, 0], v[:, far]) < 1e-4
+    for window in (1, 33, 200, 512 - far, 511 - far):
+        got = run_attention(q, k, v, dtype=torch.float32, scale=1.0, window=window, impl="decode", n_split=n_split)
+        assert rel_err(got, plain_attention(q, k, v, 1.0, window)) < 2e-5
 
 
 @pytest.mark.parametrize("window", [1, 31, 32, 33, 64, 100])

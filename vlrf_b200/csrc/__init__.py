@@ -36,6 +36,14 @@ _SIGNATURES = {
     "vlrf_attn_generic": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
                           _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
                           _c_void_p, _c_void_p],
+    "vlrf_gemm_skinny_ln_fits": [_c_int, _c_int],
+    "vlrf_gemm_skinny": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
+                         _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_float,
+                         _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
+                         _c_int, _c_int, _c_void_p],
+    "vlrf_attn_decode": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
+                         _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int,
+                         _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "vlrf_sample": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                     _c_void_p, _c_void_p],
     "vlrf_apply_penalties": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,

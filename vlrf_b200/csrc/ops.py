@@ -94,9 +94,97 @@ def linear(x, w, bias, out, *, act=None, residual=None, rows: int | None = None)
     _linear_dispatch(x, w, bias, out, ACT[act], residual, M, N, K)
 
 
+_SM_COUNT = None
+SKINNY_MAX_ROWS = 64
+
+
+def sm_count() -> int:
+    global _SM_COUNT
+    if _SM_COUNT is None:
+        import ctypes
+        from . import library
+        vals = [ctypes.c_int(0) for _ in range(4)]
+        if library().vlrf_device_info(*[ctypes.byref(v) for v in vals]) != 0:
+            raise KernelError("cannot query the device")
+        _SM_COUNT = vals[0].value
+    return _SM_COUNT
+
+
 def _linear_dispatch(x, w, bias, out, act, residual, M, N, K) -> None:
+    if x.dtype == torch.bfloat16 and M <= SKINNY_MAX_ROWS and K % 32 == 0:
+        # few rows: the product is bound by streaming w once
+        call("vlrf_gemm_skinny", _ptr(x), 0, _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), dtype_code(out.dtype),
+             M, N, K, K, N, act, 0, 0, 0.0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, sm_count(), _stream())
+        return
     call("vlrf_gemm_simt", _ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), M, N, K, K, N,
          dtype_code(x.dtype), dtype_code(out.dtype), act, _stream())
+
+
+def can_fuse_layernorm(n_rows: int, width: int, w_dtype: torch.dtype) -> bool:
+    """Whether `linear_layernorm` takes this many rows of this width."""
+    if w_dtype != torch.bfloat16 or n_rows > SKINNY_MAX_ROWS or n_rows < 1 or width % 32 != 0:
+        return False
+    from . import library
+    return bool(library().vlrf_gemm_skinny_ln_fits(n_rows, width))
+
+
+def linear_layernorm(x, gamma, beta, eps: float, w, bias, out, *, act=None, rows: int | None = None,
+                     kv_scatter=None) -> None:
+    """out = act(LayerNorm(x) · wᵀ + bias) for few rows, the norm fused into the product's prologue.
+    x float32 [M,K]; w bfloat16 [N,K]; out bfloat16 or float32.  `kv_scatter` = (k_cache, v_cache,
+    block_table, tok_slot, tok_pos, k_off, v_off, n_kv_heads, head_dim) also writes those columns of the
+    result into one layer's paged cache."""
+    _dev(x, "x", torch.float32); _dev(w, "w", torch.bfloat16); _dev(out, "out")
+    _dev(gamma, "gamma", torch.float32); _dev(beta, "beta", torch.float32)
+    M = x.shape[0] if rows is None else rows
+    K, N = x.shape[1], w.shape[0]
+    if w.shape[1] != K or out.shape[1] != N or out.shape[0] < M or gamma.shape[0] != K or beta.shape[0] != K:
+        raise KernelError("linear_layernorm: sizes do not match")
+    if bias is not None:
+        _dev(bias, "bias", torch.float32)
+    kv = [0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0]
+    if kv_scatter is not None:
+        kc, vc, table, tok_slot, tok_pos, k_off, v_off, hkv, dh = kv_scatter
+        _dev(kc, "k_cache", torch.bfloat16); _dev(vc, "v_cache", torch.bfloat16)
+        _dev(table, "block_table", torch.int32); _dev(tok_slot, "tok_slot", torch.int32)
+        _dev(tok_pos, "tok_pos", torch.int32)
+        if kc.shape[1] != hkv or kc.shape[3] != dh or max(k_off, v_off) + hkv * dh > N:
+            raise KernelError("linear_layernorm: cache scatter does not match")
+        kv = [_ptr(kc), _ptr(vc), _ptr(table), table.shape[1], _ptr(tok_slot), _ptr(tok_pos), k_off, v_off, hkv, dh,
+              kc.shape[2]]
+    call("vlrf_gemm_skinny", _ptr(x), 1, _ptr(w), _ptr(bias), 0, _ptr(out), dtype_code(out.dtype), M, N, K, K, N,
+         ACT[act], _ptr(gamma), _ptr(beta), float(eps), *kv, sm_count(), _stream())
+
+
+def decode_splits(n_rows: int, n_heads: int, max_context: int) -> int:
+    """Into how many parts a decode step cuts each context so that every SM has work."""
+    want = -(-2 * sm_count() // max(1, n_rows * n_heads))
+    return max(1, min(16, want, -(-max_context // 128)))
+
+
+def attention_decode(qkv, q_off: int, k_cache, v_cache, block_table, tok_slot, tok_pos, out, n_rows: int,
+                     n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int, n_split: int,
+                     partials, counters, dev_err) -> None:
+    """One query per row attends the keys 0…position of its slot; the context is cut into n_split parts.
+    partials: float32 scratch of n_rows·n_heads·n_split·(head_dim+2); counters: int32 [n_rows·n_heads],
+    zero between calls."""
+    _dev(qkv, "qkv"); _dev(k_cache, "k_cache", qkv.dtype); _dev(v_cache, "v_cache", qkv.dtype)
+    _dev(out, "out", qkv.dtype); _dev(block_table, "block_table", torch.int32)
+    _dev(tok_slot, "tok_slot", torch.int32); _dev(tok_pos, "tok_pos", torch.int32)
+    _dev(dev_err, "dev_err", torch.int32)
+    nb, hkv, bt, dh = k_cache.shape
+    if hkv != n_kv_heads or dh != head_dim or v_cache.shape != k_cache.shape:
+        raise KernelError("attention_decode: cache shape does not match the heads")
+    if out.shape[1] != n_heads * head_dim or out.shape[0] < n_rows or qkv.shape[0] < n_rows:
+        raise KernelError("attention_decode: output does not match")
+    if n_split > 1:
+        _dev(partials, "partials", torch.float32); _dev(counters, "counters", torch.int32)
+        if partials.numel() < n_rows * n_heads * n_split * (head_dim + 2) or counters.numel() < n_rows * n_heads:
+            raise KernelError("attention_decode: scratch is too small")
+    call("vlrf_attn_decode", _ptr(qkv), dtype_code(qkv.dtype), qkv.shape[1], q_off, _ptr(k_cache), _ptr(v_cache),
+         _ptr(block_table), block_table.shape[1], _ptr(tok_slot), _ptr(tok_pos), _ptr(out), out.shape[1], n_rows,
+         n_heads, n_kv_heads, head_dim, bt, float(scale), int(window), int(n_split), _ptr(partials), _ptr(counters),
+         _ptr(dev_err), _stream())
 
 
 def kv_append(qkv, k_off: int, v_off: int, k_cache, v_cache, block_table, tok_slot, tok_pos, n_tokens: int,

@@ -19,8 +19,13 @@ class PreNormBlock:
         return self.mixer.cache_need()
 
     def forward(self, x: torch.Tensor, ctx: StepContext, view, writes_cache: bool = True) -> None:
-        h = ctx.ws.get("block_normed", ctx.n_tokens, x.shape[1], ctx.act_dtype)
-        self.norm1(x, h)
-        self.mixer.forward(h, x, ctx, view, writes_cache)
-        self.norm2(x, h)
-        self.feed_forward.forward(h, x, ctx)
+        if getattr(self.mixer, "fuses_norm", False):
+            self.mixer.forward(None, x, ctx, view, writes_cache, norm=self.norm1)
+        else:
+            h = ctx.ws.get("block_normed", ctx.n_tokens, x.shape[1], ctx.act_dtype)
+            self.mixer.forward(self.norm1(x, h), x, ctx, view, writes_cache)
+        if getattr(self.feed_forward, "fuses_norm", False):
+            self.feed_forward.forward(None, x, ctx, norm=self.norm2)
+        else:
+            h = ctx.ws.get("block_normed", ctx.n_tokens, x.shape[1], ctx.act_dtype)
+            self.feed_forward.forward(self.norm2(x, h), x, ctx)

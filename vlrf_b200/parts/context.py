@@ -35,6 +35,17 @@ class Workspace:
             self._bufs[name] = buf
         return buf[:n].view(rows, cols)
 
+    def get_zeroed(self, name: str, n: int, dtype: torch.dtype) -> torch.Tensor:
+        """A flat buffer that is zero when first handed out (and again after it had to grow); whoever uses
+        it leaves it zero."""
+        buf = self._bufs.get(name)
+        if buf is None or buf.dtype != dtype or buf.numel() < n:
+            if self.frozen:
+                raise RuntimeError(f"workspace '{name}' would have to grow while a captured step uses it")
+            buf = torch.zeros(max(n, 1), dtype=dtype, device=self.device)
+            self._bufs[name] = buf
+        return buf[:n]
+
     def bytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._bufs.values())
 

@@ -30,7 +30,16 @@ class DenseMLP:
         self.activation = activation
         self.inner = w_in.shape[0]
 
-    def forward(self, h: torch.Tensor, x: torch.Tensor, ctx: StepContext) -> None:
-        u = ctx.ws.get("ffn_inner", ctx.n_tokens, self.inner, ctx.act_dtype)
-        ops.linear(h, self.w_in, self.b_in, u, act=self.activation)
+    #: the block may hand over its norm instead of normed rows: forward(None, x, ctx, norm=…)
+    fuses_norm = True
+
+    def forward(self, h, x: torch.Tensor, ctx: StepContext, norm=None) -> None:
+        T = ctx.n_tokens
+        u = ctx.ws.get("ffn_inner", T, self.inner, ctx.act_dtype)
+        if h is None and ops.can_fuse_layernorm(T, x.shape[1], self.w_in.dtype) and hasattr(norm, "eps"):
+            ops.linear_layernorm(x, norm.weight, norm.bias, norm.eps, self.w_in, self.b_in, u, act=self.activation)
+        else:
+            if h is None:
+                h = norm(x, ctx.ws.get("block_normed", T, x.shape[1], ctx.act_dtype))
+            ops.linear(h, self.w_in, self.b_in, u, act=self.activation)
         ops.linear(u, self.w_out, self.b_out, x, residual=x)

@@ -4,6 +4,8 @@ Interface of a mixer (what `Block` and the step rely on):
 
     cache_need() -> KVNeed | StateNeed | None     what it keeps per sequence
     forward(h, x, ctx, view, writes_cache=True)   x += mix(h), in place.
+        (a mixer that sets `fuses_norm = True` also accepts h=None with `norm=` the block's norm, and
+        applies the norm itself, fused where its kernels allow)
         h     [n_tokens, width]  normed input in the activation dtype
         x     [n_tokens, width]  float32 residual stream
         ctx   StepContext        tokens' slots and positions, scratch, error word
@@ -57,11 +59,26 @@ class CausalSelfAttention:
             return KVNeed(self.n_kv_heads, self.head_dim, "window", self.window)
         return KVNeed(self.n_kv_heads, self.head_dim, "full")
 
-    def forward(self, h: torch.Tensor, x: torch.Tensor, ctx: StepContext, view, writes_cache: bool = True) -> None:
+    #: the block may hand over its norm instead of normed rows: forward(None, x, …, norm=…)
+    fuses_norm = True
+
+    def forward(self, h, x: torch.Tensor, ctx: StepContext, view, writes_cache: bool = True, norm=None) -> None:
         T = ctx.n_tokens
         qkv = ctx.ws.get("attn_qkv", T, self.qkv_width, ctx.act_dtype)
-        ops.linear(h, self.w_qkv, self.b_qkv, qkv)
-        if writes_cache:
+        appended = False
+        if h is None and ops.can_fuse_layernorm(T, x.shape[1], self.w_qkv.dtype) and hasattr(norm, "eps"):
+            # few rows: norm, projection and the cache write in one kernel
+            scatter = None
+            if writes_cache:
+                scatter = (view.k, view.v, view.block_table, ctx.tok_slot, ctx.tok_pos, self.k_off, self.v_off,
+                           self.n_kv_heads, self.head_dim)
+                appended = True
+            ops.linear_layernorm(x, norm.weight, norm.bias, norm.eps, self.w_qkv, self.b_qkv, qkv, kv_scatter=scatter)
+        else:
+            if h is None:
+                h = norm(x, ctx.ws.get("block_normed", T, x.shape[1], ctx.act_dtype))
+            ops.linear(h, self.w_qkv, self.b_qkv, qkv)
+        if writes_cache and not appended:
             ops.kv_append(qkv, self.k_off, self.v_off, view.k, view.v, view.block_table, ctx.tok_slot,
                           ctx.tok_pos, T, self.n_kv_heads, self.head_dim, ctx.dev_err)
         merged = ctx.ws.get("attn_out", T, self.n_heads * self.head_dim, ctx.act_dtype)
@@ -69,6 +86,18 @@ class CausalSelfAttention:
         ops.linear(merged, self.w_out, self.b_out, x, residual=x)
 
     def _attend(self, qkv, view, merged, ctx: StepContext) -> None:
+        T = ctx.n_tokens
+        if ctx.max_new == 1:
+            # a decode step: few queries, long contexts → split every context across CTAs
+            n_split = ops.decode_splits(T, self.n_heads, ctx.max_context)
+            partials = counters = None
+            if n_split > 1:
+                partials = ctx.ws.get("attn_partials", T * self.n_heads * n_split, self.head_dim + 2, torch.float32)
+                counters = ctx.ws.get_zeroed("attn_counters", T * self.n_heads, torch.int32)
+            ops.attention_decode(qkv, self.q_off, view.k, view.v, view.block_table, ctx.tok_slot, ctx.tok_pos,
+                                 merged, T, self.n_heads, self.n_kv_heads, self.head_dim, self.scale, self.window,
+                                 n_split, partials, counters, ctx.dev_err)
+            return
         ops.attention_generic(qkv, self.q_off, view.k, view.v, view.block_table, ctx.tok_slot, ctx.tok_pos,
-                              merged, ctx.n_tokens, self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
+                              merged, T, self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
                               self.window, ctx.dev_err)
