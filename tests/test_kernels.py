@@ -103,7 +103,7 @@ def test_linear(M, N, K, in_dtype, out_dtype, tol, act):
         assert rel_err(nob.cpu(), x.double() @ w.double().T) < tol
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 96, 64), (8, 2304, 768), (13, 200, 96), (40, 320, 96), (32, 130, 1600), (64, 130, 768)])
+@pytest.mark.parametrize("M,N,K", [(1, 96, 64), (8, 2304, 768), (13, 200, 96), (16, 320, 96), (9, 130, 1600), (16, 130, 768)])
 @pytest.mark.parametrize("out_dtype,act", [(torch.bfloat16, None), (torch.bfloat16, "gelu_tanh"), (torch.float32, "gelu_erf")])
 def test_linear_with_fused_layernorm(M, N, K, out_dtype, act):
     from vlrf_b200.csrc import ops

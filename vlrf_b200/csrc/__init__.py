@@ -36,11 +36,12 @@ _SIGNATURES = {
     "vlrf_attn_generic": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
                           _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
                           _c_void_p, _c_void_p],
+    "vlrf_set_chained_launch": [_c_int],
     "vlrf_gemm_skinny_ln_fits": [_c_int, _c_int],
     "vlrf_gemm_skinny": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
                          _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_float,
                          _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
-                         _c_int, _c_int, _c_void_p],
+                         _c_int, _c_int, _c_void_p, _c_void_p],
     "vlrf_attn_decode": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
                          _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int,
                          _c_void_p, _c_void_p, _c_void_p, _c_void_p],

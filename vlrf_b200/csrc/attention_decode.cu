@@ -2,11 +2,11 @@
 //
 // A decode step has few queries (rows × heads), far fewer than the GPU has SMs, and each has a long
 // stream of keys and values to read; so the keys 0…position of a (row, head) are cut into `n_split`
-// contiguous parts, one CTA each.  Inside a CTA four warps take the 32-key chunks of the part in turn:
-// a lane computes one key's score from a 16-byte-vectorised read of its row, the warp keeps a running
-// (max, sum, weighted V sum) in float32 (reference: include/model/attention.hpp:265-307), the warps'
-// results are merged in shared memory, and the CTA writes its partial (max, sum, sum·V) to scratch
-// memory.  The CTA that finishes a (row, head) last — found with a counter in scratch memory that it
+// contiguous parts, one CTA each.  Inside a CTA four warps take the 32-key chunks of the part in turn
+// and each keeps a running (max, sum, weighted V sum) in float32 (reference:
+// include/model/attention.hpp:265-307); the warps' results are merged in shared memory, and the CTA
+// writes its partial (max, sum, sum·V) to scratch memory.  For head sizes 64 and 128 the keys and values
+// come by bulk copies into shared memory, all of a part in flight at once, on bounded mbarrier waits.  The CTA that finishes a (row, head) last — found with a counter in scratch memory that it
 // resets for the next call — merges the parts in the order of the splits and writes the output, so no
 // second launch is needed and the result does not depend on which CTA came last.
 //
@@ -40,150 +40,38 @@ template <> struct Vec16d<__nv_bfloat16> {
 constexpr int DEC_WARPS = 4;
 constexpr int DEC_MAX_DH = 256;
 constexpr int DEC_ND = DEC_MAX_DH / 32;
+constexpr uint32_t DEC_WAIT_LIMIT = 4000000u;
+constexpr int DEC_STAGE_BYTES = 64 * 1024;       // shared memory for the keys and values in flight
 
-// DH > 0: the head size is known at compile time and everything is unrolled, with all 16-byte loads of a
-// 32-key chunk in flight at once; DH == 0: any head size that is a multiple of 16, with loops.
-template <typename ET, int DH>
-__global__ void __launch_bounds__(DEC_WARPS * 32)
-attn_decode_kernel(const ET* __restrict__ qkv, int ld, int q_off, const ET* __restrict__ Kc,
-                   const ET* __restrict__ Vc, const int* __restrict__ block_table, int max_blocks,
-                   const int* __restrict__ tok_slot, const int* __restrict__ tok_pos, ET* __restrict__ out,
-                   int ld_out, int H, int Hkv, int dh, int BT, float scale, int window, int n_split,
-                   float* __restrict__ partials, int* __restrict__ counters, int* __restrict__ dev_err) {
-    extern __shared__ float sm[];                 // q [dh] | per warp: m, l, acc[dh]
-    float* q = sm;
-    float* wpart = sm + dh;                       // [DEC_WARPS][dh + 2]
-    __shared__ int s_last;
+__device__ __forceinline__ uint32_t dsmem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void dmbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(dsmem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void dmbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(dsmem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool dmbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(dsmem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void dbulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dsmem_u32(dst)), "l"(src), "r"(bytes), "r"(dsmem_u32(bar)) : "memory");
+}
+
+// What every variant does once its warps hold (m, l, acc by dimension) in `wpart` [DEC_WARPS][dh + 2]:
+// merge the warps in order, write the output (one split) or the CTA's partial, and let the CTA that
+// finishes a (row, head) last merge all splits in order.
+template <typename ET>
+__device__ void finish_cta(const float* wpart, int dh, int row, int h, int H, int split, int n_split,
+                           float* __restrict__ partials, int* __restrict__ counters, ET* __restrict__ out,
+                           int ld_out, int* s_last) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
-    const int slot = tok_slot[row];
-    if (slot < 0) return;                          // padding row: the whole CTA leaves
-    const int pos = tok_pos[row];
-    const int hk = h / (H / Hkv);
-    const ET* qsrc = qkv + (size_t)row * ld + q_off + (size_t)h * dh;
-    for (int i = threadIdx.x; i < dh; i += DEC_WARPS * 32) q[i] = ElemIO<ET>::load(qsrc + i) * scale;
-    __syncthreads();
-
-    const int first = (window > 0) ? max(0, pos - window + 1) : 0;
-    const int chunk0 = first / 32;
-    const int n_chunks = pos / 32 + 1 - chunk0;
-    const int per_split = (n_chunks + n_split - 1) / n_split;
-    const int c_begin = chunk0 + split * per_split;
-    const int c_end = min(chunk0 + n_chunks, c_begin + per_split);
-    const int* table = block_table + (size_t)slot * max_blocks;
-
-    constexpr int E = 16 / (int)sizeof(ET);               // elements of a 16-byte piece
-    constexpr int PARTS = DH > 0 ? DH / E : 1;            // pieces of a key's row
-    constexpr int KEYS_PER_ROUND = DH > 0 ? 32 / PARTS : 1;
-    constexpr int NACC = DH > 0 ? E : DEC_ND;
-    float acc[NACC];
-#pragma unroll
-    for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
-    float m = -INFINITY, l = 0.f;
-    bool lost = false;
-    const int part = DH > 0 ? lane % PARTS : 0, key_in_round = DH > 0 ? lane / PARTS : 0;
-    for (int c = c_begin + warp; c < c_end; c += DEC_WARPS) {
-        const int k0 = c * 32;
-        const int blk = table[k0 / BT];
-        if (blk < 0) { lost = true; break; }
-        const size_t base = (((size_t)blk * Hkv + hk) * BT + (k0 % BT)) * dh;
-        const int key = k0 + lane;
-        const bool valid = key >= first && key <= pos;
-        float s = -INFINITY;
-        if (DH > 0) {
-            // every lane reads its key's row (rows past the last key are inside the block: harmless, unused)
-            const ET* krow = Kc + base + (size_t)lane * DH;
-            float dot = 0.f;
-#pragma unroll
-            for (int p0 = 0; p0 < PARTS; p0 += 8) {
-                float kv[8][E];
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    if (p0 + i < PARTS) Vec16d<ET>::load(krow + (p0 + i) * E, kv[i]);
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    if (p0 + i < PARTS) {
-#pragma unroll
-                        for (int j = 0; j < E; ++j) dot = fmaf(q[(p0 + i) * E + j], kv[i][j], dot);
-                    }
-            }
-            if (valid) s = dot;
-        } else if (valid) {
-            const ET* krow = Kc + base + (size_t)lane * dh;
-            float dot = 0.f;
-            for (int cc = 0; cc < dh; cc += Vec16d<ET>::N) {
-                float kv[Vec16d<ET>::N];
-                Vec16d<ET>::load(krow + cc, kv);
-#pragma unroll
-                for (int j = 0; j < Vec16d<ET>::N; ++j) dot = fmaf(q[cc + j], kv[j], dot);
-            }
-            s = dot;
-        }
-        const float m_new = fmaxf(m, warp_max(s));
-        const float p = valid ? expf(s - m_new) : 0.f;
-        const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
-        l = l * corr + warp_sum(p);
-#pragma unroll
-        for (int i = 0; i < NACC; ++i) acc[i] *= corr;
-        const ET* vbase = Vc + base;
-        if (DH > 0) {
-            // the chunk's V rows are 32·DH contiguous elements: lane takes piece `part` of keys
-            // key_in_round, key_in_round + KEYS_PER_ROUND, …
-#pragma unroll
-            for (int r0 = 0; r0 < PARTS; r0 += 8) {
-                float vv[8][E];
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    if (r0 + i < PARTS)
-                        Vec16d<ET>::load(vbase + (size_t)((r0 + i) * KEYS_PER_ROUND + key_in_round) * DH + part * E, vv[i]);
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    if (r0 + i < PARTS) {
-                        const float pk = __shfl_sync(0xffffffffu, p, (r0 + i) * KEYS_PER_ROUND + key_in_round);
-                        if (pk != 0.f) {      // keys outside the range hold whatever was there before
-#pragma unroll
-                            for (int j = 0; j < E; ++j) acc[j] = fmaf(pk, vv[i][j], acc[j]);
-                        }
-                    }
-            }
-        } else {
-            const int n_here = min(32, pos - k0 + 1);
-            for (int j = 0; j < n_here; ++j) {
-                const float pj = __shfl_sync(0xffffffffu, p, j);
-                if (pj == 0.f) continue;
-                const ET* vrow = vbase + (size_t)j * dh;
-#pragma unroll
-                for (int i = 0; i < DEC_ND; ++i) {
-                    const int cc = i * 32 + lane;
-                    if (cc < dh) acc[i] = fmaf(pj, ElemIO<ET>::load(vrow + cc), acc[i]);
-                }
-            }
-        }
-        m = m_new;
-    }
-    if (lost && lane == 0) atomicOr(dev_err, VLRF_DEVERR_NO_BLOCK);
-
-    // merge the warps of this CTA (fixed order), write the CTA's partial
-    float* mine = wpart + warp * (dh + 2);
-    if (lane == 0) { mine[0] = m; mine[1] = l; }
-    if (DH > 0) {
-        // lanes with the same piece hold sums over different keys: add them up
-#pragma unroll
-        for (int o = PARTS; o < 32; o <<= 1)
-#pragma unroll
-            for (int j = 0; j < E; ++j) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
-        if (lane < PARTS) {
-#pragma unroll
-            for (int j = 0; j < E; ++j) mine[2 + part * E + j] = acc[j];
-        }
-    } else {
-#pragma unroll
-        for (int i = 0; i < DEC_ND; ++i) {
-            const int cc = i * 32 + lane;
-            if (cc < dh) mine[2 + cc] = acc[i];
-        }
-    }
-    __syncthreads();
     const size_t pidx = ((size_t)row * H + h) * n_split;
     if (warp == 0) {
         float M = -INFINITY;
@@ -223,41 +111,315 @@ attn_decode_kernel(const ET* __restrict__ qkv, int ld, int q_off, const ET* __re
         __syncwarp();
         if (lane == 0) {
             const int done = atomicAdd(counters + (size_t)row * H + h, 1);
-            s_last = (done == n_split - 1);
+            *s_last = (done == n_split - 1);
         }
     }
     if (n_split == 1) return;
     __syncthreads();
-    if (!s_last || warp != 0) return;
+    if (!*s_last || warp != 0) return;
     __threadfence();
     // this CTA finished last: merge all parts in split order
-    {
-        float M = -INFINITY;
-        for (int s = 0; s < n_split; ++s) M = fmaxf(M, __ldcg(partials + (pidx + s) * (dh + 2)));
-        float L = 0.f;
-        float o[DEC_ND];
+    float M = -INFINITY;
+    for (int s = 0; s < n_split; ++s) M = fmaxf(M, __ldcg(partials + (pidx + s) * (dh + 2)));
+    float L = 0.f;
+    float o[DEC_ND];
 #pragma unroll
-        for (int i = 0; i < DEC_ND; ++i) o[i] = 0.f;
-        for (int s = 0; s < n_split; ++s) {
-            const float* ps = partials + (pidx + s) * (dh + 2);
-            const float pm = __ldcg(ps);
-            const float f = (pm == -INFINITY) ? 0.f : expf(pm - M);
-            L += __ldcg(ps + 1) * f;
-#pragma unroll
-            for (int i = 0; i < DEC_ND; ++i) {
-                const int cc = i * 32 + lane;
-                if (cc < dh) o[i] += __ldcg(ps + 2 + cc) * f;
-            }
-        }
-        const float inv = (L > 0.f) ? 1.f / L : 0.f;
-        ET* dst = out + (size_t)row * ld_out + (size_t)h * dh;
+    for (int i = 0; i < DEC_ND; ++i) o[i] = 0.f;
+    for (int s = 0; s < n_split; ++s) {
+        const float* ps = partials + (pidx + s) * (dh + 2);
+        const float pm = __ldcg(ps);
+        const float f = (pm == -INFINITY) ? 0.f : expf(pm - M);
+        L += __ldcg(ps + 1) * f;
 #pragma unroll
         for (int i = 0; i < DEC_ND; ++i) {
             const int cc = i * 32 + lane;
-            if (cc < dh) ElemIO<ET>::store(dst + cc, o[i] * inv);
+            if (cc < dh) o[i] += __ldcg(ps + 2 + cc) * f;
         }
-        if (lane == 0) counters[(size_t)row * H + h] = 0;   // zero again for the next call
     }
+    const float inv = (L > 0.f) ? 1.f / L : 0.f;
+    ET* dst = out + (size_t)row * ld_out + (size_t)h * dh;
+#pragma unroll
+    for (int i = 0; i < DEC_ND; ++i) {
+        const int cc = i * 32 + lane;
+        if (cc < dh) ElemIO<ET>::store(dst + cc, o[i] * inv);
+    }
+    if (lane == 0) counters[(size_t)row * H + h] = 0;   // zero again for the next call
+}
+
+// Any head size that is a multiple of 16: ordinary loads, loops over the head size.
+template <typename ET>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+attn_decode_generic_kernel(const ET* __restrict__ qkv, int ld, int q_off, const ET* __restrict__ Kc,
+                           const ET* __restrict__ Vc, const int* __restrict__ block_table, int max_blocks,
+                           const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
+                           ET* __restrict__ out, int ld_out, int H, int Hkv, int dh, int BT, float scale,
+                           int window, int n_split, float* __restrict__ partials, int* __restrict__ counters,
+                           int* __restrict__ dev_err) {
+    extern __shared__ float sm[];                 // q [dh] | per warp: m, l, acc[dh]
+    float* q = sm;
+    float* wpart = sm + dh;                       // [DEC_WARPS][dh + 2]
+    __shared__ int s_last;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
+    pdl_launch_dependents();                       // the next kernel may start fetching its weights
+    pdl_wait();                                    // everything read below was written by earlier kernels
+    const int slot = tok_slot[row];
+    if (slot < 0) return;                          // padding row: the whole CTA leaves
+    const int pos = tok_pos[row];
+    const int hk = h / (H / Hkv);
+    const ET* qsrc = qkv + (size_t)row * ld + q_off + (size_t)h * dh;
+    for (int i = threadIdx.x; i < dh; i += DEC_WARPS * 32) q[i] = ElemIO<ET>::load(qsrc + i) * scale;
+    __syncthreads();
+
+    const int first = (window > 0) ? max(0, pos - window + 1) : 0;
+    const int chunk0 = first / 32;
+    const int n_chunks = pos / 32 + 1 - chunk0;
+    const int per_split = (n_chunks + n_split - 1) / n_split;
+    const int c_begin = chunk0 + split * per_split;
+    const int c_end = min(chunk0 + n_chunks, c_begin + per_split);
+    const int* table = block_table + (size_t)slot * max_blocks;
+
+    float acc[DEC_ND];
+#pragma unroll
+    for (int i = 0; i < DEC_ND; ++i) acc[i] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    bool lost = false;
+    for (int c = c_begin + warp; c < c_end; c += DEC_WARPS) {
+        const int k0 = c * 32;
+        const int blk = table[k0 / BT];
+        if (blk < 0) { lost = true; break; }
+        const size_t base = (((size_t)blk * Hkv + hk) * BT + (k0 % BT)) * dh;
+        const int key = k0 + lane;
+        const bool valid = key >= first && key <= pos;
+        float s = -INFINITY;
+        if (valid) {
+            const ET* krow = Kc + base + (size_t)lane * dh;
+            float dot = 0.f;
+            for (int cc = 0; cc < dh; cc += Vec16d<ET>::N) {
+                float kv[Vec16d<ET>::N];
+                Vec16d<ET>::load(krow + cc, kv);
+#pragma unroll
+                for (int j = 0; j < Vec16d<ET>::N; ++j) dot = fmaf(q[cc + j], kv[j], dot);
+            }
+            s = dot;
+        }
+        const float m_new = fmaxf(m, warp_max(s));
+        const float p = valid ? expf(s - m_new) : 0.f;
+        const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
+        l = l * corr + warp_sum(p);
+#pragma unroll
+        for (int i = 0; i < DEC_ND; ++i) acc[i] *= corr;
+        const int n_here = min(32, pos - k0 + 1);
+        const ET* vbase = Vc + base;
+        for (int j = 0; j < n_here; ++j) {
+            const float pj = __shfl_sync(0xffffffffu, p, j);
+            if (pj == 0.f) continue;
+            const ET* vrow = vbase + (size_t)j * dh;
+#pragma unroll
+            for (int i = 0; i < DEC_ND; ++i) {
+                const int cc = i * 32 + lane;
+                if (cc < dh) acc[i] = fmaf(pj, ElemIO<ET>::load(vrow + cc), acc[i]);
+            }
+        }
+        m = m_new;
+    }
+    if (lost && lane == 0) atomicOr(dev_err, VLRF_DEVERR_NO_BLOCK);
+    float* mine = wpart + warp * (dh + 2);
+    if (lane == 0) { mine[0] = m; mine[1] = l; }
+#pragma unroll
+    for (int i = 0; i < DEC_ND; ++i) {
+        const int cc = i * 32 + lane;
+        if (cc < dh) mine[2 + cc] = acc[i];
+    }
+    __syncthreads();
+    finish_cta<ET>(wpart, dh, row, h, H, split, n_split, partials, counters, out, ld_out, &s_last);
+}
+
+// Head size known at compile time.  The keys and values of the CTA's part are fetched by bulk copies,
+// 32 keys (one contiguous piece of a cache block) per copy, all in flight at once, each chunk completing on
+// its own mbarrier.  A 16-byte piece of a key's row belongs to one lane: the PARTS lanes of a key add
+// their partial dot products with shuffles, and the same lanes then weigh the same key's value pieces,
+// so a quarter warp always reads 128 contiguous bytes of shared memory.
+template <typename ET, int DH>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+attn_decode_bulk_kernel(const ET* __restrict__ qkv, int ld, int q_off, const ET* __restrict__ Kc,
+                        const ET* __restrict__ Vc, const int* __restrict__ block_table, int max_blocks,
+                        const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
+                        ET* __restrict__ out, int ld_out, int H, int Hkv, int BT, float scale, int window,
+                        int n_split, float* __restrict__ partials, int* __restrict__ counters,
+                        int* __restrict__ dev_err) {
+    constexpr int E = 16 / (int)sizeof(ET);               // elements of a 16-byte piece
+    constexpr int PARTS = DH / E;                         // pieces of a key's row = lanes per key
+    constexpr int KPR = 32 / PARTS;                       // keys per round of 32 lanes
+    constexpr int ROUNDS = PARTS;                         // rounds per 32-key chunk
+    constexpr int CHUNK_BYTES = 32 * DH * (int)sizeof(ET);
+    constexpr int CH_MAX = DEC_STAGE_BYTES / (2 * CHUNK_BYTES) < 8 ? DEC_STAGE_BYTES / (2 * CHUNK_BYTES) : 8;
+    static_assert(CH_MAX >= 1, "stage too small");
+    extern __shared__ __align__(128) unsigned char dsm[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(dsm);                        // CH_MAX barriers
+    unsigned char* kbuf = dsm + 128;                                         // [CH_MAX][CHUNK_BYTES]
+    unsigned char* vbuf = kbuf + (size_t)CH_MAX * CHUNK_BYTES;
+    float* wpart = reinterpret_cast<float*>(vbuf + (size_t)CH_MAX * CHUNK_BYTES);   // [DEC_WARPS][DH + 2]
+    __shared__ int s_last;
+    __shared__ int s_bad;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
+    pdl_launch_dependents();                       // the next kernel may start fetching its weights
+    pdl_wait();                                    // everything read below was written by earlier kernels
+    const int slot = tok_slot[row];
+    if (slot < 0) return;                          // padding row: the whole CTA leaves
+    const int pos = tok_pos[row];
+    const int hk = h / (H / Hkv);
+    const int part = lane % PARTS, kir = lane / PARTS;
+
+    const int first = (window > 0) ? max(0, pos - window + 1) : 0;
+    const int chunk0 = first / 32;
+    const int n_chunks = pos / 32 + 1 - chunk0;
+    const int per_split = (n_chunks + n_split - 1) / n_split;
+    const int c_begin = chunk0 + split * per_split;
+    const int c_end = min(chunk0 + n_chunks, c_begin + per_split);
+    const int* table = block_table + (size_t)slot * max_blocks;
+
+    if (threadIdx.x == 0) {
+        s_bad = 0;
+        for (int i = 0; i < CH_MAX; ++i) dmbar_init(&bars[i], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // this lane's piece of the query, scaled
+    float q[E];
+    {
+        const ET* qsrc = qkv + (size_t)row * ld + q_off + (size_t)h * DH + part * E;
+#pragma unroll
+        for (int j = 0; j < E; ++j) q[j] = ElemIO<ET>::load(qsrc + j) * scale;
+    }
+    __syncthreads();
+
+    float acc[E];
+#pragma unroll
+    for (int j = 0; j < E; ++j) acc[j] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    bool gave_up = false;
+    uint32_t parity = 0;
+    for (int r0 = c_begin; r0 < c_end; r0 += CH_MAX) {
+        const int n_here = min(CH_MAX, c_end - r0);
+        bool issued = false;
+        if (r0 > c_begin) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // reads of the buffers before refilling them
+        if ((int)threadIdx.x < n_here) {
+            const int k0 = (r0 + threadIdx.x) * 32;
+            const int blk = table[k0 / BT];
+            if (blk < 0) {
+                atomicOr(dev_err, VLRF_DEVERR_NO_BLOCK);
+                s_bad = 1;
+            } else {
+                const size_t base = (((size_t)blk * Hkv + hk) * BT + (k0 % BT)) * DH;
+                dmbar_expect_tx(&bars[threadIdx.x], 2 * CHUNK_BYTES);
+                dbulk_g2s(kbuf + (size_t)threadIdx.x * CHUNK_BYTES, Kc + base, CHUNK_BYTES, &bars[threadIdx.x]);
+                dbulk_g2s(vbuf + (size_t)threadIdx.x * CHUNK_BYTES, Vc + base, CHUNK_BYTES, &bars[threadIdx.x]);
+                issued = true;
+            }
+        }
+        __syncthreads();                           // s_bad is known
+        if (s_bad) {                               // leave only after the copies already issued have landed
+            if (issued) {
+                uint32_t polls = 0;
+                while (!dmbar_try_wait(&bars[threadIdx.x], parity) && ++polls <= DEC_WAIT_LIMIT) {}
+            }
+            __syncthreads();
+            break;
+        }
+        for (int i = warp; i < n_here && !gave_up; i += DEC_WARPS) {
+            uint32_t polls = 0;
+            while (!dmbar_try_wait(&bars[i], parity)) {
+                if (++polls > DEC_WAIT_LIMIT) { gave_up = true; break; }
+            }
+            if (gave_up) break;
+            const int k0 = (r0 + i) * 32;
+            const ET* kc = reinterpret_cast<const ET*>(kbuf + (size_t)i * CHUNK_BYTES);
+            const ET* vc = reinterpret_cast<const ET*>(vbuf + (size_t)i * CHUNK_BYTES);
+            float s[ROUNDS];
+#pragma unroll
+            for (int r = 0; r < ROUNDS; ++r) {
+                float kv[E];
+                Vec16d<ET>::load(kc + (size_t)(r * KPR + kir) * DH + part * E, kv);
+                float d = 0.f;
+#pragma unroll
+                for (int j = 0; j < E; ++j) d = fmaf(q[j], kv[j], d);
+                s[r] = d;
+            }
+            float cmax = -INFINITY;
+#pragma unroll
+            for (int r = 0; r < ROUNDS; ++r) {
+#pragma unroll
+                for (int o = 1; o < PARTS; o <<= 1) s[r] += __shfl_xor_sync(0xffffffffu, s[r], o);
+                const int key = k0 + r * KPR + kir;
+                if (key < first || key > pos) s[r] = -INFINITY;
+                cmax = fmaxf(cmax, s[r]);
+            }
+#pragma unroll
+            for (int o = PARTS; o < 32; o <<= 1) cmax = fmaxf(cmax, __shfl_xor_sync(0xffffffffu, cmax, o));
+            const float m_new = fmaxf(m, cmax);            // a chunk that is visited has a visible key
+            const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
+            float psum = 0.f;
+#pragma unroll
+            for (int j = 0; j < E; ++j) acc[j] *= corr;
+#pragma unroll
+            for (int r = 0; r < ROUNDS; ++r) {
+                const float p = (s[r] == -INFINITY) ? 0.f : expf(s[r] - m_new);
+                psum += p;
+                if (p != 0.f) {                            // hidden keys hold whatever was there before
+                    float vv[E];
+                    Vec16d<ET>::load(vc + (size_t)(r * KPR + kir) * DH + part * E, vv);
+#pragma unroll
+                    for (int j = 0; j < E; ++j) acc[j] = fmaf(p, vv[j], acc[j]);
+                }
+            }
+#pragma unroll
+            for (int o = PARTS; o < 32; o <<= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
+            l = l * corr + psum;
+            m = m_new;
+        }
+        if (gave_up) s_bad = 1;
+        parity ^= 1;
+        __syncthreads();                           // everyone is done with the buffers before they are refilled
+        if (s_bad) break;
+    }
+    if (gave_up && lane == 0) atomicOr(dev_err, VLRF_DEVERR_WAIT_TIMEOUT);
+
+    float* mine = wpart + warp * (DH + 2);
+    if (lane == 0) { mine[0] = m; mine[1] = l; }
+    // lanes with the same piece hold sums over different keys: add them up
+#pragma unroll
+    for (int o = PARTS; o < 32; o <<= 1)
+#pragma unroll
+        for (int j = 0; j < E; ++j) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+    if (lane < PARTS) {
+#pragma unroll
+        for (int j = 0; j < E; ++j) mine[2 + part * E + j] = acc[j];
+    }
+    __syncthreads();
+    finish_cta<ET>(wpart, DH, row, h, H, split, n_split, partials, counters, out, ld_out, &s_last);
+}
+
+template <typename ET, int DH>
+int launch_bulk(dim3 grid, const void* qkv, int ld, int q_off, const void* Kc, const void* Vc, const int* block_table,
+                int max_blocks, const int* tok_slot, const int* tok_pos, void* out, int ld_out, int H, int Hkv, int BT,
+                float scale, int window, int n_split, float* partials, int* counters, int* dev_err,
+                cudaStream_t stream) {
+    constexpr int CHUNK_BYTES = 32 * DH * (int)sizeof(ET);
+    constexpr int CH_MAX = DEC_STAGE_BYTES / (2 * CHUNK_BYTES) < 8 ? DEC_STAGE_BYTES / (2 * CHUNK_BYTES) : 8;
+    const size_t smem = 128 + (size_t)2 * CH_MAX * CHUNK_BYTES + (size_t)DEC_WARPS * (DH + 2) * sizeof(float);
+    auto kern = attn_decode_bulk_kernel<ET, DH>;
+    static bool raised = false;
+    if (!raised && smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "attn_decode: %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        raised = true;
+    }
+    cudaError_t e = launch_chained(kern, grid, dim3(DEC_WARPS * 32), smem, stream, (const ET*)qkv, ld, q_off,
+                                   (const ET*)Kc, (const ET*)Vc, block_table, max_blocks, tok_slot, tok_pos, (ET*)out,
+                                   ld_out, H, Hkv, BT, scale, window, n_split, partials, counters, dev_err);
+    if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "attn_decode: %s", cudaGetErrorString(e));
+    return vlrf_check_launch("attn_decode");
 }
 }  // namespace
 
@@ -281,22 +443,24 @@ extern "C" int vlrf_attn_decode(const void* qkv, int dtype, int ld, int q_off, c
     VLRF_REQUIRE(window >= 0 && dev_err != nullptr, "attn_decode: bad window or no error word");
     if (rows == 0) return VLRF_OK;
     dim3 grid(rows, H, n_split);
+#define BULK(ET, DHT) return launch_bulk<ET, DHT>(grid, qkv, ld, q_off, Kc, Vc, block_table, max_blocks, tok_slot, tok_pos, \
+                                                  out, ld_out, H, Hkv, BT, scale, window, n_split, partials, counters, dev_err, stream)
+    if (dtype == VLRF_BF16 && dh == 64) BULK(__nv_bfloat16, 64);
+    if (dtype == VLRF_BF16 && dh == 128) BULK(__nv_bfloat16, 128);
+    if (dtype == VLRF_F32 && dh == 64) BULK(float, 64);
+    if (dtype == VLRF_F32 && dh == 128) BULK(float, 128);
+#undef BULK
     const size_t smem = (size_t)(dh + DEC_WARPS * (dh + 2)) * sizeof(float);
-#define LAUNCH(ET, DHT)                                                                                      \
-    attn_decode_kernel<ET, DHT><<<grid, DEC_WARPS * 32, smem, stream>>>(                                    \
-        (const ET*)qkv, ld, q_off, (const ET*)Kc, (const ET*)Vc, block_table, max_blocks, tok_slot, tok_pos, \
-        (ET*)out, ld_out, H, Hkv, dh, BT, scale, window, n_split, partials, counters, dev_err)
-    if (dtype == VLRF_F32) {
-        if (dh == 64) LAUNCH(float, 64);
-        else if (dh == 128) LAUNCH(float, 128);
-        else LAUNCH(float, 0);
-    } else if (dtype == VLRF_BF16) {
-        if (dh == 64) LAUNCH(__nv_bfloat16, 64);
-        else if (dh == 128) LAUNCH(__nv_bfloat16, 128);
-        else LAUNCH(__nv_bfloat16, 0);
-    } else {
+    if (dtype == VLRF_F32)
+        attn_decode_generic_kernel<float><<<grid, DEC_WARPS * 32, smem, stream>>>(
+            (const float*)qkv, ld, q_off, (const float*)Kc, (const float*)Vc, block_table, max_blocks, tok_slot,
+            tok_pos, (float*)out, ld_out, H, Hkv, dh, BT, scale, window, n_split, partials, counters, dev_err);
+    else if (dtype == VLRF_BF16)
+        attn_decode_generic_kernel<__nv_bfloat16><<<grid, DEC_WARPS * 32, smem, stream>>>(
+            (const __nv_bfloat16*)qkv, ld, q_off, (const __nv_bfloat16*)Kc, (const __nv_bfloat16*)Vc, block_table,
+            max_blocks, tok_slot, tok_pos, (__nv_bfloat16*)out, ld_out, H, Hkv, dh, BT, scale, window, n_split,
+            partials, counters, dev_err);
+    else
         return vlrf_fail(VLRF_ERR_INVALID_ARG, "attn_decode: unknown dtype %d", dtype);
-    }
-#undef LAUNCH
     return vlrf_check_launch("attn_decode");
 }

@@ -35,6 +35,32 @@ int vlrf_check_launch(const char* what);
 #define VLRF_REQUIRE(cond, ...) \
     do { if (!(cond)) return vlrf_fail(VLRF_ERR_INVALID_ARG, __VA_ARGS__); } while (0)
 
+// Programmatic dependent launch: a kernel launched through `launch_chained` may begin while the kernel
+// before it on the stream is still running.  It may do only what does not depend on that kernel (set up
+// shared memory, start fetching weights) until `pdl_wait()` returns, which happens once every earlier
+// kernel has finished and its writes are visible.  `pdl_launch_dependents()` lets the next kernel begin in
+// the same way.  Every kernel of the step calls both, so that the chain never lets a kernel overtake data
+// it needs.  `vlrf_set_chained_launch(0)` turns the launch attribute off (the calls then do nothing).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+extern "C" int vlrf_chained_launch_enabled();
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                           Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = vlrf_chained_launch_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 template <typename T> struct ElemIO;
 template <> struct ElemIO<float> {
     static __device__ __forceinline__ float load(const float* p) { return *p; }

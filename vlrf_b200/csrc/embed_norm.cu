@@ -12,6 +12,8 @@ __global__ void embed_pos_kernel(const WT* __restrict__ wte, const WT* __restric
                                  const int* __restrict__ tokens, const int* __restrict__ positions,
                                  float* __restrict__ x, int d, int V, int P, int* __restrict__ dev_err) {
     const int t = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     int tok = tokens[t];
     if (tok < 0 || tok >= V) {
         if (threadIdx.x == 0) atomicOr(dev_err, VLRF_DEVERR_TOKEN_RANGE);
@@ -42,11 +44,11 @@ extern "C" int vlrf_embed(const void* wte, const void* wpe, int w_dtype, const i
     if (T == 0) return VLRF_OK;
     const int threads = d >= 256 ? 256 : 128;
     if (w_dtype == VLRF_F32)
-        embed_pos_kernel<float><<<T, threads, 0, stream>>>((const float*)wte, (const float*)wpe, tokens,
-                                                           positions, x, d, V, P, dev_err);
+        launch_chained(embed_pos_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)wte, (const float*)wpe,
+                       tokens, positions, x, d, V, P, dev_err);
     else if (w_dtype == VLRF_BF16)
-        embed_pos_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(
-            (const __nv_bfloat16*)wte, (const __nv_bfloat16*)wpe, tokens, positions, x, d, V, P, dev_err);
+        launch_chained(embed_pos_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (const __nv_bfloat16*)wte,
+                       (const __nv_bfloat16*)wpe, tokens, positions, x, d, V, P, dev_err);
     else
         return vlrf_fail(VLRF_ERR_INVALID_ARG, "embed: unknown weight dtype %d", w_dtype);
     return vlrf_check_launch("embed");
@@ -74,6 +76,8 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
     float* row = smem;          // d floats
     float* red = smem + d;      // 32 floats
     const int r = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     const float* src = x + (size_t)(rows ? rows[r] : r) * d;
     float s = 0.f;
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
@@ -104,10 +108,10 @@ extern "C" int vlrf_layernorm(const float* x, const int* rows, const float* gamm
     const int threads = d >= 1024 ? 256 : 128;
     const size_t smem = (size_t)(d + 32) * sizeof(float);
     if (out_dtype == VLRF_F32)
-        layernorm_kernel<float><<<n_rows, threads, smem, stream>>>(x, rows, gamma, beta, (float*)out, d, eps);
+        launch_chained(layernorm_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, x, rows, gamma, beta, (float*)out, d, eps);
     else if (out_dtype == VLRF_BF16)
-        layernorm_kernel<__nv_bfloat16><<<n_rows, threads, smem, stream>>>(x, rows, gamma, beta,
-                                                                         (__nv_bfloat16*)out, d, eps);
+        launch_chained(layernorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), smem, stream, x, rows, gamma, beta,
+                       (__nv_bfloat16*)out, d, eps);
     else
         return vlrf_fail(VLRF_ERR_INVALID_ARG, "layernorm: unknown output dtype %d", out_dtype);
     return vlrf_check_launch("layernorm");

@@ -96,6 +96,33 @@ def linear(x, w, bias, out, *, act=None, residual=None, rows: int | None = None)
 
 _SM_COUNT = None
 SKINNY_MAX_ROWS = 64
+FUSED_NORM_MAX_ROWS = 16
+_DEV_ERR = None
+
+
+def _dev_err() -> torch.Tensor:
+    """The process-wide device error word for kernels whose callers pass none: int32 [1]; `device_errors()`
+    reads and clears it."""
+    global _DEV_ERR
+    if _DEV_ERR is None:
+        _DEV_ERR = torch.zeros(1, dtype=torch.int32, device="cuda")
+    return _DEV_ERR
+
+
+def set_chained_launch(on: bool) -> None:
+    """Whether kernels are launched so that each may begin (fetch weights) while the one before it still
+    runs.  On by default; off gives plain stream order."""
+    call("vlrf_set_chained_launch", 1 if on else 0)
+
+
+def device_errors() -> int:
+    """Bits that kernels set in the shared error word since the last call (synchronises)."""
+    if _DEV_ERR is None:
+        return 0
+    word = int(_DEV_ERR.item())
+    if word:
+        _DEV_ERR.zero_()
+    return word
 
 
 def sm_count() -> int:
@@ -114,7 +141,7 @@ def _linear_dispatch(x, w, bias, out, act, residual, M, N, K) -> None:
     if x.dtype == torch.bfloat16 and M <= SKINNY_MAX_ROWS and K % 32 == 0:
         # few rows: the product is bound by streaming w once
         call("vlrf_gemm_skinny", _ptr(x), 0, _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), dtype_code(out.dtype),
-             M, N, K, K, N, act, 0, 0, 0.0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, sm_count(), _stream())
+             M, N, K, K, N, act, 0, 0, 0.0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, sm_count(), _ptr(_dev_err()), _stream())
         return
     call("vlrf_gemm_simt", _ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), M, N, K, K, N,
          dtype_code(x.dtype), dtype_code(out.dtype), act, _stream())
@@ -122,7 +149,8 @@ def _linear_dispatch(x, w, bias, out, act, residual, M, N, K) -> None:
 
 def can_fuse_layernorm(n_rows: int, width: int, w_dtype: torch.dtype) -> bool:
     """Whether `linear_layernorm` takes this many rows of this width."""
-    if w_dtype != torch.bfloat16 or n_rows > SKINNY_MAX_ROWS or n_rows < 1 or width % 32 != 0:
+    # with more rows, every CTA repeating the norm costs more than a norm kernel of its own
+    if w_dtype != torch.bfloat16 or n_rows > FUSED_NORM_MAX_ROWS or n_rows < 1 or width % 32 != 0:
         return False
     from . import library
     return bool(library().vlrf_gemm_skinny_ln_fits(n_rows, width))
@@ -153,7 +181,7 @@ def linear_layernorm(x, gamma, beta, eps: float, w, bias, out, *, act=None, rows
         kv = [_ptr(kc), _ptr(vc), _ptr(table), table.shape[1], _ptr(tok_slot), _ptr(tok_pos), k_off, v_off, hkv, dh,
               kc.shape[2]]
     call("vlrf_gemm_skinny", _ptr(x), 1, _ptr(w), _ptr(bias), 0, _ptr(out), dtype_code(out.dtype), M, N, K, K, N,
-         ACT[act], _ptr(gamma), _ptr(beta), float(eps), *kv, sm_count(), _stream())
+         ACT[act], _ptr(gamma), _ptr(beta), float(eps), *kv, sm_count(), _ptr(_dev_err()), _stream())
 
 
 def decode_splits(n_rows: int, n_heads: int, max_context: int) -> int:

@@ -102,6 +102,8 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
     __shared__ int s_choice;
 
     const int row = blockIdx.x, tid = threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     const float* lg = logits + (size_t)row * ld;
 
     ArgMax am{-INFINITY, 0x7fffffff};
@@ -296,7 +298,8 @@ extern "C" int vlrf_sample(const float* logits, int ld, int n_rows, int V, const
     VLRF_REQUIRE(temperature == nullptr || (rng_key != nullptr && rng_ctr != nullptr),
                  "sample: temperature sampling needs the rows' random keys and counters");
     if (n_rows == 0) return VLRF_OK;
-    sample_kernel<<<n_rows, ST, 0, stream>>>(logits, ld, V, temperature, top_k, top_p, rng_key, rng_ctr, out_token);
+    launch_chained(sample_kernel, dim3(n_rows), dim3(ST), 0, stream, logits, ld, V, temperature, top_k, top_p, rng_key,
+                   rng_ctr, out_token);
     return vlrf_check_launch("sample");
 }
 

@@ -33,3 +33,7 @@ extern "C" int vlrf_device_info(int* sm_count, int* cc_major, int* cc_minor, int
     *max_smem_optin = (int)p.sharedMemPerBlockOptin;
     return VLRF_OK;
 }
+
+static int g_chained = 1;
+extern "C" int vlrf_chained_launch_enabled() { return g_chained; }
+extern "C" int vlrf_set_chained_launch(int on) { g_chained = on ? 1 : 0; return VLRF_OK; }

@@ -157,7 +157,8 @@ class Engine:
 
     def check_device_errors(self) -> None:
         """Read the device's error word (synchronises) and raise if a kernel set a bit."""
-        word = int(self.dev_err.item())
+        from ..csrc import ops
+        word = int(self.dev_err.item()) | ops.device_errors()
         if word:
             self.dev_err.zero_()
             what = [txt for bit, txt in DEVERR_TEXT.items() if word & bit]
