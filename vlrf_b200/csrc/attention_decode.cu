@@ -428,11 +428,11 @@ extern "C" long long vlrf_attn_decode_scratch_floats(int rows, int H, int dh, in
     return (long long)rows * H * n_split * (dh + 2);
 }
 
-extern "C" int vlrf_attn_decode(const void* qkv, int dtype, int ld, int q_off, const void* Kc, const void* Vc,
-                                const int* block_table, int max_blocks, const int* tok_slot,
-                                const int* tok_pos, void* out, int ld_out, int rows, int H, int Hkv, int dh,
-                                int BT, float scale, int window, int n_split, float* partials, int* counters,
-                                int* dev_err, cudaStream_t stream) {
+static int attn_decode_impl(const void* qkv, int dtype, int ld, int q_off, const void* Kc, const void* Vc,
+                            const int* block_table, int max_blocks, const int* tok_slot, const int* tok_pos,
+                            void* out, int ld_out, int rows, int H, int Hkv, int dh, int BT, float scale,
+                            int window, int n_split, float* partials, int* counters, int* dev_err,
+                            cudaStream_t stream) {
     VLRF_REQUIRE(rows >= 0 && H > 0 && Hkv > 0 && max_blocks > 0, "attn_decode: bad sizes");
     VLRF_REQUIRE(H % Hkv == 0, "attn_decode: %d heads cannot share %d key/value heads", H, Hkv);
     VLRF_REQUIRE(dh > 0 && dh % 16 == 0 && dh <= DEC_MAX_DH,
@@ -463,4 +463,73 @@ extern "C" int vlrf_attn_decode(const void* qkv, int dtype, int ld, int q_off, c
     else
         return vlrf_fail(VLRF_ERR_INVALID_ARG, "attn_decode: unknown dtype %d", dtype);
     return vlrf_check_launch("attn_decode");
+}
+
+extern "C" int vlrf_attn_decode(const void* qkv, int dtype, int ld, int q_off, const void* Kc, const void* Vc,
+                                const int* block_table, int max_blocks, const int* tok_slot,
+                                const int* tok_pos, void* out, int ld_out, int rows, int H, int Hkv, int dh,
+                                int BT, float scale, int window, int n_split, float* partials, int* counters,
+                                int* dev_err, cudaStream_t stream) {
+    return attn_decode_impl(qkv, dtype, ld, q_off, Kc, Vc, block_table, max_blocks, tok_slot, tok_pos, out, ld_out,
+                            rows, H, Hkv, dh, BT, scale, window, n_split, partials, counters, dev_err, stream);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// The same decode attention for callers that must not allocate (declared in attention_decode_noalloc.h).
+// Its scratch memory lives in this library's image instead of coming from the caller.
+#include "attention_decode_noalloc.h"
+#include <mutex>
+
+static __device__ __align__(256) float g_noalloc_partials[VLRF_NOALLOC_MAX_PARTIAL_FLOATS];
+static __device__ __align__(256) int g_noalloc_counters[VLRF_NOALLOC_MAX_ROW_HEADS];
+
+namespace {
+constexpr int NOALLOC_MAX_DEVICES = 64;
+std::mutex g_noalloc_mutex;
+float* g_noalloc_partials_addr[NOALLOC_MAX_DEVICES] = {nullptr};
+int* g_noalloc_counters_addr[NOALLOC_MAX_DEVICES] = {nullptr};
+}  // namespace
+
+extern "C" int vlrf_attn_decode_noalloc(const void* qkv, int dtype, int ld, int q_off, const void* Kc,
+                                        const void* Vc, const int* block_table, int max_blocks,
+                                        const int* tok_slot, const int* tok_pos, void* out, int ld_out,
+                                        int rows, int H, int Hkv, int dh, int BT, float scale, int window,
+                                        int n_split, int* dev_err, cudaStream_t stream) {
+    VLRF_REQUIRE(rows >= 0 && H > 0 && n_split >= 1 && dh > 0, "attn_decode_noalloc: bad sizes");
+    VLRF_REQUIRE((long long)rows * H <= VLRF_NOALLOC_MAX_ROW_HEADS,
+                 "attn_decode_noalloc: %d rows x %d heads exceed the built-in scratch for %d (row, head) pairs",
+                 rows, H, VLRF_NOALLOC_MAX_ROW_HEADS);
+    VLRF_REQUIRE((long long)rows * H * n_split * (dh + 2) <= VLRF_NOALLOC_MAX_PARTIAL_FLOATS,
+                 "attn_decode_noalloc: %d rows x %d heads x %d splits x head size %d exceed the built-in scratch of %d floats",
+                 rows, H, n_split, dh, VLRF_NOALLOC_MAX_PARTIAL_FLOATS);
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "attn_decode_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
+    VLRF_REQUIRE(dev >= 0 && dev < NOALLOC_MAX_DEVICES, "attn_decode_noalloc: device %d is beyond the %d this entry point tracks", dev, NOALLOC_MAX_DEVICES);
+    float* partials = nullptr;
+    int* counters = nullptr;
+    {
+        // Set-up, once per device, with that device current: in host code the arrays' names are only
+        // stand-ins; their device addresses have to be asked for.
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        if (g_noalloc_partials_addr[dev] == nullptr) {
+            float* p = nullptr;
+            int* c = nullptr;
+            e = cudaGetSymbolAddress((void**)&p, g_noalloc_partials);
+            if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "attn_decode_noalloc: address of the partials: %s", cudaGetErrorString(e));
+            e = cudaGetSymbolAddress((void**)&c, g_noalloc_counters);
+            if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "attn_decode_noalloc: address of the counters: %s", cudaGetErrorString(e));
+            g_noalloc_partials_addr[dev] = p;
+            g_noalloc_counters_addr[dev] = c;
+        }
+        partials = g_noalloc_partials_addr[dev];
+        counters = g_noalloc_counters_addr[dev];
+    }
+    if (n_split > 1 && rows > 0) {
+        // the counters must start at zero; whatever an earlier call left is cleared (no allocation involved)
+        e = cudaMemsetAsync(counters, 0, (size_t)rows * H * sizeof(int), stream);
+        if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "attn_decode_noalloc: clearing the counters: %s", cudaGetErrorString(e));
+    }
+    return attn_decode_impl(qkv, dtype, ld, q_off, Kc, Vc, block_table, max_blocks, tok_slot, tok_pos, out, ld_out,
+                            rows, H, Hkv, dh, BT, scale, window, n_split, partials, counters, dev_err, stream);
 }
