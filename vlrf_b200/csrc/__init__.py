@@ -42,6 +42,9 @@ _SIGNATURES = {
                          _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_float,
                          _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
                          _c_int, _c_int, _c_void_p, _c_void_p],
+    "vlrf_gemm_tcgen05_takes": [_c_int, _c_int, _c_int, _c_int],
+    "vlrf_gemm_tcgen05": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+                          _c_int, _c_int, _c_void_p, _c_void_p],
     "vlrf_attn_decode": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
                          _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int,
                          _c_void_p, _c_void_p, _c_void_p, _c_void_p],

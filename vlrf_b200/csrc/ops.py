@@ -95,6 +95,7 @@ def linear(x, w, bias, out, *, act=None, residual=None, rows: int | None = None)
 
 
 _SM_COUNT = None
+USE_TCGEN05 = True
 SKINNY_MAX_ROWS = 64
 FUSED_NORM_MAX_ROWS = 16
 _DEV_ERR = None
@@ -142,6 +143,11 @@ def _linear_dispatch(x, w, bias, out, act, residual, M, N, K) -> None:
         # few rows: the product is bound by streaming w once
         call("vlrf_gemm_skinny", _ptr(x), 0, _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), dtype_code(out.dtype),
              M, N, K, K, N, act, 0, 0, 0.0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, sm_count(), _ptr(_dev_err()), _stream())
+        return
+    if x.dtype == torch.bfloat16 and K % 8 == 0 and USE_TCGEN05:
+        # many rows: the tensor-core kernel (tcgen05, accumulator in tensor memory)
+        call("vlrf_gemm_tcgen05", _ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), M, N, K, K, N,
+             dtype_code(out.dtype), act, _ptr(_dev_err()), _stream())
         return
     call("vlrf_gemm_simt", _ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), M, N, K, K, N,
          dtype_code(x.dtype), dtype_code(out.dtype), act, _stream())
