@@ -16,7 +16,12 @@ TINY_A = dict(model_type="gpt2", n_layer=2, n_embd=64, n_head=4, n_inner=256, vo
 TINY_B = dict(model_type="gpt2", n_layer=3, n_embd=96, n_head=3, n_inner=320, vocab_size=1000, n_positions=256,
               layer_norm_epsilon=1e-6, activation_function="gelu", scale_attn_by_inverse_layer_idx=True,
               tie_word_embeddings=True, bos_token_id=1, eos_token_id=2)
-TINY = {"tiny_a": TINY_A, "tiny_b": TINY_B}
+#: a third one with the head size of the real GPT-2 family (64), so that the kernels that serving uses
+#: (tensor-core prompt attention, bulk-copy decode attention) run inside the engine tests too
+TINY_C = dict(model_type="gpt2", n_layer=2, n_embd=192, n_head=3, n_inner=None, vocab_size=777, n_positions=320,
+              layer_norm_epsilon=1e-5, activation_function="gelu_new", scale_attn_by_inverse_layer_idx=False,
+              tie_word_embeddings=True, bos_token_id=5, eos_token_id=6)
+TINY = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C}
 
 #: tolerances, fixed before the first measurement: the largest absolute logit error over the logit scale
 #: (largest absolute logit of the plain implementation)

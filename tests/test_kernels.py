@@ -295,6 +295,62 @@ def test_attention_finds_one_far_key(far):
     assert rel_err(got, plain_attention(q, k, v, 1.0)) < 2e-5
 
 
+PREFILL_CASES = [  # H, Hkv, dh, [(tokens already cached, new tokens)], window
+    (2, 2, 64, [(0, 64)], 0), (3, 3, 64, [(0, 1), (0, 65), (0, 200)], 0), (4, 2, 64, [(37, 100), (128, 3), (0, 64)], 0),
+    (2, 1, 128, [(0, 130), (64, 70)], 0), (12, 12, 64, [(0, 300), (250, 50)], 0), (2, 2, 64, [(0, 260), (100, 90)], 70),
+    (2, 2, 128, [(5, 140)], 64),
+]
+
+
+@pytest.mark.parametrize("H,Hkv,dh,seqs,window", PREFILL_CASES)
+def test_attention_prefill_tensor_cores(H, Hkv, dh, seqs, window):
+    """Ragged batches with unequal lengths and continuations, grouped heads, a window; the cache is NaN
+    outside what the sequences hold, and freed-looking rows inside their last blocks are NaN too."""
+    from vlrf_b200.csrc import ops
+    dtype = torch.bfloat16
+    scale = 0.8 / math.sqrt(dh)
+    n_blocks = sum((p + n + 63) // 64 for p, n in seqs) + 2
+    kc = torch.full((n_blocks, Hkv, 64, dh), float("nan"), dtype=dtype)
+    vc = torch.full((n_blocks, Hkv, 64, dh), float("nan"), dtype=dtype)
+    order = torch.randperm(n_blocks, generator=g(50)).tolist()
+    max_blocks = max((p + n + 63) // 64 for p, n in seqs) + 1
+    table = torch.full((len(seqs) + 1, max_blocks), -1, dtype=torch.int32)
+    T = sum(n for _, n in seqs)
+    W = (H + 2 * Hkv) * dh
+    qkv = torch.zeros(T, W, dtype=dtype)
+    starts, want, at = [0], [], 0
+    for i, (p0, n) in enumerate(seqs):
+        C = p0 + n
+        q = randn(H, n, dh, seed=60 + i).to(dtype).float()
+        k = randn(Hkv, C, dh, seed=70 + i).to(dtype).float()
+        v = randn(Hkv, C, dh, seed=80 + i).to(dtype).float()
+        if C > 40:                          # one far key that a late query likes best
+            k[:, 3] = q[:Hkv, -1] * 3.0 if Hkv <= H else k[:, 3]
+        for b in range((C + 63) // 64):
+            blk = order.pop()
+            table[i + 1, b] = blk           # slot i+1 (slot 0 stays unused)
+            m = min(64, C - 64 * b)
+            kc[blk, :, :m] = k[:, 64 * b:64 * b + m].to(dtype)
+            vc[blk, :, :m] = v[:, 64 * b:64 * b + m].to(dtype)
+        qkv[at:at + n, :H * dh] = q.permute(1, 0, 2).reshape(n, H * dh).to(dtype)
+        want.append(plain_attention(q, k, v, scale, window))
+        at += n
+        starts.append(at)
+    out = torch.full((T, H * dh), float("nan"), dtype=dtype, device=DEV)
+    e = err_word()
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)  # noqa: E731
+    assert ops.attention_prefill_takes(dtype, dh, 64, W, 0)
+    ops.attention_prefill(qkv.to(DEV), 0, kc.to(DEV), vc.to(DEV), table.to(DEV), i32(list(range(1, len(seqs) + 1))),
+                          i32(starts), i32([p for p, _ in seqs]), out, T, len(seqs), max(n for _, n in seqs), H, Hkv, dh,
+                          scale, window, e)
+    assert int(e.item()) == 0
+    got = out.float().cpu()
+    assert torch.isfinite(got).all()
+    for i, (p0, n) in enumerate(seqs):
+        mine = got[starts[i]:starts[i + 1]].reshape(n, H, dh).permute(1, 0, 2)
+        assert rel_err(mine, want[i]) < 1.5e-2, (i, p0, n)
+
+
 def test_kv_append_writes_each_token_where_its_slot_says():
     from vlrf_b200.csrc import ops
     Hkv, dh, T = 3, 16, 70

@@ -45,6 +45,10 @@ _SIGNATURES = {
     "vlrf_gemm_tcgen05_takes": [_c_int, _c_int, _c_int, _c_int],
     "vlrf_gemm_tcgen05": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
                           _c_int, _c_int, _c_void_p, _c_void_p],
+    "vlrf_attn_prefill_takes": [_c_int, _c_int, _c_int, _c_int],
+    "vlrf_attn_prefill": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
+                          _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
+                          _c_int, _c_void_p, _c_void_p],
     "vlrf_attn_decode": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
                          _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int,
                          _c_void_p, _c_void_p, _c_void_p, _c_void_p],

@@ -291,3 +291,33 @@ def apply_penalties(logits, n_rows: int, generated, generated_len, *, repetition
     V = logits.shape[1]
     call("vlrf_apply_penalties", _ptr(logits), V, n_rows, V, _ptr(generated), generated.shape[1],
          _ptr(generated_len), _ptr(repetition), _ptr(frequency), _ptr(presence), _ptr(no_repeat_ngram), _stream())
+
+
+def attention_prefill_takes(dtype: torch.dtype, head_dim: int, block_tokens: int, row_width: int, q_off: int) -> bool:
+    """Whether the tensor-core prompt attention takes these sizes."""
+    if dtype != torch.bfloat16:
+        return False
+    from . import library
+    return bool(library().vlrf_attn_prefill_takes(head_dim, block_tokens, row_width, q_off))
+
+
+def attention_prefill(qkv, q_off: int, k_cache, v_cache, block_table, seq_slot, seq_start, seq_pos0, out,
+                      n_tokens: int, n_seqs: int, max_new: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                      scale: float, window: int, dev_err) -> None:
+    """Causal attention of every sequence's new tokens (rows seq_start[i] … seq_start[i+1]−1 of qkv, the
+    first of them at position seq_pos0[i]) over the sequence's cache, which already holds these tokens'
+    keys and values.  bfloat16, head size 64 or 128."""
+    _dev(qkv, "qkv", torch.bfloat16); _dev(k_cache, "k_cache", torch.bfloat16); _dev(v_cache, "v_cache", torch.bfloat16)
+    _dev(out, "out", torch.bfloat16); _dev(block_table, "block_table", torch.int32)
+    _dev(seq_slot, "seq_slot", torch.int32); _dev(seq_start, "seq_start", torch.int32)
+    _dev(seq_pos0, "seq_pos0", torch.int32); _dev(dev_err, "dev_err", torch.int32)
+    nb, hkv, bt, dh = k_cache.shape
+    if hkv != n_kv_heads or dh != head_dim or v_cache.shape != k_cache.shape:
+        raise KernelError("attention_prefill: cache shape does not match the heads")
+    if out.shape[1] != n_heads * head_dim or out.shape[0] < n_tokens or qkv.shape[0] < n_tokens:
+        raise KernelError("attention_prefill: output does not match")
+    if seq_slot.shape[0] < n_seqs or seq_start.shape[0] < n_seqs + 1 or seq_pos0.shape[0] < n_seqs:
+        raise KernelError("attention_prefill: sequence tables are too short")
+    call("vlrf_attn_prefill", _ptr(qkv), qkv.shape[1], q_off, _ptr(k_cache), _ptr(v_cache), nb, _ptr(block_table),
+         block_table.shape[1], _ptr(seq_slot), _ptr(seq_start), _ptr(seq_pos0), _ptr(out), out.shape[1], n_tokens, n_seqs,
+         max_new, n_heads, n_kv_heads, head_dim, bt, float(scale), int(window), _ptr(dev_err), _stream())

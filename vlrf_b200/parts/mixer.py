@@ -98,6 +98,12 @@ class CausalSelfAttention:
                                  merged, T, self.n_heads, self.n_kv_heads, self.head_dim, self.scale, self.window,
                                  n_split, partials, counters, ctx.dev_err)
             return
+        if ops.attention_prefill_takes(qkv.dtype, self.head_dim, view.k.shape[2], qkv.shape[1], self.q_off):
+            # a prompt step in bfloat16: tiles of 64 queries on the tensor cores
+            ops.attention_prefill(qkv, self.q_off, view.k, view.v, view.block_table, ctx.seq_slot, ctx.seq_start,
+                                  ctx.seq_pos0, merged, T, ctx.n_seqs, ctx.max_new, self.n_heads, self.n_kv_heads,
+                                  self.head_dim, self.scale, self.window, ctx.dev_err)
+            return
         ops.attention_generic(qkv, self.q_off, view.k, view.v, view.block_table, ctx.tok_slot, ctx.tok_pos,
                               merged, T, self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
                               self.window, ctx.dev_err)
