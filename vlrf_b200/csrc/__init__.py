@@ -44,7 +44,8 @@ _SIGNATURES = {
                          _c_int, _c_int, _c_void_p, _c_void_p],
     "vlrf_gemm_tcgen05_takes": [_c_int, _c_int, _c_int, _c_int],
     "vlrf_gemm_tcgen05": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
-                          _c_int, _c_int, _c_void_p, _c_void_p],
+                          _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int,
+                          _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "vlrf_attn_prefill_takes": [_c_int, _c_int, _c_int, _c_int],
     "vlrf_attn_prefill": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
                           _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,

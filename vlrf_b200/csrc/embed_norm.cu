@@ -98,6 +98,80 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
         ElemIO<OT>::store(dst + i, (row[i] - mean) * inv * gamma[i] + beta[i]);
 }
 
+// One warp per row, 16 bytes a lane a load; the row stays in registers when it has at most 2,048 values,
+// else it is read a second and third time (from L1/L2).  For widths that are multiples of 4.
+template <typename OT>
+__global__ void __launch_bounds__(256) layernorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                                                              const float* __restrict__ gamma,
+                                                              const float* __restrict__ beta, OT* __restrict__ out,
+                                                              int n_rows, int d, float eps) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.x * 8 + warp;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (r >= n_rows) return;
+    const float4* src = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * d);
+    const int nv = d >> 2;                       // float4s in the row
+    constexpr int CACHE = 16;                    // float4s a lane keeps (16 × 32 × 4 = 2,048 values)
+    float4 v[CACHE];
+    const bool cached = nv <= CACHE * 32;
+    float s = 0.f;
+    if (cached) {
+#pragma unroll
+        for (int j = 0; j < CACHE; ++j) {
+            const int i = j * 32 + lane;
+            if (i < nv) { v[j] = src[i]; s += (v[j].x + v[j].y) + (v[j].z + v[j].w); }
+        }
+    } else {
+        for (int i = lane; i < nv; i += 32) { const float4 a = src[i]; s += (a.x + a.y) + (a.z + a.w); }
+    }
+    const float mean = warp_sum(s) / (float)d;
+    float q = 0.f;
+    if (cached) {
+#pragma unroll
+        for (int j = 0; j < CACHE; ++j) {
+            const int i = j * 32 + lane;
+            if (i < nv) {
+                const float a = v[j].x - mean, b = v[j].y - mean, c = v[j].z - mean, e = v[j].w - mean;
+                q += (a * a + b * b) + (c * c + e * e);
+            }
+        }
+    } else {
+        for (int i = lane; i < nv; i += 32) {
+            const float4 t = src[i];
+            const float a = t.x - mean, b = t.y - mean, c = t.z - mean, e = t.w - mean;
+            q += (a * a + b * b) + (c * c + e * e);
+        }
+    }
+    const float inv = 1.f / sqrtf(warp_sum(q) / (float)d + eps);
+    OT* dst = out + (size_t)r * d;
+    const float4* g4 = reinterpret_cast<const float4*>(gamma);
+    const float4* b4 = reinterpret_cast<const float4*>(beta);
+    auto emit = [&](int i, const float4& t) {
+        const float4 gm = g4[i], bt = b4[i];
+        const float y0 = (t.x - mean) * inv * gm.x + bt.x, y1 = (t.y - mean) * inv * gm.y + bt.y;
+        const float y2 = (t.z - mean) * inv * gm.z + bt.z, y3 = (t.w - mean) * inv * gm.w + bt.w;
+        if (sizeof(OT) == 4) {
+            reinterpret_cast<float4*>(dst)[i] = make_float4(y0, y1, y2, y3);
+        } else {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(y0, y1), hi = __floats2bfloat162_rn(y2, y3);
+            uint2 pk;
+            pk.x = *reinterpret_cast<uint32_t*>(&lo);
+            pk.y = *reinterpret_cast<uint32_t*>(&hi);
+            reinterpret_cast<uint2*>(dst)[i] = pk;
+        }
+    };
+    if (cached) {
+#pragma unroll
+        for (int j = 0; j < CACHE; ++j) {
+            const int i = j * 32 + lane;
+            if (i < nv) emit(i, v[j]);
+        }
+    } else {
+        for (int i = lane; i < nv; i += 32) emit(i, src[i]);
+    }
+}
+
 extern "C" int vlrf_layernorm(const float* x, const int* rows, const float* gamma, const float* beta,
                               void* out, int out_dtype, int n_rows, int d, float eps,
                               cudaStream_t stream) {
@@ -105,6 +179,17 @@ extern "C" int vlrf_layernorm(const float* x, const int* rows, const float* gamm
     VLRF_REQUIRE(d <= 48 * 1024 / 4 - 32, "layernorm: width %d exceeds the %d this kernel holds in shared memory",
                  d, 48 * 1024 / 4 - 32);
     if (n_rows == 0) return VLRF_OK;
+    if (d % 4 == 0 && n_rows >= 8) {
+        const dim3 grid((n_rows + 7) / 8);
+        if (out_dtype == VLRF_F32)
+            launch_chained(layernorm_warp_kernel<float>, grid, dim3(256), 0, stream, x, rows, gamma, beta, (float*)out, n_rows, d, eps);
+        else if (out_dtype == VLRF_BF16)
+            launch_chained(layernorm_warp_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, x, rows, gamma, beta,
+                           (__nv_bfloat16*)out, n_rows, d, eps);
+        else
+            return vlrf_fail(VLRF_ERR_INVALID_ARG, "layernorm: unknown output dtype %d", out_dtype);
+        return vlrf_check_launch("layernorm");
+    }
     const int threads = d >= 1024 ? 256 : 128;
     const size_t smem = (size_t)(d + 32) * sizeof(float);
     if (out_dtype == VLRF_F32)

@@ -27,6 +27,14 @@ constexpr int TC_BK = 64;
 constexpr int TC_THREADS = 192;
 constexpr uint32_t TC_WAIT_LIMIT = 1u << 21;
 
+// Optional scatter of the K and V columns of a fused q/k/v projection into one layer's paged cache
+// (reference: include/model/kv_cache.hpp:215-251).  Kc == nullptr: none.
+struct TcKvScatter {
+    void* Kc; void* Vc;            // [block][kv_head][BT][dh], bf16
+    const int* block_table; const int* tok_slot; const int* tok_pos;
+    int max_blocks, k_off, v_off, width, dh, Hkv, BT;   // width = Hkv*dh
+};
+
 __device__ __forceinline__ uint32_t tsm(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void tbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(tsm(bar)), "r"(count));
@@ -91,7 +99,7 @@ template <int BN, int STAGES, typename OT>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                     const float* __restrict__ bias, const float* residual, OT* Y, int M, int N, int K, int ldy,
-                    int act, int* __restrict__ dev_err) {
+                    int act, TcKvScatter kv, int* __restrict__ dev_err) {
     extern __shared__ unsigned char tc_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
@@ -159,6 +167,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         if (!have) atomicExch(s_abort, 1);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int m = m0 + warp * 32 + lane;
+        // where this thread's row goes in the cache, if the product feeds one
+        int kv_blk = -2, kv_row = 0;                   // −2: nothing to write
+        if (kv.Kc != nullptr && m < M) {
+            const int slot = kv.tok_slot[m];
+            if (slot >= 0) {
+                const int pos = kv.tok_pos[m];
+                kv_blk = kv.block_table[(size_t)slot * kv.max_blocks + pos / kv.BT];
+                kv_row = pos % kv.BT;
+                if (kv_blk < 0) atomicOr(dev_err, VLRF_DEVERR_NO_BLOCK);
+            }
+        }
         if (have && !*s_abort) {
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -196,6 +215,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                                 pk.x = *reinterpret_cast<uint32_t*>(&p0); pk.y = *reinterpret_cast<uint32_t*>(&p1);
                                 pk.z = *reinterpret_cast<uint32_t*>(&p2); pk.w = *reinterpret_cast<uint32_t*>(&p3);
                                 *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(yrow) + j) = pk;
+                                const int n = n0 + c0 + j;                 // 8 columns: one head, one of q / k / v
+                                if (kv_blk >= 0 && n >= kv.k_off) {
+                                    const bool is_v = n >= kv.v_off;
+                                    const int col = n - (is_v ? kv.v_off : kv.k_off);
+                                    if (col < kv.width) {
+                                        const int hh = col / kv.dh, cc = col - hh * kv.dh;
+                                        __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(is_v ? kv.Vc : kv.Kc);
+                                        *reinterpret_cast<uint4*>(base + (((size_t)kv_blk * kv.Hkv + hh) * kv.BT + kv_row) * kv.dh + cc) = pk;
+                                    }
+                                }
                             }
                         }
                     } else {
@@ -205,6 +234,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                             x = apply_act_rt(x, act);
                             if (rrow) x += rrow[j];
                             ElemIO<OT>::store(yrow + j, x);
+                            const int n = n0 + c0 + j;
+                            if (kv_blk >= 0 && n >= kv.k_off) {
+                                const bool is_v = n >= kv.v_off;
+                                const int col = n - (is_v ? kv.v_off : kv.k_off);
+                                if (col < kv.width) {
+                                    const int hh = col / kv.dh, cc = col - hh * kv.dh;
+                                    __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(is_v ? kv.Vc : kv.Kc);
+                                    base[(((size_t)kv_blk * kv.Hkv + hh) * kv.BT + kv_row) * kv.dh + cc] = __float2bfloat16_rn(x);
+                                }
+                            }
                         }
                     }
                 }
@@ -223,7 +262,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
 
 template <int BN, int STAGES, typename OT>
 int launch_tc(const void* X, const void* W, const float* bias, const float* residual, void* Y, int M, int N, int K,
-              int ldx, int ldy, int act, int* dev_err, cudaStream_t stream) {
+              int ldx, int ldy, int act, const TcKvScatter& kv, int* dev_err, cudaStream_t stream) {
     CUtensorMap tx, tw;
     int st = vlrf_make_tmap_bf16(X, M, K, ldx, TC_BM, TC_BK, &tx);
     if (st != VLRF_OK) return st;
@@ -239,7 +278,7 @@ int launch_tc(const void* X, const void* W, const float* bias, const float* resi
     }
     dim3 grid((N + BN - 1) / BN, (M + TC_BM - 1) / TC_BM);
     cudaError_t e = launch_chained(kern, grid, dim3(TC_THREADS), smem, stream, tx, tw, bias, residual, (OT*)Y, M, N, K, ldy,
-                                   act, dev_err);
+                                   act, kv, dev_err);
     if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "gemm_tcgen05: %s", cudaGetErrorString(e));
     return vlrf_check_launch("gemm_tcgen05");
 }
@@ -251,21 +290,32 @@ extern "C" int vlrf_gemm_tcgen05_takes(int M, int N, int K, int ldx) {
 }
 
 extern "C" int vlrf_gemm_tcgen05(const void* X, const void* W, const float* bias, const float* residual, void* Y,
-                                 int M, int N, int K, int ldx, int ldy, int out_dtype, int act, int* dev_err,
+                                 int M, int N, int K, int ldx, int ldy, int out_dtype, int act,
+                                 // optional scatter of K/V columns into the cache (Kc == nullptr: none)
+                                 void* Kc, void* Vc, const int* block_table, int max_blocks, const int* tok_slot,
+                                 const int* tok_pos, int k_off, int v_off, int Hkv, int dh, int BT, int* dev_err,
                                  cudaStream_t stream) {
     VLRF_REQUIRE(vlrf_gemm_tcgen05_takes(M, N, K, ldx), "gemm_tcgen05: M=%d N=%d K=%d ldx=%d: K and the row stride must be multiples of 8", M, N, K, ldx);
     VLRF_REQUIRE(ldy >= N && act >= 0 && act <= 2 && dev_err != nullptr, "gemm_tcgen05: bad arguments");
     VLRF_REQUIRE((M + TC_BM - 1) / TC_BM <= 65535, "gemm_tcgen05: too many row tiles");
+    TcKvScatter kv{};
+    if (Kc != nullptr) {
+        VLRF_REQUIRE(Vc && block_table && tok_slot && tok_pos && Hkv > 0 && dh > 0 && BT > 0 && max_blocks > 0,
+                     "gemm_tcgen05: incomplete cache scatter arguments");
+        VLRF_REQUIRE(out_dtype == VLRF_BF16 && dh % 8 == 0 && k_off % 8 == 0 && v_off % 8 == 0,
+                     "gemm_tcgen05: the cache scatter writes bfloat16 heads of a multiple of 8 columns");
+        kv = TcKvScatter{Kc, Vc, block_table, tok_slot, tok_pos, max_blocks, k_off, v_off, Hkv * dh, dh, Hkv, BT};
+    }
     // narrower tiles when wide ones would leave most SMs idle
     const long long tiles128 = (long long)((N + 127) / 128) * ((M + 127) / 128);
     const bool narrow = tiles128 < 120;
     if (out_dtype == VLRF_BF16) {
-        if (narrow) return launch_tc<64, 4, __nv_bfloat16>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, dev_err, stream);
-        return launch_tc<128, 3, __nv_bfloat16>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, dev_err, stream);
+        if (narrow) return launch_tc<64, 4, __nv_bfloat16>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, kv, dev_err, stream);
+        return launch_tc<128, 3, __nv_bfloat16>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, kv, dev_err, stream);
     }
     if (out_dtype == VLRF_F32) {
-        if (narrow) return launch_tc<64, 4, float>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, dev_err, stream);
-        return launch_tc<128, 3, float>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, dev_err, stream);
+        if (narrow) return launch_tc<64, 4, float>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, kv, dev_err, stream);
+        return launch_tc<128, 3, float>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, kv, dev_err, stream);
     }
     return vlrf_fail(VLRF_ERR_INVALID_ARG, "gemm_tcgen05: unknown output dtype %d", out_dtype);
 }

@@ -72,9 +72,11 @@ def layernorm(x, gamma, beta, eps: float, out, rows=None) -> None:
          float(eps), _stream())
 
 
-def linear(x, w, bias, out, *, act=None, residual=None, rows: int | None = None) -> None:
+def linear(x, w, bias, out, *, act=None, residual=None, rows: int | None = None, kv_scatter=None) -> bool:
     """out = act(x · wᵀ + bias) (+ residual).  x [M,K], w [N,K] (same dtype), bias/residual float32,
-    out [M,N] float32 or bfloat16.  `rows` limits M to the first rows of x/out/residual."""
+    out [M,N] float32 or bfloat16.  `rows` limits M to the first rows of x/out/residual.  `kv_scatter`
+    (see linear_layernorm) asks the kernel to write K/V columns into a cache as well; the return value
+    says whether it did (only the tensor-core kernels can)."""
     _dev(x, "x"); _dev(w, "w", x.dtype); _dev(out, "out")
     M = x.shape[0] if rows is None else rows
     K = x.shape[1]
@@ -91,7 +93,7 @@ def linear(x, w, bias, out, *, act=None, residual=None, rows: int | None = None)
             raise KernelError("linear: residual does not match")
     if x.dtype == torch.float32 and out.dtype != torch.float32:
         raise KernelError("linear: float32 input gives float32 output")
-    _linear_dispatch(x, w, bias, out, ACT[act], residual, M, N, K)
+    return _linear_dispatch(x, w, bias, out, ACT[act], residual, M, N, K, kv_scatter)
 
 
 _SM_COUNT = None
@@ -138,19 +140,37 @@ def sm_count() -> int:
     return _SM_COUNT
 
 
-def _linear_dispatch(x, w, bias, out, act, residual, M, N, K) -> None:
+def _kv_args(kv_scatter, N: int) -> list:
+    if kv_scatter is None:
+        return [0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0]
+    kc, vc, table, tok_slot, tok_pos, k_off, v_off, hkv, dh = kv_scatter
+    _dev(kc, "k_cache", torch.bfloat16); _dev(vc, "v_cache", torch.bfloat16)
+    _dev(table, "block_table", torch.int32); _dev(tok_slot, "tok_slot", torch.int32)
+    _dev(tok_pos, "tok_pos", torch.int32)
+    if kc.shape[1] != hkv or kc.shape[3] != dh or max(k_off, v_off) + hkv * dh > N:
+        raise KernelError("cache scatter does not match the projection")
+    return [_ptr(kc), _ptr(vc), _ptr(table), table.shape[1], _ptr(tok_slot), _ptr(tok_pos), k_off, v_off, hkv, dh,
+            kc.shape[2]]
+
+
+def _linear_dispatch(x, w, bias, out, act, residual, M, N, K, kv_scatter=None) -> bool:
+    bf16_out = out.dtype == torch.bfloat16
     if x.dtype == torch.bfloat16 and M <= SKINNY_MAX_ROWS and K % 32 == 0:
         # few rows: the product is bound by streaming w once
+        scatter = kv_scatter is not None and bf16_out
         call("vlrf_gemm_skinny", _ptr(x), 0, _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), dtype_code(out.dtype),
-             M, N, K, K, N, act, 0, 0, 0.0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, sm_count(), _ptr(_dev_err()), _stream())
-        return
+             M, N, K, K, N, act, 0, 0, 0.0, *_kv_args(kv_scatter if scatter else None, N), sm_count(), _ptr(_dev_err()),
+             _stream())
+        return scatter
     if x.dtype == torch.bfloat16 and K % 8 == 0 and USE_TCGEN05:
         # many rows: the tensor-core kernel (tcgen05, accumulator in tensor memory)
+        scatter = kv_scatter is not None and bf16_out and kv_scatter[8] % 8 == 0 and kv_scatter[5] % 8 == 0
         call("vlrf_gemm_tcgen05", _ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), M, N, K, K, N,
-             dtype_code(out.dtype), act, _ptr(_dev_err()), _stream())
-        return
+             dtype_code(out.dtype), act, *_kv_args(kv_scatter if scatter else None, N), _ptr(_dev_err()), _stream())
+        return scatter
     call("vlrf_gemm_simt", _ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), M, N, K, K, N,
          dtype_code(x.dtype), dtype_code(out.dtype), act, _stream())
+    return False
 
 
 def can_fuse_layernorm(n_rows: int, width: int, w_dtype: torch.dtype) -> bool:
@@ -176,16 +196,7 @@ def linear_layernorm(x, gamma, beta, eps: float, w, bias, out, *, act=None, rows
         raise KernelError("linear_layernorm: sizes do not match")
     if bias is not None:
         _dev(bias, "bias", torch.float32)
-    kv = [0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0]
-    if kv_scatter is not None:
-        kc, vc, table, tok_slot, tok_pos, k_off, v_off, hkv, dh = kv_scatter
-        _dev(kc, "k_cache", torch.bfloat16); _dev(vc, "v_cache", torch.bfloat16)
-        _dev(table, "block_table", torch.int32); _dev(tok_slot, "tok_slot", torch.int32)
-        _dev(tok_pos, "tok_pos", torch.int32)
-        if kc.shape[1] != hkv or kc.shape[3] != dh or max(k_off, v_off) + hkv * dh > N:
-            raise KernelError("linear_layernorm: cache scatter does not match")
-        kv = [_ptr(kc), _ptr(vc), _ptr(table), table.shape[1], _ptr(tok_slot), _ptr(tok_pos), k_off, v_off, hkv, dh,
-              kc.shape[2]]
+    kv = _kv_args(kv_scatter, N)
     call("vlrf_gemm_skinny", _ptr(x), 1, _ptr(w), _ptr(bias), 0, _ptr(out), dtype_code(out.dtype), M, N, K, K, N,
          ACT[act], _ptr(gamma), _ptr(beta), float(eps), *kv, sm_count(), _ptr(_dev_err()), _stream())
 

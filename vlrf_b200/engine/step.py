@@ -50,6 +50,14 @@ class Engine:
         self._meta_dev = None
         self._meta_copied = None   # event: the last copy out of the pinned staging buffer has finished
         self.steps_run = 0
+        # Steps of a shape seen before are replayed from a captured CUDA graph: the step's integer tables
+        # live at fixed device addresses, so only their contents change from step to step.
+        self.capture_repeated_steps = True
+        self._graphs: dict = {}        # (tokens, sequences, longest run, wanted rows) -> (graph, logits)
+        self._seen: dict = {}
+        self._graph_generation = -1
+        from ..csrc import ops
+        ops._dev_err()             # exists before any capture
 
     # -- sequences ----------------------------------------------------------------------------
     def start_sequence(self) -> int:
@@ -68,6 +76,7 @@ class Engine:
             self._meta_host = torch.empty(cap, dtype=torch.int32, pin_memory=True)
             self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
             self._meta_cap = cap
+            self._graphs.clear()       # captured steps point into the old tables
         return self._meta_host, self._meta_dev
 
     def plan(self, entries: list) -> dict:
@@ -149,10 +158,38 @@ class Engine:
             max_context=max(a + b for a, b in zip(p["pos0"], p["lens"])), logit_rows=views[6],
             n_logit_rows=n_want, act_dtype=self.model.act_dtype, dev_err=self.dev_err, ws=self.ws,
             host_seq_slots=[e.slot for e in entries], host_seq_lens=p["lens"], host_seq_pos0=p["pos0"])
-        logits = self.model.forward(ctx, self.cache)
+        logits = self._forward(ctx, (T, B, ctx.max_new, n_want))
         for e in entries:
             self.cache.advance(e.slot, len(e.tokens))
         self.steps_run += 1
+        return logits
+
+    def _forward(self, ctx: StepContext, signature) -> torch.Tensor:
+        """Run the model on the step, replaying a captured graph when a step of the same shape ran before."""
+        if not self.capture_repeated_steps or ctx.max_new == 1:
+            return self.model.forward(ctx, self.cache)     # single-token steps have DecodeSession's graph
+        if self._graph_generation != self.ws.generation:
+            self._graphs.clear()                           # scratch moved: captured addresses are stale
+            self._graph_generation = self.ws.generation
+        hit = self._graphs.get(signature)
+        if hit is not None:
+            hit[0].replay()
+            return hit[1]
+        n = self._seen.get(signature, 0)
+        self._seen[signature] = n + 1
+        if n == 0 or len(self._graphs) >= 16:
+            logits = self.model.forward(ctx, self.cache)   # first time: plain launches (they size the scratch)
+            self._graph_generation = self.ws.generation
+            return logits
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(ctx, self.cache)
+        if self.ws.generation != self._graph_generation:   # the capture itself had to allocate: do not keep it
+            self._graph_generation = self.ws.generation
+            return self.model.forward(ctx, self.cache)
+        self._graphs[signature] = (graph, logits)
+        graph.replay()
         return logits
 
     def check_device_errors(self) -> None:

@@ -21,6 +21,7 @@ class Workspace:
         self.device = torch.device(device)
         self._bufs: dict[str, torch.Tensor] = {}
         self.frozen = False  # set while a captured graph depends on the addresses
+        self.generation = 0  # counts (re)allocations: captured steps are valid for one generation only
 
     def get(self, name: str, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
         n = rows * cols
@@ -33,6 +34,7 @@ class Workspace:
                 cap = max(cap, 2 * buf.numel())
             buf = torch.empty(cap, dtype=dtype, device=self.device)
             self._bufs[name] = buf
+            self.generation += 1
         return buf[:n].view(rows, cols)
 
     def get_zeroed(self, name: str, n: int, dtype: torch.dtype) -> torch.Tensor:
@@ -44,6 +46,7 @@ class Workspace:
                 raise RuntimeError(f"workspace '{name}' would have to grow while a captured step uses it")
             buf = torch.zeros(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[name] = buf
+            self.generation += 1
         return buf[:n]
 
     def bytes(self) -> int:

@@ -77,7 +77,11 @@ class CausalSelfAttention:
         else:
             if h is None:
                 h = norm(x, ctx.ws.get("block_normed", T, x.shape[1], ctx.act_dtype))
-            ops.linear(h, self.w_qkv, self.b_qkv, qkv)
+            scatter = None
+            if writes_cache:
+                scatter = (view.k, view.v, view.block_table, ctx.tok_slot, ctx.tok_pos, self.k_off, self.v_off,
+                           self.n_kv_heads, self.head_dim)
+            appended = ops.linear(h, self.w_qkv, self.b_qkv, qkv, kv_scatter=scatter)   # the epilogue writes the cache if it can
         if writes_cache and not appended:
             ops.kv_append(qkv, self.k_off, self.v_off, view.k, view.v, view.block_table, ctx.tok_slot,
                           ctx.tok_pos, T, self.n_kv_heads, self.head_dim, ctx.dev_err)
