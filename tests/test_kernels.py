@@ -76,6 +76,8 @@ GEMM_SHAPES = [(1, 53, 19), (37, 53, 19), (64, 64, 16), (130, 200, 72), (3, 1000
                # few rows and K a multiple of 32: the weight-streaming kernel of the decode step
                (8, 2304, 768), (64, 200, 96), (17, 50, 64), (33, 1000, 320), (1, 768, 3072), (9, 17, 32),
                # many rows and K a multiple of 8: the tcgen05 kernel (tails in M, N and K)
+               # few rows, very many columns: the tcgen05 kernel with the operands' roles exchanged
+               (1, 16500, 64), (8, 20000, 96), (17, 16385, 128), (40, 16400, 72), (64, 17000, 64),
                (65, 64, 64), (128, 128, 128), (300, 768, 768), (1000, 200, 1600), (129, 1000, 72), (2048, 320, 96)]
 
 

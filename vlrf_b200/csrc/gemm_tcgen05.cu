@@ -95,7 +95,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr));
 }
 
-template <int BN, int STAGES, typename OT>
+// SWAP: the roles of the two matrices are exchanged — the 128-row operand is W (tmap_x then describes W),
+// the BN-row operand is X with its few rows — so that a product with few rows still fills the 128-row MMA.
+// The accumulator then holds Yᵀ: lane = output column n, TMEM column = row m; the epilogue writes Y[m][n],
+// for each m 32 consecutive n per warp.
+template <int BN, int STAGES, typename OT, bool SWAP>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                     const float* __restrict__ bias, const float* residual, OT* Y, int M, int N, int K, int ldy,
@@ -103,6 +107,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     extern __shared__ unsigned char tc_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
+    constexpr int TMEM_COLS = BN < 32 ? 32 : BN;       // tensor memory is allocated in powers of two from 32 columns
     unsigned char* a_tiles = smem;                                   // [STAGES][128][128 B]
     unsigned char* b_tiles = smem + (size_t)STAGES * A_BYTES;        // [STAGES][BN][128 B]
     uint64_t* full = reinterpret_cast<uint64_t*>(b_tiles + (size_t)STAGES * B_BYTES);
@@ -112,7 +117,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
+    // not swapped: m0 = first row of X, n0 = first row of W.  Swapped: m0 = first row of W (output column), n0 = 0.
+    const int m0 = SWAP ? blockIdx.x * TC_BM : blockIdx.y * TC_BM, n0 = SWAP ? 0 : blockIdx.x * BN;
     const int n_kb = (K + TC_BK - 1) / TC_BK;
 
     if (threadIdx.x == 0) {
@@ -124,7 +130,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     if (warp == 4) {
         if (lane == 0) { tma_prefetch_descriptor(&tmap_x); tma_prefetch_descriptor(&tmap_w); }
         __syncwarp();
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tsm(tmem_slot)), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tsm(tmem_slot)), "r"((uint32_t)TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -178,7 +184,34 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 if (kv_blk < 0) atomicOr(dev_err, VLRF_DEVERR_NO_BLOCK);
             }
         }
-        if (have && !*s_abort) {
+        if (SWAP) {
+            if (have && !*s_abort) {
+                const int n = m0 + warp * 32 + lane;          // this thread's output column = row of W
+                const float bv = (bias && n < N) ? bias[n] : 0.f;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    uint32_t r[16];
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+                        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                        : "r"(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0));
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (n < N) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int m = c0 + j;
+                            if (m < M) {
+                                float x = apply_act_rt(__uint_as_float(r[j]) + bv, act);
+                                if (residual) x += residual[(size_t)m * ldy + n];
+                                ElemIO<OT>::store(Y + (size_t)m * ldy + n, x);
+                            }
+                        }
+                    }
+                }
+            }
+        } else if (have && !*s_abort) {
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
@@ -255,21 +288,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (warp == 4) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
     }
     if (threadIdx.x == 0 && *s_abort) atomicOr(dev_err, VLRF_DEVERR_WAIT_TIMEOUT);
 }
 
-template <int BN, int STAGES, typename OT>
+template <int BN, int STAGES, typename OT, bool SWAP = false>
 int launch_tc(const void* X, const void* W, const float* bias, const float* residual, void* Y, int M, int N, int K,
               int ldx, int ldy, int act, const TcKvScatter& kv, int* dev_err, cudaStream_t stream) {
-    CUtensorMap tx, tw;
-    int st = vlrf_make_tmap_bf16(X, M, K, ldx, TC_BM, TC_BK, &tx);
+    CUtensorMap tx, tw;      // tx: the 128-row operand, tw: the BN-row operand
+    int st = SWAP ? vlrf_make_tmap_bf16(W, N, K, K, TC_BM, TC_BK, &tx) : vlrf_make_tmap_bf16(X, M, K, ldx, TC_BM, TC_BK, &tx);
     if (st != VLRF_OK) return st;
-    st = vlrf_make_tmap_bf16(W, N, K, K, BN, TC_BK, &tw);
+    st = SWAP ? vlrf_make_tmap_bf16(X, M, K, ldx, BN, TC_BK, &tw) : vlrf_make_tmap_bf16(W, N, K, K, BN, TC_BK, &tw);
     if (st != VLRF_OK) return st;
     const size_t smem = 1024 + (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 1) * 8 + 16;
-    auto kern = gemm_tcgen05_kernel<BN, STAGES, OT>;
+    auto kern = gemm_tcgen05_kernel<BN, STAGES, OT, SWAP>;
     static bool raised = false;
     if (!raised) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -277,6 +310,7 @@ int launch_tc(const void* X, const void* W, const float* bias, const float* resi
         raised = true;
     }
     dim3 grid((N + BN - 1) / BN, (M + TC_BM - 1) / TC_BM);
+    if (SWAP) grid = dim3((N + TC_BM - 1) / TC_BM, 1);
     cudaError_t e = launch_chained(kern, grid, dim3(TC_THREADS), smem, stream, tx, tw, bias, residual, (OT*)Y, M, N, K, ldy,
                                    act, kv, dev_err);
     if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "gemm_tcgen05: %s", cudaGetErrorString(e));
@@ -305,6 +339,16 @@ extern "C" int vlrf_gemm_tcgen05(const void* X, const void* W, const float* bias
         VLRF_REQUIRE(out_dtype == VLRF_BF16 && dh % 8 == 0 && k_off % 8 == 0 && v_off % 8 == 0,
                      "gemm_tcgen05: the cache scatter writes bfloat16 heads of a multiple of 8 columns");
         kv = TcKvScatter{Kc, Vc, block_table, tok_slot, tok_pos, max_blocks, k_off, v_off, Hkv * dh, dh, Hkv, BT};
+    }
+    if (M <= 64 && Kc == nullptr) {
+        // few rows: W fills the 128-row operand, the rows of X are the MMA's N
+#define SWAPPED(BNV) (out_dtype == VLRF_BF16 ? launch_tc<BNV, 4, __nv_bfloat16, true>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, kv, dev_err, stream) \
+                                             : launch_tc<BNV, 4, float, true>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, kv, dev_err, stream))
+        VLRF_REQUIRE(out_dtype == VLRF_BF16 || out_dtype == VLRF_F32, "gemm_tcgen05: unknown output dtype %d", out_dtype);
+        if (M <= 16) return SWAPPED(16);
+        if (M <= 32) return SWAPPED(32);
+        return SWAPPED(64);
+#undef SWAPPED
     }
     // narrower tiles when wide ones would leave most SMs idle
     const long long tiles128 = (long long)((N + 127) / 128) * ((M + 127) / 128);

@@ -100,6 +100,7 @@ _SM_COUNT = None
 USE_TCGEN05 = True
 SKINNY_MAX_ROWS = 64
 FUSED_NORM_MAX_ROWS = 16
+SWAPPED_MIN_COLUMNS = 16384
 _DEV_ERR = None
 
 
@@ -155,6 +156,13 @@ def _kv_args(kv_scatter, N: int) -> list:
 
 def _linear_dispatch(x, w, bias, out, act, residual, M, N, K, kv_scatter=None) -> bool:
     bf16_out = out.dtype == torch.bfloat16
+    if (x.dtype == torch.bfloat16 and M <= SKINNY_MAX_ROWS and K % 8 == 0 and USE_TCGEN05 and kv_scatter is None
+            and N >= SWAPPED_MIN_COLUMNS):
+        # few rows, very many columns (the head over the vocabulary): enough 128-row tiles of w to fill the GPU,
+        # so w becomes the 128-row operand of the tcgen05 kernel and the rows of x its N
+        call("vlrf_gemm_tcgen05", _ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), M, N, K, K, N,
+             dtype_code(out.dtype), act, *_kv_args(None, N), _ptr(_dev_err()), _stream())
+        return False
     if x.dtype == torch.bfloat16 and M <= SKINNY_MAX_ROWS and K % 32 == 0:
         # few rows: the product is bound by streaming w once
         scatter = kv_scatter is not None and bf16_out
