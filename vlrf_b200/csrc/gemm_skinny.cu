@@ -434,17 +434,21 @@ extern "C" int vlrf_gemm_skinny(const void* X, int x_is_f32_ln, const void* W, c
         VLRF_REQUIRE(xmode != 2, "gemm_skinny: fused LayerNorm does not fit");
         xmode = 0;
     }
-    // 8·CG rows of W per group: the choice that keeps most SMs busy over whole rounds; larger groups on ties
+    // 8·CG rows of W per group.  These products are short: a CTA's time is a fixed latency (request, HBM
+    // round trip, reduction, epilogue) plus its slab's bytes over the bandwidth it gets, times the rounds it
+    // has to make.  The estimate below picks the group size with the least of that.
     int CG = 1;
-    double best = -1.0;
+    double best = 1e30;
     for (int cg = SK_WARPS; cg >= 1; cg /= 2) {
-        if (cg > 1 && (size_t)8 * cg * tiling(K).n_tiles * 128 > 64 * 1024) continue;
+        const double slab = (double)8 * cg * tiling(K).n_tiles * 128;
+        if (cg > 1 && slab > 64 * 1024) continue;
         if (smem_bytes(mt16, M, xmode, K, cg, 1) > SMEM_BUDGET) continue;
         const int groups = (N + 8 * cg - 1) / (8 * cg);
         const int ctas = groups < sm_count ? groups : sm_count;
         const int rounds = (groups + ctas - 1) / ctas;
-        const double eff = (double)groups / ((double)rounds * sm_count);
-        if (eff > best + 0.05) { best = eff; CG = cg; }
+        const double gbs = 6500.0 / ctas < 100.0 ? 6500.0 / ctas : 100.0;      // GB/s a CTA gets
+        const double cost = rounds * (1.2 + slab / (gbs * 1e3));               // microseconds
+        if (cost < best - 1e-9) { best = cost; CG = cg; }
     }
     const int groups = (N + 8 * CG - 1) / (8 * CG);
     const int grid = groups < sm_count ? groups : sm_count;
