@@ -254,6 +254,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the preset (named in config)")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                    help="measure one part only and print a short line (for profiling runs); the full line needs 'all'")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -272,6 +274,15 @@ def main() -> int:
     full_layers = load_preset(args.preset)["n_layer"]
     with tempfile.TemporaryDirectory(prefix="vlrf_b200_bench_") as tmp:
         model_dir = make_model_dir(args.preset, args.layers, tmp)
+        if args.only == "decode":
+            dec = decode_device(model_dir, args.batch, args.steps, warmup)
+            print(json.dumps({"only": "decode", "batch": args.batch, "tok_s": round(dec["tok_s"], 1),
+                              "ms_per_step": round(dec["ms_per_step"], 4), "kernels_per_step": dec["kernels_per_step"]}))
+            return 0
+        if args.only == "prefill":
+            pre = prefill_device(model_dir, reps=max(1, args.steps))
+            print(json.dumps({"only": "prefill", "tokens": pre["tokens"], "ms": round(pre["ms"], 4)}))
+            return 0
         dec = decode_device(model_dir, args.batch, args.steps, warmup)
         e2e = decode_e2e(model_dir, args.batch, dec["steps"], warmup)
         pre = prefill_device(model_dir)

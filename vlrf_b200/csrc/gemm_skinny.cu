@@ -89,6 +89,12 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
+    // The MMA fixes which lane holds which row of a fragment, but not which row of the tile that is: fragment
+    // row g is tile row pg = g/2 + 4·(g mod 2).  Then the eight lanes that read shared memory together
+    // (two fragment rows × four 16-byte pieces) touch tile rows that differ in bit 2, and under the
+    // 128-byte swizzle their pieces fall into eight different bank groups.  Fragment column c of the
+    // result is tile row π(c) of W in the same way: columns 2t and 2t+1 are rows t and t+4.
+    const int pg = (g >> 1) | ((g & 1) << 2);
     const int rows_w = 8 * CG;
     constexpr int XR = 16 * MT16;                      // rows of the staged X tile
     const Tiling tl = tiling(K);
@@ -200,7 +206,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         for (int mt = 0; mt < MT16; ++mt)
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
-                const int m = mt * 16 + g + hh * 8;
+                const int m = mt * 16 + pg + hh * 8;
                 kv_blk[mt][hh] = -2;                   // −2: nothing to write for this row
                 kv_off[mt][hh] = 0;
                 if (m < M) {
@@ -226,14 +232,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             for (int mt = 0; mt < MT16; ++mt)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const int m = mt * 16 + g + ((j & 2) ? 8 : 0);
-                    const int n = n0 + 2 * t + (j & 1);
+                    const int m = mt * 16 + pg + ((j & 2) ? 8 : 0);
+                    const int n = n0 + t + 4 * (j & 1);
                     pre[mt][j] = (n < N && m < M && residual) ? residual[(size_t)m * ldy + n] : 0.f;
                 }
             if (bias) {
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
-                    if (n0 + 2 * t + j < N) pre_bias[j] = bias[n0 + 2 * t + j];
+                    if (n0 + t + 4 * j < N) pre_bias[j] = bias[n0 + t + 4 * j];
             }
         }
 
@@ -244,7 +250,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
         // A warp takes the 64-wide k tiles kpart, kpart + wpg, … of its 8 columns.  Everything that does not
         // change from tile to tile (the swizzled places of this lane's pieces) is computed once.
-        const int wrow = sub * 8 + g;
+        const int wrow = sub * 8 + pg;
         const unsigned char* wp = ws + (size_t)stage * stage_bytes + (size_t)kpart * tile_bytes;
         const int w_off0 = swz(wrow, t), w_off1 = swz(wrow, 4 + t);
         const unsigned char* xp = xs + (size_t)kpart * XR * 128;
@@ -268,8 +274,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             for (int mt = 0; mt < MT16; ++mt) {
                 uint4 lo0, hi0, lo1 = make_uint4(0, 0, 0, 0), hi1 = make_uint4(0, 0, 0, 0);
                 if (XMODE == 0) {
-                    const __nv_bfloat16* r_lo = Xb + (size_t)min(mt * 16 + g, M - 1) * ldx + tile * 64 + t * 8;
-                    const __nv_bfloat16* r_hi = Xb + (size_t)min(mt * 16 + g + 8, M - 1) * ldx + tile * 64 + t * 8;
+                    const __nv_bfloat16* r_lo = Xb + (size_t)min(mt * 16 + pg, M - 1) * ldx + tile * 64 + t * 8;
+                    const __nv_bfloat16* r_hi = Xb + (size_t)min(mt * 16 + pg + 8, M - 1) * ldx + tile * 64 + t * 8;
                     lo0 = __ldg(reinterpret_cast<const uint4*>(r_lo));
                     hi0 = __ldg(reinterpret_cast<const uint4*>(r_hi));
                     if (second_half) {
@@ -277,11 +283,11 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                         hi1 = __ldg(reinterpret_cast<const uint4*>(r_hi + 32));
                     }
                 } else {
-                    lo0 = *reinterpret_cast<const uint4*>(xp + swz(mt * 16 + g, t));
-                    hi0 = *reinterpret_cast<const uint4*>(xp + swz(mt * 16 + g + 8, t));
+                    lo0 = *reinterpret_cast<const uint4*>(xp + swz(mt * 16 + pg, t));
+                    hi0 = *reinterpret_cast<const uint4*>(xp + swz(mt * 16 + pg + 8, t));
                     if (second_half) {
-                        lo1 = *reinterpret_cast<const uint4*>(xp + swz(mt * 16 + g, 4 + t));
-                        hi1 = *reinterpret_cast<const uint4*>(xp + swz(mt * 16 + g + 8, 4 + t));
+                        lo1 = *reinterpret_cast<const uint4*>(xp + swz(mt * 16 + pg, 4 + t));
+                        hi1 = *reinterpret_cast<const uint4*>(xp + swz(mt * 16 + pg + 8, 4 + t));
                     }
                 }
                 mma_bf16(acc[mt], lo0.x, hi0.x, lo0.y, hi0.y, w0.x, w0.y);
@@ -315,13 +321,13 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                 for (int j = 0; j < 4; ++j) acc[mt][j] += other[(mt * 4 + j) * 32 + lane];
         }
 
-        // epilogue: the thread holds rows mt*16 + g, +8 and columns n0 + 2t, 2t+1
+        // epilogue: the thread holds rows mt*16 + pg, +8 and columns n0 + t, n0 + t + 4
 #pragma unroll
         for (int mt = 0; mt < MT16; ++mt) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const int m = mt * 16 + g + ((j & 2) ? 8 : 0);
-                const int n = n0 + 2 * t + (j & 1);
+                const int m = mt * 16 + pg + ((j & 2) ? 8 : 0);
+                const int n = n0 + t + 4 * (j & 1);
                 if (n >= N || m >= M) continue;
                 float v = acc[mt][j] + pre_bias[j & 1];
                 v = apply_act_rt(v, act) + pre[mt][j];
