@@ -1,30 +1,44 @@
 // Y[M,N] = act(X[M,K] · W[N,K]^T + bias) (+ residual) on the 5th-generation tensor cores (tcgen05), for
 // the many-row products of a prompt step.  bfloat16 operands, float32 accumulation in tensor memory.
 //
-// One CTA computes a 128 × BN tile of Y.  Its six warps have fixed jobs:
-//   warp 4  producer: for every 64-wide k block it waits until the ring stage is free, announces the
+// A persistent CTA computes 128 × BN tiles of Y, one after another.  Its ten warps have fixed jobs:
+//   warp 8  producer: for every 64-wide k block it waits until the ring stage is free, announces the
 //           bytes on the stage's "full" mbarrier and issues two tiled TMA loads (128 rows of X, BN rows of
 //           W; 128-byte swizzle; rows and columns outside the matrices read as zeros);
-//   warp 5  one elected thread issues the MMAs: four `tcgen05.mma.cta_group::1.kind::f16` of shape
+//   warp 9  one elected thread issues the MMAs: four `tcgen05.mma.cta_group::1.kind::f16` of shape
 //           128 × BN × 16 per k block, operands straight from shared memory through matrix descriptors,
-//           accumulator in tensor memory; `tcgen05.commit` frees the stage when those MMAs have read it,
-//           and after the last k block signals the accumulator as complete;
-//   warps 0-3  epilogue: each reads its 32 lanes of the accumulator with `tcgen05.ld`, adds bias, applies
+//           accumulator in tensor memory (two accumulators alternate, so a tile's epilogue overlaps the
+//           next tile's MMAs); `tcgen05.commit` frees the stage when those MMAs have read it, and after the
+//           last k block signals the accumulator as complete;
+//   warps 0-7  epilogue: two warps share 32 lanes of the accumulator and take half of its columns each;
+//           they read them with `tcgen05.ld` (bias and residual are fetched while that is in flight), add bias, apply
 //           GELU, adds the float32 residual (reference: include/model/feedforward.hpp:54-76,
 //           include/model/transformer_block.hpp:153,158) and stores bfloat16 or float32 rows.
-// Tensor memory (BN columns) is allocated by warp 4 and freed by it at the end on every path.  Every
+// Tensor memory (2·BN columns) is allocated by warp 8 and freed by it at the end on every path.  Every
 // mbarrier wait is bounded; a wait that gives up sets a bit in the device error word, and the CTA still
 // frees its tensor memory and returns.
 //
 // The product is the reference's linear(x, W) = x · Wᵀ (include/model/compute.hpp:64-68).
 #include "common.cuh"
 #include "tma.cuh"
+#include <cstdlib>
 
 namespace {
 
+int sm_count_cached() {                          // asked once: the query is slow next to a launch
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0, v = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+        sms = v > 0 ? v : 148;
+    }
+    return sms;
+}
+
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 64;
-constexpr int TC_THREADS = 192;
+constexpr int TC_THREADS = 320;      // warps 0-7: epilogue (two per 32 accumulator lanes), 8: producer, 9: MMA issue
 constexpr uint32_t TC_WAIT_LIMIT = 1u << 21;
 
 // Optional scatter of the K and V columns of a fused q/k/v projection into one layer's paged cache
@@ -51,13 +65,6 @@ __device__ __forceinline__ bool tbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "=r"(ok) : "r"(tsm(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-// false if the wait gave up
-__device__ __forceinline__ bool tbar_wait(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i)
-        if (tbar_try_wait(bar, parity)) return true;
-    return false;
-}
-
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16) written by TMA with
 // the 128-byte swizzle: 8-row groups are 1024 bytes apart; version 1 (Blackwell); layout type 2 (128B swizzle).
 __device__ __forceinline__ uint64_t umma_desc_k128(const void* tile) {
@@ -83,6 +90,10 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tsm(bar)) : "memory");
 }
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -95,10 +106,26 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr));
 }
 
+// a wait that also gives up when another role of the CTA has already given up
+__device__ __forceinline__ bool tbar_wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i) {
+        if (tbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u && *abort_flag) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void tbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tsm(bar)) : "memory");
+}
+
 // SWAP: the roles of the two matrices are exchanged — the 128-row operand is W (tmap_x then describes W),
 // the BN-row operand is X with its few rows — so that a product with few rows still fills the 128-row MMA.
 // The accumulator then holds Yᵀ: lane = output column n, TMEM column = row m; the epilogue writes Y[m][n],
 // for each m 32 consecutive n per warp.
+//
+// The CTA is persistent: it takes the output tiles blockIdx.x, + gridDim.x, …  Tensor memory holds two
+// accumulators, so the epilogue of one tile runs while the MMAs of the next fill the other, and the
+// producer keeps the shared-memory ring full across tile boundaries.
 template <int BN, int STAGES, typename OT, bool SWAP>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
@@ -107,27 +134,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     extern __shared__ unsigned char tc_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
-    constexpr int TMEM_COLS = BN < 32 ? 32 : BN;       // tensor memory is allocated in powers of two from 32 columns
+    constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;     // two accumulators; allocation is a power of two ≥ 32
     unsigned char* a_tiles = smem;                                   // [STAGES][128][128 B]
     unsigned char* b_tiles = smem + (size_t)STAGES * A_BYTES;        // [STAGES][BN][128 B]
     uint64_t* full = reinterpret_cast<uint64_t*>(b_tiles + (size_t)STAGES * B_BYTES);
     uint64_t* empty = full + STAGES;
-    uint64_t* acc_done = empty + STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
+    uint64_t* acc_full = empty + STAGES;                             // [2] MMAs of a tile are complete
+    uint64_t* acc_empty = acc_full + 2;                              // [2] the epilogue has read the accumulator
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // not swapped: m0 = first row of X, n0 = first row of W.  Swapped: m0 = first row of W (output column), n0 = 0.
-    const int m0 = SWAP ? blockIdx.x * TC_BM : blockIdx.y * TC_BM, n0 = SWAP ? 0 : blockIdx.x * BN;
     const int n_kb = (K + TC_BK - 1) / TC_BK;
+    // tiles: not swapped — 128 rows of X by BN rows of W, neighbours in N first (they share the rows of X in
+    // L2); swapped — 128 rows of W by all rows of X
+    const int tiles_n = SWAP ? 1 : (N + BN - 1) / BN;
+    const int n_tiles = SWAP ? (N + TC_BM - 1) / TC_BM : tiles_n * ((M + TC_BM - 1) / TC_BM);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { tbar_init(&full[s], 1); tbar_init(&empty[s], 1); }
-        tbar_init(acc_done, 1);
+        for (int b = 0; b < 2; ++b) { tbar_init(&acc_full[b], 1); tbar_init(&acc_empty[b], 8); }
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 4) {
+    if (warp == 8) {
         if (lane == 0) { tma_prefetch_descriptor(&tmap_x); tma_prefetch_descriptor(&tmap_w); }
         __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tsm(tmem_slot)), "r"((uint32_t)TMEM_COLS) : "memory");
@@ -140,142 +170,185 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     pdl_launch_dependents();
     pdl_wait();                                    // X (and the residual) come from the kernel before
 
-    if (warp == 4) {
+    if (warp == 8) {
         if (lane == 0) {
-            for (int kb = 0; kb < n_kb; ++kb) {
-                const int s = kb % STAGES;
-                if (kb >= STAGES && !tbar_wait(&empty[s], ((kb / STAGES) - 1) & 1)) { atomicExch(s_abort, 1); break; }
-                tbar_expect_tx(&full[s], A_BYTES + B_BYTES);
-                tma_load_2d(a_tiles + (size_t)s * A_BYTES, &tmap_x, kb * TC_BK, m0, &full[s]);
-                tma_load_2d(b_tiles + (size_t)s * B_BYTES, &tmap_w, kb * TC_BK, n0, &full[s]);
+            uint32_t kc = 0;                       // k-blocks requested so far, over all tiles
+            for (int tile = blockIdx.x; tile < n_tiles && !*(volatile int*)s_abort; tile += gridDim.x) {
+                const int m0 = SWAP ? tile * TC_BM : (tile / tiles_n) * TC_BM, n0 = SWAP ? 0 : (tile % tiles_n) * BN;
+                for (int kb = 0; kb < n_kb; ++kb, ++kc) {
+                    const int s = kc % STAGES;
+                    const uint32_t use = kc / STAGES;
+                    if (use >= 1 && !tbar_wait_or_abort(&empty[s], (use - 1) & 1, s_abort)) { atomicExch(s_abort, 1); break; }
+                    tbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+                    tma_load_2d(a_tiles + (size_t)s * A_BYTES, &tmap_x, kb * TC_BK, m0, &full[s]);
+                    tma_load_2d(b_tiles + (size_t)s * B_BYTES, &tmap_w, kb * TC_BK, n0, &full[s]);
+                }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_bf16(TC_BM, BN);
-            bool ok = true;
-            for (int kb = 0; kb < n_kb && ok; ++kb) {
-                const int s = kb % STAGES;
-                if (!tbar_wait(&full[s], (kb / STAGES) & 1)) { atomicExch(s_abort, 1); ok = false; break; }
+            uint32_t kc = 0, tc = 0;
+            for (int tile = blockIdx.x; tile < n_tiles && !*(volatile int*)s_abort; tile += gridDim.x, ++tc) {
+                const uint32_t b = tc & 1, use = tc >> 1;
+                if (use >= 1 && !tbar_wait_or_abort(&acc_empty[b], (use - 1) & 1, s_abort)) { atomicExch(s_abort, 1); break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t da = umma_desc_k128(a_tiles + (size_t)s * A_BYTES);
-                const uint64_t db = umma_desc_k128(b_tiles + (size_t)s * B_BYTES);
+                const uint32_t tmem_d = tmem_base + b * BN;
+                bool ok = true;
+                for (int kb = 0; kb < n_kb; ++kb, ++kc) {
+                    const int s = kc % STAGES;
+                    if (!tbar_wait_or_abort(&full[s], (kc / STAGES) & 1, s_abort)) { atomicExch(s_abort, 1); ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t da = umma_desc_k128(a_tiles + (size_t)s * A_BYTES);
+                    const uint64_t db = umma_desc_k128(b_tiles + (size_t)s * B_BYTES);
 #pragma unroll
-                for (int k = 0; k < TC_BK / 16; ++k)          // 16 elements = 32 bytes = 2 descriptor units along K
-                    umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-                umma_commit(&empty[s]);                       // the stage is free once these MMAs have read it
+                    for (int k = 0; k < TC_BK / 16; ++k)      // 16 elements = 32 bytes = 2 descriptor units along K
+                        umma_bf16(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(&empty[s]);                   // the stage is free once these MMAs have read it
+                }
+                if (!ok) break;
+                umma_commit(&acc_full[b]);                    // arrives when every MMA issued so far is complete
             }
-            umma_commit(acc_done);                            // arrives when every MMA issued so far is complete
         }
     } else {
-        // epilogue: warp w reads accumulator lanes 32w … 32w+31 = rows m0 + 32w + lane
-        const bool have = tbar_wait(acc_done, 0);
-        if (!have) atomicExch(s_abort, 1);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const int m = m0 + warp * 32 + lane;
-        // where this thread's row goes in the cache, if the product feeds one
-        int kv_blk = -2, kv_row = 0;                   // −2: nothing to write
-        if (kv.Kc != nullptr && m < M) {
-            const int slot = kv.tok_slot[m];
-            if (slot >= 0) {
-                const int pos = kv.tok_pos[m];
-                kv_blk = kv.block_table[(size_t)slot * kv.max_blocks + pos / kv.BT];
-                kv_row = pos % kv.BT;
-                if (kv_blk < 0) atomicOr(dev_err, VLRF_DEVERR_NO_BLOCK);
-            }
-        }
-        if (SWAP) {
-            if (have && !*s_abort) {
-                const int n = m0 + warp * 32 + lane;          // this thread's output column = row of W
+        // epilogue: warps q and q+4 share accumulator lanes 32q … 32q+31 and take half of the columns each
+        const int q = warp & 3, half = warp >> 2;
+        uint32_t tc = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tc) {
+            const uint32_t b = tc & 1;
+            const int m0 = SWAP ? tile * TC_BM : (tile / tiles_n) * TC_BM, n0 = SWAP ? 0 : (tile % tiles_n) * BN;
+            if (*(volatile int*)s_abort || !tbar_wait_or_abort(&acc_full[b], (tc >> 1) & 1, s_abort)) { atomicExch(s_abort, 1); break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t tmem_d = tmem_base + b * BN + ((uint32_t)(q * 32) << 16);
+            if (SWAP) {
+                const int n = m0 + q * 32 + lane;             // this thread's output column = row of W
                 const float bv = (bias && n < N) ? bias[n] : 0.f;
+                constexpr int PER_HALF = BN >= 32 ? BN / 2 : BN;     // with 16 columns only the first half works
+                if (BN >= 32 || half == 0) {
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 16) {
-                    uint32_t r[16];
-                    asm volatile(
-                        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-                        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
-                        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                        : "r"(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0));
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (n < N) {
+                    for (int c0 = half * PER_HALF; c0 < (half + 1) * PER_HALF && c0 < BN; c0 += 16) {
+                        uint32_t r[16];
+                        asm volatile(
+                            "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+                            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                            : "r"(tmem_d + (uint32_t)c0));
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if (n < N) {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const int m = c0 + j;
-                            if (m < M) {
-                                float x = apply_act_rt(__uint_as_float(r[j]) + bv, act);
-                                if (residual) x += residual[(size_t)m * ldy + n];
-                                ElemIO<OT>::store(Y + (size_t)m * ldy + n, x);
+                            for (int j = 0; j < 16; ++j) {
+                                const int m = c0 + j;
+                                if (m < M) {
+                                    float x = apply_act_rt(__uint_as_float(r[j]) + bv, act);
+                                    if (residual) x += residual[(size_t)m * ldy + n];
+                                    ElemIO<OT>::store(Y + (size_t)m * ldy + n, x);
+                                }
                             }
                         }
                     }
                 }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) tbar_arrive(&acc_empty[b]);    // this warp has read all it needs of the accumulator
+                continue;
             }
-        } else if (have && !*s_abort) {
+            const int m = m0 + q * 32 + lane;                 // this thread's row
+            // where this thread's row goes in the cache, if the product feeds one
+            int kv_blk = -2, kv_row = 0;                      // −2: nothing to write
+            if (kv.Kc != nullptr && m < M) {
+                const int slot = kv.tok_slot[m];
+                if (slot >= 0) {
+                    const int pos = kv.tok_pos[m];
+                    kv_blk = kv.block_table[(size_t)slot * kv.max_blocks + pos / kv.BT];
+                    kv_row = pos % kv.BT;
+                    if (kv_blk < 0) atomicOr(dev_err, VLRF_DEVERR_NO_BLOCK);
+                }
+            }
+            constexpr int HALF_COLS = BN / 2;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = half * HALF_COLS; c0 < (half + 1) * HALF_COLS; c0 += 32) {
                 uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
+                tmem_ld32(tmem_d + (uint32_t)c0, r);          // in flight while the bias and the residual are fetched
+                const bool live = m < M && n0 + c0 < N;
+                const int n_here = live ? min(32, N - (n0 + c0)) : 0;
+                const bool fast = n_here == 32 && (ldy % 8) == 0;
+                OT* __restrict__ yrow = Y + (size_t)m * ldy + n0 + c0;
+                float4 bq[8], rq[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { bq[i] = make_float4(0.f, 0.f, 0.f, 0.f); rq[i] = bq[i]; }
+                if (fast) {
+                    if (bias && ((n0 + c0) % 4 == 0)) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) bq[i] = __ldg(reinterpret_cast<const float4*>(bias + n0 + c0) + i);
+                    } else if (bias) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            bq[i] = make_float4(bias[n0 + c0 + 4 * i], bias[n0 + c0 + 4 * i + 1], bias[n0 + c0 + 4 * i + 2], bias[n0 + c0 + 4 * i + 3]);
+                    }
+                    if (residual) {
+                        const float4* rr = reinterpret_cast<const float4*>(residual + (size_t)m * ldy + n0 + c0);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) rq[i] = rr[i];
+                    }
+                }
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (m < M && n0 + c0 < N) {
-                    const int n_here = min(32, N - (n0 + c0));
-                    OT* yrow = Y + (size_t)m * ldy + n0 + c0;
-                    const float* rrow = residual ? residual + (size_t)m * ldy + n0 + c0 : nullptr;
-                    const float* brow = bias ? bias + n0 + c0 : nullptr;
-                    if (n_here == 32 && (ldy % 8) == 0) {
+                if (c0 + 32 >= (half + 1) * HALF_COLS) {      // this warp's last columns are in registers
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) tbar_arrive(&acc_empty[b]);
+                }
+                if (!live) continue;
+                if (fast) {
 #pragma unroll
-                        for (int j = 0; j < 32; j += 8) {
-                            float v[8];
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) {
-                                float x = __uint_as_float(r[j + e]);
-                                if (brow) x += __ldg(brow + j + e);
-                                v[e] = apply_act_rt(x, act);
-                            }
-                            if (rrow) {
-                                const float4 r0 = *reinterpret_cast<const float4*>(rrow + j);
-                                const float4 r1 = *reinterpret_cast<const float4*>(rrow + j + 4);
-                                v[0] += r0.x; v[1] += r0.y; v[2] += r0.z; v[3] += r0.w;
-                                v[4] += r1.x; v[5] += r1.y; v[6] += r1.z; v[7] += r1.w;
-                            }
-                            if (sizeof(OT) == 4) {
-                                *reinterpret_cast<float4*>(reinterpret_cast<float*>(yrow) + j) = make_float4(v[0], v[1], v[2], v[3]);
-                                *reinterpret_cast<float4*>(reinterpret_cast<float*>(yrow) + j + 4) = make_float4(v[4], v[5], v[6], v[7]);
-                            } else {
-                                uint4 pk;
-                                __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0], v[1]), p1 = __floats2bfloat162_rn(v[2], v[3]);
-                                __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4], v[5]), p3 = __floats2bfloat162_rn(v[6], v[7]);
-                                pk.x = *reinterpret_cast<uint32_t*>(&p0); pk.y = *reinterpret_cast<uint32_t*>(&p1);
-                                pk.z = *reinterpret_cast<uint32_t*>(&p2); pk.w = *reinterpret_cast<uint32_t*>(&p3);
-                                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(yrow) + j) = pk;
-                                const int n = n0 + c0 + j;                 // 8 columns: one head, one of q / k / v
-                                if (kv_blk >= 0 && n >= kv.k_off) {
-                                    const bool is_v = n >= kv.v_off;
-                                    const int col = n - (is_v ? kv.v_off : kv.k_off);
-                                    if (col < kv.width) {
-                                        const int hh = col / kv.dh, cc = col - hh * kv.dh;
-                                        __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(is_v ? kv.Vc : kv.Kc);
-                                        *reinterpret_cast<uint4*>(base + (((size_t)kv_blk * kv.Hkv + hh) * kv.BT + kv_row) * kv.dh + cc) = pk;
-                                    }
-                                }
-                            }
-                        }
-                    } else {
-                        for (int j = 0; j < n_here; ++j) {
-                            float x = __uint_as_float(r[j]);
-                            if (brow) x += brow[j];
-                            x = apply_act_rt(x, act);
-                            if (rrow) x += rrow[j];
-                            ElemIO<OT>::store(yrow + j, x);
-                            const int n = n0 + c0 + j;
+                    for (int j = 0; j < 32; j += 8) {
+                        const float4 b0 = bq[j / 4], b1 = bq[j / 4 + 1], r0 = rq[j / 4], r1 = rq[j / 4 + 1];
+                        float v[8];
+                        v[0] = apply_act_rt(__uint_as_float(r[j + 0]) + b0.x, act) + r0.x;
+                        v[1] = apply_act_rt(__uint_as_float(r[j + 1]) + b0.y, act) + r0.y;
+                        v[2] = apply_act_rt(__uint_as_float(r[j + 2]) + b0.z, act) + r0.z;
+                        v[3] = apply_act_rt(__uint_as_float(r[j + 3]) + b0.w, act) + r0.w;
+                        v[4] = apply_act_rt(__uint_as_float(r[j + 4]) + b1.x, act) + r1.x;
+                        v[5] = apply_act_rt(__uint_as_float(r[j + 5]) + b1.y, act) + r1.y;
+                        v[6] = apply_act_rt(__uint_as_float(r[j + 6]) + b1.z, act) + r1.z;
+                        v[7] = apply_act_rt(__uint_as_float(r[j + 7]) + b1.w, act) + r1.w;
+                        if (sizeof(OT) == 4) {
+                            *reinterpret_cast<float4*>(reinterpret_cast<float*>(yrow) + j) = make_float4(v[0], v[1], v[2], v[3]);
+                            *reinterpret_cast<float4*>(reinterpret_cast<float*>(yrow) + j + 4) = make_float4(v[4], v[5], v[6], v[7]);
+                        } else {
+                            uint4 pk;
+                            pk.x = pack2(v[0], v[1]); pk.y = pack2(v[2], v[3]); pk.z = pack2(v[4], v[5]); pk.w = pack2(v[6], v[7]);
+                            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(yrow) + j) = pk;
+                            const int n = n0 + c0 + j;                 // 8 columns: one head, one of q / k / v
                             if (kv_blk >= 0 && n >= kv.k_off) {
                                 const bool is_v = n >= kv.v_off;
                                 const int col = n - (is_v ? kv.v_off : kv.k_off);
                                 if (col < kv.width) {
                                     const int hh = col / kv.dh, cc = col - hh * kv.dh;
                                     __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(is_v ? kv.Vc : kv.Kc);
-                                    base[(((size_t)kv_blk * kv.Hkv + hh) * kv.BT + kv_row) * kv.dh + cc] = __float2bfloat16_rn(x);
+                                    *reinterpret_cast<uint4*>(base + (((size_t)kv_blk * kv.Hkv + hh) * kv.BT + kv_row) * kv.dh + cc) = pk;
                                 }
+                            }
+                        }
+                    }
+                } else {
+                    const float* rrow = residual ? residual + (size_t)m * ldy + n0 + c0 : nullptr;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {            // unrolled so that r stays in registers
+                        if (j >= n_here) break;
+                        float x = __uint_as_float(r[j]);
+                        if (bias) x += bias[n0 + c0 + j];
+                        x = apply_act_rt(x, act);
+                        if (rrow) x += rrow[j];
+                        ElemIO<OT>::store(yrow + j, x);
+                        const int n = n0 + c0 + j;
+                        if (kv_blk >= 0 && n >= kv.k_off) {
+                            const bool is_v = n >= kv.v_off;
+                            const int col = n - (is_v ? kv.v_off : kv.k_off);
+                            if (col < kv.width) {
+                                const int hh = col / kv.dh, cc = col - hh * kv.dh;
+                                __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(is_v ? kv.Vc : kv.Kc);
+                                base[(((size_t)kv_blk * kv.Hkv + hh) * kv.BT + kv_row) * kv.dh + cc] = __float2bfloat16_rn(x);
                             }
                         }
                     }
@@ -287,7 +360,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (warp == 4) {
+    if (warp == 8) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
     }
     if (threadIdx.x == 0 && *s_abort) atomicOr(dev_err, VLRF_DEVERR_WAIT_TIMEOUT);
@@ -301,7 +374,7 @@ int launch_tc(const void* X, const void* W, const float* bias, const float* resi
     if (st != VLRF_OK) return st;
     st = SWAP ? vlrf_make_tmap_bf16(X, M, K, ldx, BN, TC_BK, &tw) : vlrf_make_tmap_bf16(W, N, K, K, BN, TC_BK, &tw);
     if (st != VLRF_OK) return st;
-    const size_t smem = 1024 + (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 1) * 8 + 16;
+    const size_t smem = 1024 + (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 4) * 8 + 16;
     auto kern = gemm_tcgen05_kernel<BN, STAGES, OT, SWAP>;
     static bool raised = false;
     if (!raised) {
@@ -309,8 +382,9 @@ int launch_tc(const void* X, const void* W, const float* bias, const float* resi
         if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "gemm_tcgen05: %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         raised = true;
     }
-    dim3 grid((N + BN - 1) / BN, (M + TC_BM - 1) / TC_BM);
-    if (SWAP) grid = dim3((N + TC_BM - 1) / TC_BM, 1);
+    const long long tiles = SWAP ? (N + TC_BM - 1) / TC_BM : (long long)((N + BN - 1) / BN) * ((M + TC_BM - 1) / TC_BM);
+    const int sms = sm_count_cached();
+    dim3 grid((unsigned)(tiles < sms ? tiles : sms));          // persistent: one CTA per SM at most
     cudaError_t e = launch_chained(kern, grid, dim3(TC_THREADS), smem, stream, tx, tw, bias, residual, (OT*)Y, M, N, K, ldy,
                                    act, kv, dev_err);
     if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "gemm_tcgen05: %s", cudaGetErrorString(e));
@@ -342,24 +416,37 @@ extern "C" int vlrf_gemm_tcgen05(const void* X, const void* W, const float* bias
     }
     if (M <= 64 && Kc == nullptr) {
         // few rows: W fills the 128-row operand, the rows of X are the MMA's N
-#define SWAPPED(BNV) (out_dtype == VLRF_BF16 ? launch_tc<BNV, 4, __nv_bfloat16, true>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, kv, dev_err, stream) \
-                                             : launch_tc<BNV, 4, float, true>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, kv, dev_err, stream))
+#define SWAPPED(BNV) (out_dtype == VLRF_BF16 ? launch_tc<BNV, 8, __nv_bfloat16, true>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, kv, dev_err, stream) \
+                                             : launch_tc<BNV, 8, float, true>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, kv, dev_err, stream))
         VLRF_REQUIRE(out_dtype == VLRF_BF16 || out_dtype == VLRF_F32, "gemm_tcgen05: unknown output dtype %d", out_dtype);
         if (M <= 16) return SWAPPED(16);
         if (M <= 32) return SWAPPED(32);
         return SWAPPED(64);
 #undef SWAPPED
     }
-    // narrower tiles when wide ones would leave most SMs idle
-    const long long tiles128 = (long long)((N + 127) / 128) * ((M + 127) / 128);
-    const bool narrow = tiles128 < 120;
-    if (out_dtype == VLRF_BF16) {
-        if (narrow) return launch_tc<64, 4, __nv_bfloat16>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, kv, dev_err, stream);
-        return launch_tc<128, 3, __nv_bfloat16>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, kv, dev_err, stream);
+    // tile width: the fewest rounds of the persistent CTAs weighted by a tile's length (MMA time grows with
+    // the width; a fixed part per tile does not)
+    int best_bn = 128;
+    {
+        const int sms = sm_count_cached();
+        long long best = -1;
+        const int widths[3] = {256, 128, 64};
+        for (int i = 0; i < 3; ++i) {
+            const int bn = widths[i];
+            if (bn > 64 && N <= bn / 2) continue;
+            const long long tiles = (long long)((N + bn - 1) / bn) * ((M + 127) / 128);
+            const long long rounds = (tiles + sms - 1) / sms;
+            const long long cost = rounds * (bn + 32);
+            if (best < 0 || cost < best) { best = cost; best_bn = bn; }
+        }
     }
-    if (out_dtype == VLRF_F32) {
-        if (narrow) return launch_tc<64, 4, float>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, kv, dev_err, stream);
-        return launch_tc<128, 3, float>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, kv, dev_err, stream);
-    }
-    return vlrf_fail(VLRF_ERR_INVALID_ARG, "gemm_tcgen05: unknown output dtype %d", out_dtype);
+    if (const char* e = getenv("VLRF_TC_BN")) { const int v = atoi(e); if (v == 64 || v == 128 || v == 256) best_bn = v; }
+#define TILED(BNV, ST) (out_dtype == VLRF_BF16 ? launch_tc<BNV, ST, __nv_bfloat16>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, kv, dev_err, stream) \
+                                              : launch_tc<BNV, ST, float>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, kv, dev_err, stream))
+    VLRF_REQUIRE(out_dtype == VLRF_BF16 || out_dtype == VLRF_F32, "gemm_tcgen05: unknown output dtype %d", out_dtype);
+    if (best_bn == 256) return TILED(256, 4);
+    if (best_bn == 128) return TILED(128, 6);
+    return TILED(64, 8);
+#undef TILED
 }
+
