@@ -163,8 +163,7 @@ def decode_device(model_dir, batch, steps, warmup, dtype="bfloat16"):
     sess.reserve_ahead(warmup + steps + 1)
     sess.set_tokens(out)
     for _ in range(warmup):
-        ops.sample(sess.step(), batch, out)
-        sess.set_tokens(out)
+        sess.step_greedy(out)
     torch.cuda.synchronize()
     bytes_first = step_bytes(model, engine, slots)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -172,17 +171,16 @@ def decode_device(model_dir, batch, steps, warmup, dtype="bfloat16"):
         torch.cuda.synchronize()
         e0.record()
         for _ in range(steps):
-            ops.sample(sess.step(), batch, out)
-            sess.set_tokens(out)
+            sess.step_greedy(out)        # model + argmax + hand-over to the next step: one replayed graph
         e1.record()
         torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
     bytes_last = step_bytes(model, engine, slots)
     engine.check_device_errors()
-    launches = steps * (sess.kernels_per_step + 1)        # the step's kernels (replayed) + the sampling kernel
+    launches = steps * sess.kernels_per_step              # the step's kernels, sampling included (replayed)
     return dict(tok_s=batch * steps / (ms / 1e3), ms_per_step=ms / steps, steps=steps,
                 bytes_per_step=(bytes_first + bytes_last) / 2, clocks=clk.summary(), launches=launches,
-                kernels_per_step=sess.kernels_per_step + 1, mean_context=PROMPT_LEN + warmup + steps / 2,
+                kernels_per_step=sess.kernels_per_step, mean_context=PROMPT_LEN + warmup + steps / 2,
                 weight_bytes=model.weight_bytes(), n_layer=cfg.n_layer)
 
 

@@ -54,7 +54,7 @@ _SIGNATURES = {
                          _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int,
                          _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "vlrf_sample": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
-                    _c_void_p, _c_void_p],
+                    _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "vlrf_apply_penalties": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
                              _c_void_p, _c_void_p, _c_void_p, _c_void_p],
 }

@@ -280,9 +280,11 @@ def attention_generic(qkv, q_off: int, k_cache, v_cache, block_table, tok_slot, 
 
 
 def sample(logits, n_rows: int, out_tokens, *, temperature=None, top_k=None, top_p=None, rng_key=None,
-           rng_ctr=None) -> None:
+           rng_ctr=None, next_tokens=None, next_pos=None, row_slot=None) -> None:
     """One token per row of float32 logits.  Rows with temperature ≤ 0 (or no temperature tensor at all)
-    take the first maximal index; the others draw after top-k / top-p filtering."""
+    take the first maximal index; the others draw after top-k / top-p filtering.  `next_tokens`,
+    `next_pos`, `row_slot` (int32 [n_rows], optional): the kernel also writes each token into next_tokens
+    and adds one to next_pos where row_slot is not −1, which is all a decode session needs to go on."""
     _dev(logits, "logits", torch.float32); _dev(out_tokens, "out_tokens", torch.int32)
     V = logits.shape[1]
     if logits.shape[0] < n_rows or out_tokens.shape[0] < n_rows:
@@ -294,8 +296,13 @@ def sample(logits, n_rows: int, out_tokens, *, temperature=None, top_k=None, top
         _dev(top_k, "top_k", torch.int32)
     if top_p is not None:
         _dev(top_p, "top_p", torch.float32)
+    for name, t in (("next_tokens", next_tokens), ("next_pos", next_pos), ("row_slot", row_slot)):
+        if t is not None:
+            _dev(t, name, torch.int32)
+            if t.shape[0] < n_rows:
+                raise KernelError(f"sample: {name} has fewer rows than asked for")
     call("vlrf_sample", _ptr(logits), V, n_rows, V, _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(rng_key),
-         _ptr(rng_ctr), _ptr(out_tokens), _stream())
+         _ptr(rng_ctr), _ptr(out_tokens), _ptr(next_tokens), _ptr(next_pos), _ptr(row_slot), _stream())
 
 
 def apply_penalties(logits, n_rows: int, generated, generated_len, *, repetition=None, frequency=None,

@@ -89,7 +89,8 @@ __global__ void __launch_bounds__(ST)
 sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p,
               const unsigned long long* __restrict__ rng_key, unsigned int* __restrict__ rng_ctr,
-              int* __restrict__ out_token) {
+              int* __restrict__ out_token, int* __restrict__ next_token, int* __restrict__ next_pos,
+              const int* __restrict__ row_slot) {
     __shared__ ArgMax sm_am[32];
     __shared__ unsigned long long sm_u64[32];
     __shared__ int sm_i32[32];
@@ -115,7 +116,12 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
     if (am.i == 0x7fffffff) am.i = 0;  // a row of NaNs or −inf: defined answer
     const float temp = temperature ? temperature[row] : 0.f;
     if (!(temp > 0.f)) {
-        if (tid == 0) out_token[row] = am.i;
+        if (tid == 0) {
+            out_token[row] = am.i;
+            // feed the next step on the device: the token becomes the row's input, its position moves on
+            if (next_token) next_token[row] = am.i;
+            if (next_pos && (!row_slot || row_slot[row] >= 0)) next_pos[row] += 1;
+        }
         return;
     }
     const float mx = am.v, inv_t = 1.f / temp;
@@ -242,7 +248,11 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
         if (tid == 0) out_token[row] = (s_choice >= 0) ? s_choice : am.i;
     }
     __syncthreads();
-    if (tid == 0) rng_ctr[row] = rng_ctr[row] + 1u;
+    if (tid == 0) {
+        rng_ctr[row] = rng_ctr[row] + 1u;
+        if (next_token) next_token[row] = out_token[row];
+        if (next_pos && (!row_slot || row_slot[row] >= 0)) next_pos[row] += 1;
+    }
 }
 
 // Penalties over the tokens a request generated so far, and the n-gram block
@@ -291,15 +301,19 @@ __global__ void penalties_kernel(float* __restrict__ logits, int ld, int V, cons
 }
 }  // namespace
 
+// next_token / next_pos / row_slot (all optional): after choosing, write the token into next_token[row] and
+// add one to next_pos[row] (for rows whose slot is not −1), so that a decode step can be followed by the
+// next without the host touching the tables.
 extern "C" int vlrf_sample(const float* logits, int ld, int n_rows, int V, const float* temperature,
                            const int* top_k, const float* top_p, const unsigned long long* rng_key,
-                           unsigned int* rng_ctr, int* out_token, cudaStream_t stream) {
+                           unsigned int* rng_ctr, int* out_token, int* next_token, int* next_pos,
+                           const int* row_slot, cudaStream_t stream) {
     VLRF_REQUIRE(n_rows >= 0 && V > 0 && ld >= V, "sample: bad sizes rows=%d V=%d ld=%d", n_rows, V, ld);
     VLRF_REQUIRE(temperature == nullptr || (rng_key != nullptr && rng_ctr != nullptr),
                  "sample: temperature sampling needs the rows' random keys and counters");
     if (n_rows == 0) return VLRF_OK;
     launch_chained(sample_kernel, dim3(n_rows), dim3(ST), 0, stream, logits, ld, V, temperature, top_k, top_p, rng_key,
-                   rng_ctr, out_token);
+                   rng_ctr, out_token, next_token, next_pos, row_slot);
     return vlrf_check_launch("sample");
 }
 

@@ -77,8 +77,8 @@ class DeviceBackend:
         for r, toks in zip(rows, tokens):
             st[r] = toks[0]
         sess.tokens[:n].copy_(st, non_blocking=True)          # this step's inputs, host → device
-        logits = sess.step()
-        out = batch.sampler.sample(logits[:n], list(range(n)))
+        logits = sess.step(advance_on_device=False)            # the sampling kernel moves the positions on
+        out = batch.sampler.sample(logits[:n], list(range(n)), next_pos=sess.tok_pos, row_slot=sess.tok_slot)
         host = out.tolist()                                    # this step's result, device → host; synchronises
         self.h2d_bytes += 4 * n
         self.d2h_bytes += 4 * n

@@ -33,6 +33,8 @@ class DecodeSession:
         self.ws = Workspace(dev)
         self.use_graph = use_graph
         self.graph = None
+        self._greedy_graph = None
+        self._greedy_out = None
         self.logits = None
         self.kernels_per_step = 0
         self._sync_tables()
@@ -50,6 +52,45 @@ class DecodeSession:
             self.tokens[:self.n].copy_(tokens[:self.n])
         else:
             self.tokens[:self.n].copy_(torch.tensor(list(tokens), dtype=torch.int32))
+
+    def step_greedy(self, out: torch.Tensor) -> torch.Tensor:
+        """A whole greedy decode step on the device: the model, the argmax, and the hand-over of token and
+        position to the next step, captured together; `out` (int32 [rows]) receives the tokens."""
+        from ..csrc import launch_count, ops
+        c = self.engine.cache
+        for s, live in zip(self.slots, self.live):
+            if live and c.lengths[s] + 1 > self.model.max_seq_len:
+                raise ValueError(f"slot {s} is at the model's last position")
+
+        def run():
+            logits = self.model.forward(self._context(), c)
+            ops.sample(logits, self.rows, out, next_tokens=self.tokens, next_pos=self.tok_pos, row_slot=self.tok_slot)
+            return logits
+
+        if not self.use_graph:
+            before = launch_count()
+            self.logits = run()
+            self.kernels_per_step = launch_count() - before
+        else:
+            if self._greedy_graph is None or self._greedy_out is not out:
+                pos = self.tok_pos.clone()             # the warm-up run must not advance anything
+                tok = self.tokens.clone()
+                before = launch_count()
+                self.logits = run()
+                self.kernels_per_step = launch_count() - before
+                torch.cuda.synchronize()
+                self.tok_pos.copy_(pos); self.tokens.copy_(tok)
+                self.ws.frozen = True
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self.logits = run()
+                self._greedy_graph, self._greedy_out = g, out
+            self._greedy_graph.replay()
+        for s, live in zip(self.slots, self.live):
+            if live:
+                c.advance(s, 1)
+        self.engine.steps_run += 1
+        return self.logits
 
     def end_row(self, row: int) -> None:
         """The sequence of this row has ended; its row becomes padding.  (The slot is the caller's to free.)"""
@@ -75,10 +116,12 @@ class DecodeSession:
             n_logit_rows=self.rows, act_dtype=self.model.act_dtype, dev_err=self.engine.dev_err, ws=self.ws,
             host_seq_slots=list(self.slots), host_seq_lens=[1] * self.rows, host_seq_pos0=[])
 
-    def step(self) -> torch.Tensor:
+    def step(self, advance_on_device: bool = True) -> torch.Tensor:
         """One decode step of all rows from `self.tokens`; returns float32 logits [rows, vocab] (static
-        storage).  Afterwards every live row's position has advanced by one, on the device and in the
-        cache's books."""
+        storage).  Afterwards every live row's position has advanced by one in the cache's books, and on
+        the device too unless `advance_on_device` is False — then whoever samples must pass
+        `next_pos=self.tok_pos, row_slot=self.tok_slot` (and `next_tokens=self.tokens`) to the sampling
+        kernel, which does it in the same launch."""
         from ..csrc import launch_count
         c = self.engine.cache
         for s, live in zip(self.slots, self.live):
@@ -101,7 +144,8 @@ class DecodeSession:
             before = launch_count()
             self.logits = self.model.forward(self._context(), c)
             self.kernels_per_step = launch_count() - before
-        self.tok_pos.add_(self.one * (self.tok_slot >= 0))
+        if advance_on_device:
+            self.tok_pos.add_(self.one * (self.tok_slot >= 0))
         for s, live in zip(self.slots, self.live):
             if live:
                 c.advance(s, 1)

@@ -39,8 +39,9 @@ class RowSampler:
             self.history_len = torch.zeros(n, dtype=torch.int32, device=self.device)
         self.out = torch.zeros(n, dtype=torch.int32, device=self.device)
 
-    def sample(self, logits: torch.Tensor, rows: list) -> torch.Tensor:
-        """logits [len(rows), vocab] float32; rows: which requests these logits belong to, in order."""
+    def sample(self, logits: torch.Tensor, rows: list, *, next_pos=None, row_slot=None) -> torch.Tensor:
+        """logits [len(rows), vocab] float32; rows: which requests these logits belong to, in order.
+        `next_pos`, `row_slot`: a decode session's tables, advanced by the sampling kernel itself."""
         m = len(rows)
         all_rows = m == self.n and rows == list(range(self.n))
         idx = None if all_rows else torch.tensor(rows, dtype=torch.long, device=self.device)
@@ -53,13 +54,14 @@ class RowSampler:
         if self.any_sampling:
             ctr = pick(self.rng_ctr).contiguous()
             ops.sample(logits, m, out, temperature=pick(self.temperature), top_k=pick(self.top_k),
-                       top_p=pick(self.top_p), rng_key=pick(self.rng_key), rng_ctr=ctr)
+                       top_p=pick(self.top_p), rng_key=pick(self.rng_key), rng_ctr=ctr, next_pos=next_pos,
+                       row_slot=row_slot)
             if all_rows:
                 pass  # the kernel advanced the counters in place
             else:
                 self.rng_ctr.index_copy_(0, idx, ctr)
         else:
-            ops.sample(logits, m, out)
+            ops.sample(logits, m, out, next_pos=next_pos, row_slot=row_slot)
         if self.any_penalties:
             r = torch.arange(self.n, device=self.device) if all_rows else idx
             at = self.history_len.index_select(0, r).long().clamp_(max=self.history.shape[1] - 1)
