@@ -37,7 +37,7 @@ template <> struct Vec16d<__nv_bfloat16> {
     }
 };
 
-constexpr int DEC_WARPS = 4;
+constexpr int DEC_WARPS = 8;
 constexpr int DEC_MAX_DH = 256;
 constexpr int DEC_ND = DEC_MAX_DH / 32;
 constexpr uint32_t DEC_WAIT_LIMIT = 4000000u;
