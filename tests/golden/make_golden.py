@@ -105,7 +105,9 @@ def write_bin(path, tensors):
 
 
 def main():
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py /path/to/VLRF")
+    ref = Path(sys.argv[1])
     inc = ref / "include"
     with tempfile.TemporaryDirectory() as tmp:
         tmp = Path(tmp)

@@ -10,7 +10,7 @@ from engine_drives import drive_batches, drive_tail_one_by_one, drive_whole, poi
 pytestmark = pytest.mark.gpu
 
 DTYPES = [("float32", TOL_F32), ("bfloat16", TOL_BF16)]
-#: request lengths per model: BASELINE's batches (5/17/31 and 1/9/40/100) with their decode steps added
+#: request lengths per model: prompts of 5/17/31 and 1/9/40/100 tokens with their decode steps added, and longer ones
 LENGTHS = {"tiny_a": [5 + 16, 17 + 16, 31 + 16, 70, 128], "tiny_b": [1 + 24, 9 + 24, 40 + 24, 100 + 24, 200, 256],
            "tiny_c": [3 + 20, 64 + 20, 65 + 20, 127 + 20, 250, 320]}
 

@@ -5,7 +5,7 @@
 //
 // Who needs it: code that runs where cudaMalloc is off limits — inside a stream capture, inside a
 // real-time or latency-critical loop that must not take the allocator's locks, in a host process whose
-// memory budget is fixed up front, or a plugin that is handed inputs and outputs but no allocator.  The
+// memory plan is fixed up front, or a plugin that is handed inputs and outputs but no allocator.  The
 // ordinary entry point, vlrf_attn_decode, needs scratch memory from its caller when a context is cut into
 // several parts (partial results of the parts, and a counter per (row, head)); such callers have nowhere
 // to get it from.  Here the scratch is a fixed array inside the library itself, so the caller passes only

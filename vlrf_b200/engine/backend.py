@@ -16,7 +16,7 @@ from .step import Engine, StepEntry
 class _Batch:
     slots: list
     sampler: RowSampler
-    budget: list                      # most tokens each sequence may come to hold
+    most_tokens: list                 # most tokens each sequence may come to hold
     session: DecodeSession | None = None
     staging: torch.Tensor | None = None   # pinned host int32: the tokens fed at a decode step
 
@@ -55,7 +55,7 @@ class DeviceBackend:
             # every sequence of the batch goes on by one token: from here on the steps are replayed
             batch.session = DecodeSession(self.engine, batch.slots, use_graph=self.use_graph,
                                           pad_to=_bucket(len(batch.slots)))
-            for s, most in zip(batch.slots, batch.budget):
+            for s, most in zip(batch.slots, batch.most_tokens):
                 self.engine.cache.reserve(s, most)
             self.engine.cache.sync_tables()
             batch.staging = torch.zeros(len(batch.slots), dtype=torch.int32, pin_memory=True)
