@@ -132,3 +132,41 @@ def test_step_refuses_what_it_cannot_run(model_dirs):
         eng.step([StepEntry(s2, [1] * 65, [0])])
     assert eng.step([StepEntry(s2, [1] * 3, [])]).shape == (0, 512)
     eng.check_device_errors()
+
+
+# ------------------------------------------------------------------------------------------------
+# The real widths of GPT-2 small (768 wide, 12 heads of 64, inner 3072, vocabulary 50257, 1024 positions)
+# with two layers: the tensor-core kernels meet the sizes they serve, tails of the vocabulary included.
+GPT2_WIDE = dict(model_type="gpt2", n_layer=2, n_embd=768, n_head=12, n_inner=None, vocab_size=50257, n_positions=1024,
+                 layer_norm_epsilon=1e-5, activation_function="gelu_new", scale_attn_by_inverse_layer_idx=False,
+                 tie_word_embeddings=True, bos_token_id=50256, eos_token_id=50256)
+
+
+#: the widths of GPT-2 XL (1600 wide, 25 heads of 64, inner 6400) with one layer and a small vocabulary
+GPT2_XL_WIDE = dict(GPT2_WIDE, n_layer=1, n_embd=1600, n_head=25, vocab_size=1003, n_positions=512,
+                    bos_token_id=1, eos_token_id=2)
+WIDE = {"small": (GPT2_WIDE, 50257), "xl": (GPT2_XL_WIDE, 1003)}
+
+
+@pytest.fixture(scope="module", params=["small", "xl"])
+def wide_model(request, tmp_path_factory):
+    from vlrf_b200.weights import write_random_model
+    cfg_dict, vocab = WIDE[request.param]
+    d = tmp_path_factory.mktemp("gpt2_wide_" + request.param)
+    write_random_model(cfg_dict, 321, d)
+    cfg, w = plain.read_model_dir(d)
+    reqs = [random_ids(vocab, n, 400 + n) for n in (70, 150, 9)]
+    truth = [plain.logits_all_positions(cfg, w, ids) for ids in reqs]
+    return d, reqs, truth
+
+
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+def test_gpt2_real_widths_whole_tail_and_batch(wide_model, dtype, tol):
+    from vlrf_b200.engine import Engine, load_model
+    d, reqs, truth = wide_model
+    eng = Engine(load_model(d, dtype), max_tokens=64 * 8)
+    poison(eng)
+    compare(drive_whole(eng, reqs), truth, tol, "GPT-2 widths, whole")
+    compare(drive_tail_one_by_one(eng, reqs, 20), truth, tol, "GPT-2 widths, prefix + 20 single tokens")
+    compare(drive_batches(eng, reqs, 3, [50, 130, 1]), truth, tol, "GPT-2 widths, unequal batch")
+    assert eng.cache.slots.n_held == 0

@@ -44,11 +44,20 @@ def unregister_architecture(name: str) -> None:
     _ARCHITECTURES.pop(name, None)
 
 
+def _load_builtin() -> None:
+    """The architectures that ship with the package register themselves when their module is imported."""
+    import importlib
+    importlib.import_module("vlrf_b200.models")
+
+
 def architecture_names() -> list[str]:
+    _load_builtin()
     return sorted(_ARCHITECTURES)
 
 
 def get_architecture(name: str) -> Architecture:
+    if name not in _ARCHITECTURES:
+        _load_builtin()
     try:
         return _ARCHITECTURES[name]
     except KeyError:
