@@ -42,6 +42,11 @@ _SIGNATURES = {
                          _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_float,
                          _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
                          _c_int, _c_int, _c_void_p, _c_void_p],
+    "vlrf_gemm_splitk_takes": [_c_int, _c_int, _c_int, _c_int, _c_int],
+    "vlrf_gemm_splitk": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
+                         _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_float,
+                         _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
+                         _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "vlrf_gemm_tcgen05_takes": [_c_int, _c_int, _c_int, _c_int],
     "vlrf_gemm_tcgen05": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
                           _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int,

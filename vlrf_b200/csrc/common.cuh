@@ -61,6 +61,28 @@ cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// The same for a kernel whose CTAs form clusters of (1, cluster_y, 1): the CTAs of a cluster run at the same
+// time on neighbouring SMs and may read one another's shared memory.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_chained_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, int cluster_y,
+                                   cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = (unsigned)cluster_y;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = vlrf_chained_launch_enabled() ? 2 : 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 template <typename T> struct ElemIO;
 template <> struct ElemIO<float> {
     static __device__ __forceinline__ float load(const float* p) { return *p; }

@@ -1,0 +1,506 @@
+// Y[M,N] = act(X[M,K] · W[N,K]^T + bias) (+ residual) for few rows (M ≤ 64) on the tcgen05 tensor cores,
+// with the sum over k cut into parts: the decode step's products for layers too wide for one CTA to
+// stream a whole group of weight rows.
+//
+// The product is bound by reading W once.  W is the 128-row operand of the MMA (a tile of 128 output
+// columns), the few rows of X are its N (16, 32 or 64), so the accumulator in tensor memory holds Yᵀ.  A
+// layer's matrices have only N/128 such tiles, too few to keep HBM busy, so the grid is tiles × splits and
+// the `splits` CTAs of a tile form a thread-block cluster: CTA (tile, s) streams the 64-wide k blocks of
+// part s through a ring of shared-memory stages (TMA, 128-byte swizzle), one elected thread issues
+// `tcgen05.mma` per block, and the partial tile is put into the CTA's own shared memory.  After a cluster
+// barrier the warps of all CTAs of the cluster share the tile's (row, 32-column) pieces among them; a warp
+// reads its piece from every CTA's shared memory (distributed shared memory) and adds the parts in the
+// order of s, so the result does not depend on timing; it then applies bias, GELU and the residual sum
+// (reference include/model/feedforward.hpp:54-76, include/model/transformer_block.hpp:153,158), stores
+// the piece and, for a fused q/k/v projection, scatters K and V columns into the paged cache (reference
+// include/model/kv_cache.hpp:215-251).  A second cluster barrier keeps every CTA's shared memory alive
+// until its neighbours have read it.
+//
+// A tile may also have 64 rows of W only (twice as many tiles for narrow matrices): the MMA still works on
+// 128 rows, the upper 64 being whatever follows in shared memory, and the upper 64 lanes of the accumulator
+// are never read.
+//
+// LN: the rows of X are the float32 residual stream; eight warps compute the LayerNorm (statistics in
+// float32 over the whole row, held in registers for both passes; reference include/model/ops.hpp:443-476)
+// and write this CTA's part of the normalised rows as bfloat16 into shared memory in the layout TMA would
+// have produced, while the weight copies are already in flight.
+//
+// Launched "chained": weights are requested before the kernel ahead has finished, activations only after.
+// Every wait on an mbarrier is bounded; a CTA that gives up sets the device error word, still meets its
+// cluster at both barriers and frees its tensor memory.
+#include "common.cuh"
+#include "tma.cuh"
+#include "tcgen05.cuh"
+#include <cstdlib>
+
+namespace {
+
+// warps 0-3: epilogue (and LayerNorm), 4: producer + tensor memory, 5: MMA issue, 6-9 (LN only): LayerNorm
+constexpr int SP_THREADS = 192, SP_THREADS_LN = 320;
+constexpr int SP_BK = 64;
+constexpr int SP_MAX_STAGES = 16;
+constexpr int SP_MAX_SPLITS = 16;        // the largest cluster (more than 8 is "non-portable": B200 takes it)
+constexpr int SP_LN_MAX_KB = 16;         // k blocks of one part with the fused norm (a lane holds 8 float4 of a row)
+constexpr int SP_STAT_SEGS = 256;        // most 32-column segments of a row whose statistics are kept (width ≤ 8192)
+constexpr size_t SP_SMEM_BUDGET = 111 * 1024;   // two CTAs fit an SM: this product's and the next one's, fetching ahead
+
+struct SpKvScatter {
+    void* Kc; void* Vc;
+    const int* block_table; const int* tok_slot; const int* tok_pos;
+    int max_blocks, k_off, v_off, width, dh, Hkv, BT;
+};
+
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// the same without ordering of memory: for "everyone has finished reading", when what was read has been used
+__device__ __forceinline__ void cluster_sync_relaxed() {
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;\nbarrier.cluster.wait.aligned;" ::: "memory");
+}
+// the value at `own_addr` (a shared-memory address of this CTA) in the CTA of rank `rank` of the cluster
+__device__ __forceinline__ float ld_cluster_f32(uint32_t own_addr, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(own_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+// bm: rows of W per tile (64 or 128); stages: depth of the ring; kb_cap: most k blocks of one part
+template <int BN, typename OT, bool LN>
+__global__ void __launch_bounds__(LN ? SP_THREADS_LN : SP_THREADS, 2)
+gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                   const float* __restrict__ Xf, int ldx, const float* __restrict__ gamma,
+                   const float* __restrict__ beta, float eps, const float* __restrict__ bias, const float* residual,
+                   OT* Y, int M, int N, int K, int ldy, int act, int bm, int stages, int kb_cap, SpKvScatter kv,
+                   const float* stats_in, float* stats_out, int* __restrict__ dev_err) {
+    extern __shared__ unsigned char sp_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(sp_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr int B_BYTES = BN * SP_BK * 2;
+    constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    const int a_bytes = bm * SP_BK * 2;
+    // the MMA reads 128 rows from each stage: with 64-row tiles the last stage's read runs 8 KiB further,
+    // which the layout keeps inside the allocation (the B tiles follow, at least 8 KiB of them or padding)
+    unsigned char* a_tiles = smem;                                   // [stages][bm][128 B]
+    const int ring_bytes = stages * a_bytes;
+    unsigned char* b_tiles = smem + ring_bytes + (bm == 64 ? 8192 : 0);   // LN: [kb_cap][BN][128 B], else [stages][BN][128 B]
+    unsigned char* after_b = b_tiles + (size_t)(LN ? kb_cap : stages) * B_BYTES;
+    float* s_gamma = reinterpret_cast<float*>(after_b);              // LN: [kb_cap·64] this part's norm weights
+    float* s_beta = s_gamma + (LN ? kb_cap * SP_BK : 0);
+    // this CTA's part of the tile, written at the end: [m][bm] float32
+    float* part = s_beta + (LN ? kb_cap * SP_BK : 0);
+    const int segs = bm >> 5, units = M * segs, ustride = 4 * (int)gridDim.y;
+    uint64_t* full = reinterpret_cast<uint64_t*>(part + (size_t)M * bm);
+    uint64_t* empty = full + SP_MAX_STAGES;
+    uint64_t* acc_full = empty + SP_MAX_STAGES;
+    uint64_t* x_ready = acc_full + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(x_ready + 1);
+    int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
+    int* s_kv_blk = s_abort + 1;                                     // [64]
+    int* s_kv_row = s_kv_blk + 64;                                   // [64]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x, split = blockIdx.y, splits = gridDim.y;
+    const int n_kb_all = (K + SP_BK - 1) / SP_BK;
+    const int kb0 = (int)(((long long)n_kb_all * split) / splits), kb1 = (int)(((long long)n_kb_all * (split + 1)) / splits);
+    const int n_kb = kb1 - kb0;
+    const int n0 = tile * bm;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) { tbar_init(&full[s], 1); tbar_init(&empty[s], 1); }
+        tbar_init(acc_full, 1);
+        tbar_init(x_ready, 8);
+        *s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 4) {
+        if (lane == 0) { tma_prefetch_descriptor(&tmap_w); if (!LN) tma_prefetch_descriptor(&tmap_x); }
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tsm(tmem_slot)), "r"((uint32_t)TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    // The weights do not depend on the kernel ahead: the first stages' tiles of W are requested at once, and
+    // the norm's weights for this part's columns are copied to shared memory.
+    const int first = n_kb < stages ? n_kb : stages;
+    if (warp == 4 && lane == 0) {
+        for (int i = 0; i < first; ++i) {
+            tbar_expect_tx(&full[i], a_bytes + (LN ? 0 : B_BYTES));
+            tma_load_2d(a_tiles + (size_t)i * a_bytes, &tmap_w, (kb0 + i) * SP_BK, n0, &full[i]);
+        }
+    }
+    const bool ln_warp = LN && warp != 4 && warp != 5;
+    const int lw = warp < 4 ? warp : warp - 2;                       // 0…7 among the LayerNorm warps
+    if (ln_warp) {
+        for (int i = lw * 32 + lane; i < n_kb * SP_BK; i += 256) {
+            const int k = kb0 * SP_BK + i;
+            s_gamma[i] = k < K ? gamma[k] : 0.f;
+            s_beta[i] = k < K ? beta[k] : 0.f;
+        }
+    }
+    pdl_launch_dependents();
+    pdl_wait();                                    // the rows of X, the residual and the positions are ready
+
+    // pieces of the tile that this warp will finish: (row m, 32-column segment), dealt to the 4·splits
+    // epilogue warps of the cluster; what the first two need from global memory is fetched now
+    const int gw = split * 4 + warp;
+    float pre_res[2] = {0.f, 0.f}, pre_bias[2] = {0.f, 0.f};
+
+    if (warp == 4) {
+        if (lane == 0) {
+            if (!LN)
+                for (int i = 0; i < first; ++i)
+                    tma_load_2d(b_tiles + (size_t)i * B_BYTES, &tmap_x, (kb0 + i) * SP_BK, 0, &full[i]);
+            for (int i = first; i < n_kb; ++i) {
+                const int s = i % stages;
+                if (!tbar_wait_or_abort(&empty[s], (uint32_t)((i / stages - 1) & 1), s_abort)) { atomicExch(s_abort, 1); break; }
+                tbar_expect_tx(&full[s], a_bytes + (LN ? 0 : B_BYTES));
+                tma_load_2d(a_tiles + (size_t)s * a_bytes, &tmap_w, (kb0 + i) * SP_BK, n0, &full[s]);
+                if (!LN) tma_load_2d(b_tiles + (size_t)s * B_BYTES, &tmap_x, (kb0 + i) * SP_BK, 0, &full[s]);
+            }
+        }
+    } else if (warp == 5) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16(128, BN);
+            bool ok = true;
+            if (LN && !tbar_wait_or_abort(x_ready, 0, s_abort)) { atomicExch(s_abort, 1); ok = false; }
+            for (int i = 0; i < n_kb && ok; ++i) {
+                const int s = i % stages;
+                if (!tbar_wait_or_abort(&full[s], (uint32_t)((i / stages) & 1), s_abort)) { atomicExch(s_abort, 1); ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t da = umma_desc_k128(a_tiles + (size_t)s * a_bytes);
+                const uint64_t db = umma_desc_k128(b_tiles + (size_t)(LN ? i : s) * B_BYTES);
+#pragma unroll
+                for (int k = 0; k < SP_BK / 16; ++k)
+                    umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                umma_commit(&empty[s]);
+            }
+            if (ok) umma_commit(acc_full);
+        }
+    } else {
+        if (LN) {
+            asm volatile("bar.sync 2, 256;" ::: "memory");     // the norm's weights are in shared memory
+            const int k_lo = kb0 * SP_BK, k_hi = kb1 * SP_BK;
+            const int G = (K + 31) >> 5;                       // 32-column segments of a row
+            for (int m = lw; m < M; m += 8) {
+                const float* row = Xf + (size_t)m * ldx;
+                // this CTA's k range of the row: requested first, used after the statistics
+                float4 v[SP_LN_MAX_KB / 2];
+#pragma unroll
+                for (int j = 0; j < SP_LN_MAX_KB / 2; ++j) {
+                    const int i = k_lo + (j * 32 + lane) * 4;
+                    v[j] = (i < k_hi && i < K) ? *reinterpret_cast<const float4*>(row + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+                // The row's mean and variance from the per-segment sums that the kernel which wrote the row
+                // left: sum and squared deviation from the segment's own mean; segments combine exactly
+                // (M2 = Σ M2_g + n_g·(mean_g − mean)²), in a fixed order.
+                const float* st = stats_in + (size_t)m * G * 2;
+                float sg[SP_STAT_SEGS / 32], qg[SP_STAT_SEGS / 32];
+                float s = 0.f;
+#pragma unroll
+                for (int j = 0; j < SP_STAT_SEGS / 32; ++j) {
+                    const int g = j * 32 + lane;
+                    sg[j] = 0.f; qg[j] = 0.f;
+                    if (g < G) { const float2 t2 = *reinterpret_cast<const float2*>(st + 2 * g); sg[j] = t2.x; qg[j] = t2.y; }
+                    s += sg[j];
+                }
+                const float mean = warp_sum(s) / (float)K;
+                float q = 0.f;
+#pragma unroll
+                for (int j = 0; j < SP_STAT_SEGS / 32; ++j) {
+                    const int g = j * 32 + lane;
+                    if (g < G) {
+                        const float n_g = (float)min(32, K - g * 32);
+                        const float dm = sg[j] / n_g - mean;
+                        q += qg[j] + n_g * dm * dm;
+                    }
+                }
+                const float inv = 1.f / sqrtf(warp_sum(q) / (float)K + eps);
+                // normalised, in the swizzled layout of a TMA tile; columns beyond K are zeros (W reads as
+                // zeros there too)
+#pragma unroll
+                for (int j = 0; j < SP_LN_MAX_KB / 2; ++j) {
+                    const int kl = (j * 32 + lane) * 4;
+                    const int i = k_lo + kl;
+                    if (i < k_hi) {
+                        uint2 pk = make_uint2(0u, 0u);
+                        if (i < K) {
+                            const float4 gm = *reinterpret_cast<const float4*>(s_gamma + kl);
+                            const float4 bt = *reinterpret_cast<const float4*>(s_beta + kl);
+                            pk.x = pack2((v[j].x - mean) * inv * gm.x + bt.x, (v[j].y - mean) * inv * gm.y + bt.y);
+                            pk.y = pack2((v[j].z - mean) * inv * gm.z + bt.z, (v[j].w - mean) * inv * gm.w + bt.w);
+                        }
+                        unsigned char* dst = b_tiles + (size_t)(kl >> 6) * B_BYTES + m * 128 + ((((kl & 63) >> 3) ^ (m & 7)) << 4) + (kl & 7) * 2;
+                        *reinterpret_cast<uint2*>(dst) = pk;
+                    }
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the MMA reads these through the async proxy
+            __syncwarp();
+            if (lane == 0) tbar_arrive(x_ready);
+        }
+        if (warp < 4) {
+            if (kv.Kc != nullptr && (int)threadIdx.x < 64) {
+                const int m = threadIdx.x;
+                int blk = -2, row = 0;                          // −2: nothing to write for this row
+                if (m < M) {
+                    const int slot = kv.tok_slot[m];
+                    if (slot >= 0) {
+                        const int pos = kv.tok_pos[m];
+                        blk = kv.block_table[(size_t)slot * kv.max_blocks + pos / kv.BT];
+                        row = pos % kv.BT;
+                        if (blk < 0 && tile == 0 && split == 0) atomicOr(dev_err, VLRF_DEVERR_NO_BLOCK);
+                    }
+                }
+                s_kv_blk[m] = blk;
+                s_kv_row[m] = row;
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int u = gw + j * ustride;
+                if (u < units) {
+                    const int m = u / segs, n = n0 + (u % segs) * 32 + lane;
+                    if (n < N) {
+                        if (residual) pre_res[j] = residual[(size_t)m * ldy + n];
+                        if (bias) pre_bias[j] = bias[n];
+                    }
+                }
+            }
+        }
+        if (warp < 4) {
+            const bool have = !*(volatile int*)s_abort && tbar_wait_or_abort(acc_full, 0, s_abort);
+            if (!have) atomicExch(s_abort, 1);
+            float r[BN];
+#pragma unroll
+            for (int m = 0; m < BN; ++m) r[m] = 0.f;
+            if (have && warp * 32 < bm) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
+#pragma unroll
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    uint32_t t[16];
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+                        : "=r"(t[0]), "=r"(t[1]), "=r"(t[2]), "=r"(t[3]), "=r"(t[4]), "=r"(t[5]), "=r"(t[6]), "=r"(t[7]),
+                          "=r"(t[8]), "=r"(t[9]), "=r"(t[10]), "=r"(t[11]), "=r"(t[12]), "=r"(t[13]), "=r"(t[14]), "=r"(t[15])
+                        : "r"(taddr + (uint32_t)c0));
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) r[c0 + j] = __uint_as_float(t[j]);
+                }
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            }
+            if (warp * 32 < bm) {
+#pragma unroll
+                for (int m = 0; m < BN; ++m)
+                    if (m < M) part[m * bm + warp * 32 + lane] = r[m];
+            }
+        }
+    }
+    __syncwarp();
+    cluster_sync_all();                                        // every part of the tile is in shared memory
+    if (warp < 4 && !*(volatile int*)s_abort) {
+        int j = 0;
+        for (int u = gw; u < units; u += ustride, ++j) {
+            const int m = u / segs, colw = (u % segs) * 32 + lane;
+            const int n = n0 + colw;
+            const uint32_t own = tsm(part + m * bm + colw);
+            float v[SP_MAX_SPLITS];
+#pragma unroll
+            for (int s = 0; s < SP_MAX_SPLITS; ++s) v[s] = s < splits ? ld_cluster_f32(own, (uint32_t)s) : 0.f;
+            float acc = v[0];
+#pragma unroll
+            for (int s = 1; s < SP_MAX_SPLITS; ++s) acc += v[s];    // always in the order of the parts
+            float res = 0.f, bv = 0.f;
+            if (n < N) {
+                if (j < 2) { res = j == 0 ? pre_res[0] : pre_res[1]; bv = j == 0 ? pre_bias[0] : pre_bias[1]; }
+                else { res = residual ? residual[(size_t)m * ldy + n] : 0.f; bv = bias ? bias[n] : 0.f; }
+            }
+            const float y = apply_act_rt(acc + bv, act) + res;
+            if (n < N) ElemIO<OT>::store(Y + (size_t)m * ldy + n, y);
+            if (stats_out != nullptr) {
+                // what a LayerNorm of these rows will need: this segment's sum and squared deviation from its
+                // own mean (of the values as stored)
+                const int seg0 = n0 + (u % segs) * 32;
+                if (seg0 < N) {
+                    const float yv = n < N ? y : 0.f;          // (statistics are kept of float32 rows only)
+                    const float sum = warp_sum(yv);
+                    const float d = n < N ? yv - sum / (float)min(32, N - seg0) : 0.f;
+                    const float m2 = warp_sum(d * d);
+                    if (lane == 0) {
+                        float* so = stats_out + ((size_t)m * ((N + 31) >> 5) + (seg0 >> 5)) * 2;
+                        so[0] = sum; so[1] = m2;
+                    }
+                }
+            }
+            if (n >= N) continue;
+            if (kv.Kc != nullptr && n >= kv.k_off) {
+                const bool is_v = n >= kv.v_off;
+                const int c = n - (is_v ? kv.v_off : kv.k_off);
+                const int blk = s_kv_blk[m];
+                if (c < kv.width && blk >= 0) {
+                    const int hh = c / kv.dh, cc = c - hh * kv.dh;
+                    __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(is_v ? kv.Vc : kv.Kc);
+                    base[(((size_t)blk * kv.Hkv + hh) * kv.BT + s_kv_row[m]) * kv.dh + cc] = __float2bfloat16_rn(y);
+                }
+            }
+        }
+    }
+    __syncwarp();
+    cluster_sync_relaxed();                                    // nobody leaves while its shared memory is being read
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (warp == 4) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
+    }
+    if (threadIdx.x == 0 && *s_abort) atomicOr(dev_err, VLRF_DEVERR_WAIT_TIMEOUT);
+}
+
+int sp_sm_count() {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0, v = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+        sms = v > 0 ? v : 148;
+    }
+    return sms;
+}
+
+struct SpPlan { int bm, tiles, splits, kb_cap, stages; size_t smem; };
+
+size_t sp_smem(int bm, int bn, bool ln, int stages, int kb_cap, int M, int splits) {
+    const size_t ring = (size_t)stages * bm * 128;
+    (void)splits;
+    const size_t part = (size_t)M * bm * sizeof(float);
+    return 1024 + ring + part + (bm == 64 ? 8192 : 0) + (size_t)(ln ? kb_cap : stages) * bn * 128 +
+           (ln ? (size_t)kb_cap * SP_BK * 8 : 0) + (2 * SP_MAX_STAGES + 2) * 8 + 16 + 128 * sizeof(int);
+}
+
+// Tile height, number of parts and ring depth: about one CTA per SM (so that the next product's CTAs find
+// room to fetch ahead), at least one k block a part, at most the largest cluster; 64-row tiles where they
+// give half as many CTAs again as 128-row tiles.
+SpPlan sp_plan(int M, int N, int K, int bn, bool ln) {
+    const int n_kb = (K + SP_BK - 1) / SP_BK;
+    int target = sp_sm_count();
+    int force_bm = 0, max_splits = SP_MAX_SPLITS;
+    size_t budget = SP_SMEM_BUDGET;
+    if (const char* e = getenv("VLRF_SPLITK_PLAN")) {            // experiment hook: "ctas,bm,max splits,smem KiB"
+        int a = 0, b = 0, c = 0, d = 0;
+        if (sscanf(e, "%d,%d,%d,%d", &a, &b, &c, &d) >= 1) {
+            if (a > 0) target = a;
+            if (b == 64 || b == 128) force_bm = b;
+            if (c > 0 && c <= SP_MAX_SPLITS) max_splits = c;
+            if (d > 0 && d <= 200) budget = (size_t)d * 1024;
+        }
+    }
+    SpPlan best{};
+    int best_ctas = -1;
+    for (int bm = 128; bm >= 64; bm -= 64) {
+        if (force_bm && bm != force_bm) continue;
+        const int tiles = (N + bm - 1) / bm;
+        int splits = (target + tiles / 2) / tiles;
+        if (splits > max_splits) splits = max_splits;
+        if (splits > n_kb) splits = n_kb;
+        if (splits < 1) splits = 1;
+        const int kb_cap = (n_kb + splits - 1) / splits;
+        int stages = kb_cap < SP_MAX_STAGES ? kb_cap : SP_MAX_STAGES;
+        while (stages > 1 && sp_smem(bm, bn, ln, stages, kb_cap, M, splits) > budget) --stages;
+        const int ctas = tiles * splits;
+        const int useful = ctas < target ? ctas : target;
+        if (best_ctas < 0 || useful * 2 >= best_ctas * 3) {      // 64-row tiles only for half as many CTAs again
+            best = SpPlan{bm, tiles, splits, kb_cap, stages, sp_smem(bm, bn, ln, stages, kb_cap, M, splits)};
+            best_ctas = useful;
+        }
+    }
+    return best;
+}
+
+template <int BN, typename OT, bool LN>
+int launch_sp(const void* X, const void* W, const float* gamma, const float* beta, float eps, const float* bias,
+              const float* residual, void* Y, int M, int N, int K, int ldx, int ldy, int act, const SpKvScatter& kv,
+              const float* stats_in, float* stats_out, int* dev_err, cudaStream_t stream) {
+    const SpPlan plan = sp_plan(M, N, K, BN, LN);
+    VLRF_REQUIRE(plan.smem <= 200 * 1024, "gemm_splitk: %zu bytes of shared memory", plan.smem);
+    CUtensorMap tw, tx;
+    int st = vlrf_make_tmap_bf16(W, N, K, K, plan.bm, SP_BK, &tw);
+    if (st != VLRF_OK) return st;
+    if (!LN) {
+        st = vlrf_make_tmap_bf16(X, M, K, ldx, BN, SP_BK, &tx);
+        if (st != VLRF_OK) return st;
+    } else {
+        tx = tw;   // unused
+    }
+    auto kern = gemm_splitk_kernel<BN, OT, LN>;
+    static bool clusters_allowed = false;
+    if (!clusters_allowed) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "gemm_splitk: large clusters: %s", cudaGetErrorString(e));
+        clusters_allowed = true;
+    }
+    static size_t allowed = 48 * 1024;
+    if (plan.smem > allowed) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem);
+        if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "gemm_splitk: %zu bytes of shared memory: %s", plan.smem, cudaGetErrorString(e));
+        allowed = plan.smem;
+    }
+    cudaError_t e = launch_chained_cluster(kern, dim3(plan.tiles, plan.splits), dim3(LN ? SP_THREADS_LN : SP_THREADS), plan.smem,
+                                           plan.splits, stream, tw, tx, (const float*)X, ldx, gamma, beta, eps, bias, residual,
+                                           (OT*)Y, M, N, K, ldy, act, plan.bm, plan.stages, plan.kb_cap, kv, stats_in, stats_out,
+                                           dev_err);
+    if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "gemm_splitk: %s", cudaGetErrorString(e));
+    return vlrf_check_launch("gemm_splitk");
+}
+}  // namespace
+
+// Floats of the statistics of `rows` rows of `width` columns.
+extern "C" long long vlrf_row_stats_floats(int rows, int width) { return (long long)rows * ((width + 31) / 32) * 2; }
+
+// Whether this kernel takes the shape.  x_is_f32_ln: X is float32 and LayerNorm is applied to it first.
+extern "C" int vlrf_gemm_splitk_takes(int M, int N, int K, int ldx, int x_is_f32_ln) {
+    if (M < 1 || M > 64 || N < 1 || K < 8 || K % 8 != 0) return 0;
+    if (x_is_f32_ln) {
+        if (ldx % 4 != 0 || M > 16 || (K + 31) / 32 > SP_STAT_SEGS) return 0;
+        return sp_plan(M, N, K, 16, true).kb_cap <= SP_LN_MAX_KB ? 1 : 0;
+    }
+    return ldx % 8 == 0 ? 1 : 0;
+}
+
+extern "C" int vlrf_gemm_splitk(const void* X, int x_is_f32_ln, const void* W, const float* bias, const float* residual,
+                                void* Y, int out_dtype, int M, int N, int K, int ldx, int ldy, int act,
+                                const float* gamma, const float* beta, float eps,
+                                // optional scatter of K/V columns into the cache (Kc == nullptr: none)
+                                void* Kc, void* Vc, const int* block_table, int max_blocks, const int* tok_slot,
+                                const int* tok_pos, int k_off, int v_off, int Hkv, int dh, int BT,
+                                // x_is_f32_ln: the row statistics of X, [M][ceil(K/32)][2]; stats_out (or null):
+                                // the same for the rows of Y, [M][ceil(N/32)][2], for a later product to use
+                                const float* stats_in, float* stats_out, int* dev_err, cudaStream_t stream) {
+    VLRF_REQUIRE(vlrf_gemm_splitk_takes(M, N, K, ldx, x_is_f32_ln), "gemm_splitk: does not take M=%d N=%d K=%d ldx=%d", M, N, K, ldx);
+    VLRF_REQUIRE(ldx >= K && ldy >= N && act >= 0 && act <= 2, "gemm_splitk: bad arguments");
+    VLRF_REQUIRE(dev_err != nullptr, "gemm_splitk: needs the device error word");
+    VLRF_REQUIRE(!x_is_f32_ln || (gamma && beta && stats_in), "gemm_splitk: the fused LayerNorm needs weight, bias and the rows' statistics");
+    VLRF_REQUIRE(stats_out == nullptr || ((N + 31) / 32 <= SP_STAT_SEGS && out_dtype == VLRF_F32),
+                 "gemm_splitk: statistics are kept of float32 rows of at most %d columns", SP_STAT_SEGS * 32);
+    VLRF_REQUIRE(out_dtype == VLRF_BF16 || out_dtype == VLRF_F32, "gemm_splitk: unknown output dtype %d", out_dtype);
+    SpKvScatter kv{};
+    if (Kc != nullptr) {
+        VLRF_REQUIRE(Vc && block_table && tok_slot && tok_pos && Hkv > 0 && dh > 0 && BT > 0 && max_blocks > 0,
+                     "gemm_splitk: incomplete cache scatter arguments");
+        VLRF_REQUIRE(out_dtype == VLRF_BF16, "gemm_splitk: the cache scatter writes bfloat16");
+        kv = SpKvScatter{Kc, Vc, block_table, tok_slot, tok_pos, max_blocks, k_off, v_off, Hkv * dh, dh, Hkv, BT};
+    }
+#define SP_GO(BNV, LNV)                                                                                                  \
+    return out_dtype == VLRF_BF16                                                                                        \
+               ? launch_sp<BNV, __nv_bfloat16, LNV>(X, W, gamma, beta, eps, bias, residual, Y, M, N, K, ldx, ldy, act, kv, stats_in, stats_out, dev_err, stream) \
+               : launch_sp<BNV, float, LNV>(X, W, gamma, beta, eps, bias, residual, Y, M, N, K, ldx, ldy, act, kv, stats_in, stats_out, dev_err, stream)
+    if (x_is_f32_ln) { SP_GO(16, true); }
+    if (M <= 16) { SP_GO(16, false); }
+    if (M <= 32) { SP_GO(32, false); }
+    SP_GO(64, false);
+#undef SP_GO
+}

@@ -53,6 +53,7 @@ def embed(wte, wpe, tokens, positions, out, dev_err) -> None:
             raise KernelError("embed: position table or positions do not match")
     if out.shape[0] < T or out.shape[1] != d:
         raise KernelError("embed: output does not match")
+    _written(out)
     call("vlrf_embed", _ptr(wte), _ptr(wpe), dtype_code(wte.dtype), _ptr(tokens), _ptr(positions), _ptr(out),
          T, d, V, P, _ptr(dev_err), _stream())
 
@@ -68,6 +69,7 @@ def layernorm(x, gamma, beta, eps: float, out, rows=None) -> None:
         n = rows.shape[0]
     if gamma.shape[0] != d or beta.shape[0] != d or out.shape[1] != d or out.shape[0] < n:
         raise KernelError("layernorm: sizes do not match")
+    _written(out)
     call("vlrf_layernorm", _ptr(x), _ptr(rows), _ptr(gamma), _ptr(beta), _ptr(out), dtype_code(out.dtype), n, d,
          float(eps), _stream())
 
@@ -93,6 +95,7 @@ def linear(x, w, bias, out, *, act=None, residual=None, rows: int | None = None,
             raise KernelError("linear: residual does not match")
     if x.dtype == torch.float32 and out.dtype != torch.float32:
         raise KernelError("linear: float32 input gives float32 output")
+    _written(out)
     return _linear_dispatch(x, w, bias, out, ACT[act], residual, M, N, K, kv_scatter)
 
 
@@ -101,7 +104,60 @@ USE_TCGEN05 = True
 SKINNY_MAX_ROWS = 64
 FUSED_NORM_MAX_ROWS = 16
 SWAPPED_MIN_COLUMNS = 16384
+#: Few-row products whose weight matrix has at least this many bytes go to the split-k tcgen05 kernel; below
+#: that the whole product is a handful of latencies, and the kernel whose CTAs need no cluster is as fast.
+#: With the LayerNorm fused in, the split-k kernel wins only for larger matrices (measured on B200).
+SPLITK_MIN_WEIGHT_BYTES = 3 << 20
+SPLITK_NORM_MIN_WEIGHT_BYTES = 12 << 20
 _DEV_ERR = None
+
+
+#: Row statistics of the float32 residual rows that a product has just written (per row and 32-column
+#: segment: sum and squared deviation from the segment's mean), kept so that the next product can apply a
+#: LayerNorm to those rows without reading them whole.  One buffer of fixed address (graphs capture it);
+#: `_ROW_STATS_OF` says whose rows it describes: (the tensor, its torch version counter then, rows, width) or
+#: None.  The tensor is held, so its memory cannot be given to another tensor meanwhile.
+ROW_STATS_MAX_ROWS, ROW_STATS_MAX_WIDTH = 64, 8192
+_ROW_STATS = None
+_ROW_STATS_OF = None
+
+
+def _row_stats_buffer() -> torch.Tensor:
+    global _ROW_STATS
+    if _ROW_STATS is None:
+        _ROW_STATS = torch.zeros(ROW_STATS_MAX_ROWS * (ROW_STATS_MAX_WIDTH // 32) * 2, dtype=torch.float32, device="cuda")
+    return _ROW_STATS
+
+
+def _written(t) -> None:
+    """Every function here that writes a tensor says so: statistics kept of it are stale then."""
+    global _ROW_STATS_OF
+    if _ROW_STATS_OF is not None and t is not None and _ROW_STATS_OF[0].data_ptr() == t.data_ptr():
+        _ROW_STATS_OF = None
+
+
+def residual_written(t) -> None:
+    """For code that changes residual rows with kernels of its own (torch's in-place operations are seen
+    without this): forget what is known about those rows."""
+    _written(t)
+
+
+def _row_stats_of(x, rows: int, width: int):
+    """The statistics buffer if it describes exactly these rows as they are now, else None."""
+    if _ROW_STATS_OF is None:
+        return None
+    held, version, n_rows, n_cols = _ROW_STATS_OF
+    if held.data_ptr() == x.data_ptr() and x._version == version and (n_rows, n_cols) == (rows, width):
+        return _ROW_STATS
+    return None
+
+
+def _splitk_takes(M: int, N: int, K: int, ldx: int, fused_norm: bool) -> bool:
+    least = SPLITK_NORM_MIN_WEIGHT_BYTES if fused_norm else SPLITK_MIN_WEIGHT_BYTES
+    if not USE_TCGEN05 or 2 * N * K < least or N >= SWAPPED_MIN_COLUMNS:
+        return False
+    from . import library
+    return bool(library().vlrf_gemm_splitk_takes(M, N, K, ldx, 1 if fused_norm else 0))
 
 
 def _dev_err() -> torch.Tensor:
@@ -163,6 +219,17 @@ def _linear_dispatch(x, w, bias, out, act, residual, M, N, K, kv_scatter=None) -
         call("vlrf_gemm_tcgen05", _ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), M, N, K, K, N,
              dtype_code(out.dtype), act, *_kv_args(None, N), _ptr(_dev_err()), _stream())
         return False
+    if x.dtype == torch.bfloat16 and M <= SKINNY_MAX_ROWS and _splitk_takes(M, N, K, K, False):
+        # few rows, a large matrix: tiles of w on the tensor cores, the sum over k cut into parts
+        scatter = kv_scatter is not None and bf16_out
+        keep = not bf16_out and M <= ROW_STATS_MAX_ROWS and N <= ROW_STATS_MAX_WIDTH
+        call("vlrf_gemm_splitk", _ptr(x), 0, _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), dtype_code(out.dtype),
+             M, N, K, K, N, act, 0, 0, 0.0, *_kv_args(kv_scatter if scatter else None, N), 0,
+             _ptr(_row_stats_buffer()) if keep else 0, _ptr(_dev_err()), _stream())
+        if keep:
+            global _ROW_STATS_OF
+            _ROW_STATS_OF = (out, out._version, M, N)
+        return scatter
     if x.dtype == torch.bfloat16 and M <= SKINNY_MAX_ROWS and K % 32 == 0:
         # few rows: the product is bound by streaming w once
         scatter = kv_scatter is not None and bf16_out
@@ -205,6 +272,13 @@ def linear_layernorm(x, gamma, beta, eps: float, w, bias, out, *, act=None, rows
     if bias is not None:
         _dev(bias, "bias", torch.float32)
     kv = _kv_args(kv_scatter, N)
+    stats = _row_stats_of(x, M, K)
+    _written(out)
+    if stats is not None and _splitk_takes(M, N, K, K, True):
+        # the rows' statistics are at hand: each CTA normalises only the columns it multiplies
+        call("vlrf_gemm_splitk", _ptr(x), 1, _ptr(w), _ptr(bias), 0, _ptr(out), dtype_code(out.dtype), M, N, K, K, N,
+             ACT[act], _ptr(gamma), _ptr(beta), float(eps), *kv, _ptr(stats), 0, _ptr(_dev_err()), _stream())
+        return
     call("vlrf_gemm_skinny", _ptr(x), 1, _ptr(w), _ptr(bias), 0, _ptr(out), dtype_code(out.dtype), M, N, K, K, N,
          ACT[act], _ptr(gamma), _ptr(beta), float(eps), *kv, sm_count(), _ptr(_dev_err()), _stream())
 
@@ -234,6 +308,7 @@ def attention_decode(qkv, q_off: int, k_cache, v_cache, block_table, tok_slot, t
         _dev(partials, "partials", torch.float32); _dev(counters, "counters", torch.int32)
         if partials.numel() < n_rows * n_heads * n_split * (head_dim + 2) or counters.numel() < n_rows * n_heads:
             raise KernelError("attention_decode: scratch is too small")
+    _written(out)
     call("vlrf_attn_decode", _ptr(qkv), dtype_code(qkv.dtype), qkv.shape[1], q_off, _ptr(k_cache), _ptr(v_cache),
          _ptr(block_table), block_table.shape[1], _ptr(tok_slot), _ptr(tok_pos), _ptr(out), out.shape[1], n_rows,
          n_heads, n_kv_heads, head_dim, bt, float(scale), int(window), int(n_split), _ptr(partials), _ptr(counters),
@@ -274,6 +349,7 @@ def attention_generic(qkv, q_off: int, k_cache, v_cache, block_table, tok_slot, 
         raise KernelError("attention: output does not match")
     if q_off + n_heads * head_dim > qkv.shape[1]:
         raise KernelError("attention: Q columns lie outside the row")
+    _written(out)
     call("vlrf_attn_generic", _ptr(qkv), dtype_code(qkv.dtype), qkv.shape[1], q_off, _ptr(k_cache), _ptr(v_cache),
          _ptr(block_table), block_table.shape[1], _ptr(tok_slot), _ptr(tok_pos), _ptr(out), out.shape[1],
          n_tokens, n_heads, n_kv_heads, head_dim, bt, float(scale), int(window), _ptr(dev_err), _stream())
@@ -344,6 +420,7 @@ def attention_prefill(qkv, q_off: int, k_cache, v_cache, block_table, seq_slot, 
         raise KernelError("attention_prefill: output does not match")
     if seq_slot.shape[0] < n_seqs or seq_start.shape[0] < n_seqs + 1 or seq_pos0.shape[0] < n_seqs:
         raise KernelError("attention_prefill: sequence tables are too short")
+    _written(out)
     call("vlrf_attn_prefill", _ptr(qkv), qkv.shape[1], q_off, _ptr(k_cache), _ptr(v_cache), nb, _ptr(block_table),
          block_table.shape[1], _ptr(seq_slot), _ptr(seq_start), _ptr(seq_pos0), _ptr(out), out.shape[1], n_tokens, n_seqs,
          max_new, n_heads, n_kv_heads, head_dim, bt, float(scale), int(window), _ptr(dev_err), _stream())
