@@ -161,6 +161,131 @@ def test_fused_projection_writes_keys_and_values_into_the_cache():
     assert written == 4 * Hkv * dh                                   # nothing else was touched
 
 
+@pytest.fixture
+def split_k_always(monkeypatch):
+    """Send every few-row bfloat16 product to the split-k tensor-core kernel, whatever its size."""
+    from vlrf_b200.csrc import ops
+    monkeypatch.setattr(ops, "SPLITK_MIN_WEIGHT_BYTES", 0)
+    monkeypatch.setattr(ops, "SPLITK_NORM_MIN_WEIGHT_BYTES", 0)
+    return ops
+
+
+# few and many tiles, one and many parts, 64- and 128-row tiles, tails in M, N and K
+SPLIT_K_SHAPES = [(1, 200, 72), (8, 512, 256), (16, 1600, 1600), (17, 1000, 320), (33, 136, 200), (64, 768, 3072),
+                  (5, 96, 64), (8, 6400, 1600), (40, 130, 8)]
+
+
+@pytest.mark.parametrize("M,N,K", SPLIT_K_SHAPES)
+@pytest.mark.parametrize("out_dtype,tol", [(torch.float32, None), (torch.bfloat16, 5e-3)])
+@pytest.mark.parametrize("act", [None, "gelu_tanh"])
+def test_linear_split_k(split_k_always, M, N, K, out_dtype, tol, act):
+    ops = split_k_always
+    assert ops._splitk_takes(M, N, K, K, False)
+    tol = tol if tol is not None else f32_sum_tol(K)
+    x, w = randn(M, K, seed=31, dtype=torch.bfloat16), randn(N, K, seed=32, dtype=torch.bfloat16, scale=0.3)
+    bias, res = randn(N, seed=33), randn(M, N, seed=34)
+    want = x.double() @ w.double().T + bias.double()
+    if act == "gelu_tanh":
+        want = plain.gelu_tanh(want)
+    out = torch.full((M + 1, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops.linear(x.to(DEV), w.to(DEV), bias.to(DEV), out, act=act, rows=M)
+    assert rel_err(out[:M].float().cpu(), want) < tol
+    assert torch.isnan(out[M].float()).all()                     # no row beyond M is written
+    if out_dtype == torch.float32:
+        acc = res.clone().to(DEV)
+        ops.linear(x.to(DEV), w.to(DEV), bias.to(DEV), acc, act=act, residual=acc)
+        assert rel_err(acc.cpu(), want + res.double()) < tol
+        again = res.clone().to(DEV)                              # the same again: the sum does not depend on timing
+        ops.linear(x.to(DEV), w.to(DEV), bias.to(DEV), again, act=act, residual=again)
+        assert torch.equal(acc, again)
+    assert ops.device_errors() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 96, 64), (8, 2304, 768), (13, 200, 200), (16, 320, 96), (9, 4800, 1600), (7, 130, 1000)])
+@pytest.mark.parametrize("out_dtype,act", [(torch.bfloat16, None), (torch.bfloat16, "gelu_tanh"), (torch.float32, None)])
+def test_split_k_layernorm_from_row_statistics(split_k_always, M, N, K, out_dtype, act):
+    """A product that writes float32 residual rows leaves their per-segment statistics; the next product
+    normalises with them.  Rows with a large common offset show a variance that is not computed as a
+    deviation from the mean."""
+    ops = split_k_always
+    eps = 1e-5
+    w0, x0 = randn(K, 64, seed=41, dtype=torch.bfloat16), randn(M, 64, seed=42, dtype=torch.bfloat16)
+    x = (randn(M, K, seed=43) * 0.5 + 300.0).to(DEV)             # mean 300, deviation about 8
+    ops.linear(x0.to(DEV), w0.to(DEV), None, x, residual=x)
+    assert ops._row_stats_of(x, M, K) is not None
+    gamma, beta = randn(K, seed=44) * 0.3 + 1, randn(K, seed=45) * 0.2
+    w, b = randn(N, K, seed=46, dtype=torch.bfloat16, scale=0.2), randn(N, seed=47)
+
+    def want_for(rows):
+        h = plain.layer_norm(rows.double().cpu(), gamma.double(), beta.double(), eps).to(torch.bfloat16).double()
+        y = h @ w.double().T + b.double()
+        return plain.gelu_tanh(y) if act == "gelu_tanh" else y
+
+    tol = 6e-3 if out_dtype == torch.bfloat16 else 3e-3
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops.linear_layernorm(x, gamma.to(DEV), beta.to(DEV), eps, w.to(DEV), b.to(DEV), out, act=act)
+    assert rel_err(out.float().cpu(), want_for(x)) < tol
+    # rows changed behind the statistics' back: by torch in place, by a kernel of this library, by a caller's own
+    x.mul_(0.5)
+    assert ops._row_stats_of(x, M, K) is None
+    if ops.can_fuse_layernorm(M, K, torch.bfloat16):             # (the kernel that reads whole rows takes this width)
+        ops.linear_layernorm(x, gamma.to(DEV), beta.to(DEV), eps, w.to(DEV), b.to(DEV), out, act=act)
+        assert rel_err(out.float().cpu(), want_for(x)) < tol
+    ops.linear(x0.to(DEV), w0.to(DEV), None, x, residual=x)
+    assert ops._row_stats_of(x, M, K) is not None
+    ops.embed(randn(50, K, seed=48).to(DEV), None, torch.zeros(M, dtype=torch.int32, device=DEV), None, x,
+              torch.zeros(1, dtype=torch.int32, device=DEV))
+    assert ops._row_stats_of(x, M, K) is None
+    ops.linear(x0.to(DEV), w0.to(DEV), None, x, residual=x)
+    ops.residual_written(x)
+    assert ops._row_stats_of(x, M, K) is None
+    assert ops.device_errors() == 0
+
+
+def test_split_k_projection_writes_keys_and_values_into_the_cache(split_k_always):
+    ops = split_k_always
+    H, Hkv, dh, K, M = 4, 2, 16, 96, 5
+    N = (H + 2 * Hkv) * dh
+    table = torch.tensor([[3, 1], [5, -1], [2, 0]], dtype=torch.int32)
+    slot = torch.tensor([0, 2, -1, 1, 2], dtype=torch.int32)      # row 2 is padding; rows 1 and 4 share slot 2
+    pos = torch.tensor([70, 5, 0, 63, 64], dtype=torch.int32)
+    w, b = randn(N, K, seed=52, dtype=torch.bfloat16, scale=0.2), randn(N, seed=53)
+    for fused_norm in (False, True):
+        kc = torch.full((6, Hkv, 64, dh), float("nan"), dtype=torch.bfloat16, device=DEV)
+        vc = torch.full_like(kc, float("nan"))
+        scatter = (kc, vc, table.to(DEV), slot.to(DEV), pos.to(DEV), H * dh, (H + Hkv) * dh, Hkv, dh)
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+        if fused_norm:
+            x = torch.zeros(M, K, device=DEV)
+            ops.linear(randn(M, 64, seed=54, dtype=torch.bfloat16).to(DEV), randn(K, 64, seed=55, dtype=torch.bfloat16).to(DEV),
+                       None, x)
+            assert ops._row_stats_of(x, M, K) is not None
+            ops.linear_layernorm(x, torch.ones(K, device=DEV), torch.zeros(K, device=DEV), 1e-5, w.to(DEV), b.to(DEV), out,
+                                 kv_scatter=scatter)
+        else:
+            assert ops.linear(randn(M, K, seed=51, dtype=torch.bfloat16).to(DEV), w.to(DEV), b.to(DEV), out, kv_scatter=scatter)
+        o = out.cpu()
+        for m in range(M):
+            if slot[m] < 0:
+                continue
+            blk = int(table[slot[m], pos[m] // 64])
+            assert torch.equal(kc[blk, :, pos[m] % 64].cpu().reshape(-1), o[m, H * dh:(H + Hkv) * dh])
+            assert torch.equal(vc[blk, :, pos[m] % 64].cpu().reshape(-1), o[m, (H + Hkv) * dh:])
+        assert (~torch.isnan(kc.float())).sum().item() == 4 * Hkv * dh     # nothing else was touched
+    assert ops.device_errors() == 0
+
+
+def test_split_k_rows_do_not_depend_on_the_batch(split_k_always):
+    ops = split_k_always
+    x, w, b = randn(64, 320, seed=56, dtype=torch.bfloat16), randn(1000, 320, seed=57, dtype=torch.bfloat16), randn(1000, seed=58)
+    full = torch.empty(64, 1000, device=DEV)
+    ops.linear(x.to(DEV), w.to(DEV), b.to(DEV), full)
+    for rows in (1, 9, 20):
+        few = torch.empty(rows, 1000, device=DEV)
+        ops.linear(x[41:41 + rows].contiguous().to(DEV), w.to(DEV), b.to(DEV), few)
+        assert torch.equal(full[41:41 + rows], few)
+
+
 def test_linear_rows_do_not_depend_on_the_batch():
     from vlrf_b200.csrc import ops
     x, w, b = randn(70, 96, seed=13), randn(200, 96, seed=14), randn(200, seed=15)

@@ -161,8 +161,8 @@ attn_decode_generic_kernel(const ET* __restrict__ qkv, int ld, int q_off, const 
     __shared__ int s_last;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
-    pdl_launch_dependents();                       // the next kernel may start fetching its weights
     pdl_wait();                                    // everything read below was written by earlier kernels
+    pdl_launch_dependents();                       // the next kernel may start fetching its weights
     const int slot = tok_slot[row];
     if (slot < 0) return;                          // padding row: the whole CTA leaves
     const int pos = tok_pos[row];
@@ -264,8 +264,10 @@ attn_decode_bulk_kernel(const ET* __restrict__ qkv, int ld, int q_off, const ET*
     __shared__ int s_bad;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
-    pdl_launch_dependents();                       // the next kernel may start fetching its weights
-    pdl_wait();                                    // everything read below was written by earlier kernels
+    // Before the wait: positions, tables and the cache of earlier positions come from kernels before the one
+    // ahead (every kernel lets its successor begin only after its own wait), so the first chunks of keys and
+    // values are requested at once.  Only the chunk that holds the new position is written by the kernel
+    // ahead; it is requested after the wait, like the query.
     const int slot = tok_slot[row];
     if (slot < 0) return;                          // padding row: the whole CTA leaves
     const int pos = tok_pos[row];
@@ -278,6 +280,7 @@ attn_decode_bulk_kernel(const ET* __restrict__ qkv, int ld, int q_off, const ET*
     const int per_split = (n_chunks + n_split - 1) / n_split;
     const int c_begin = chunk0 + split * per_split;
     const int c_end = min(chunk0 + n_chunks, c_begin + per_split);
+    const int c_new = pos / 32;                    // the chunk with the key that the kernel ahead writes
     const int* table = block_table + (size_t)slot * max_blocks;
 
     if (threadIdx.x == 0) {
@@ -285,6 +288,26 @@ attn_decode_bulk_kernel(const ET* __restrict__ qkv, int ld, int q_off, const ET*
         for (int i = 0; i < CH_MAX; ++i) dmbar_init(&bars[i], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    __syncthreads();
+    // thread i requests chunk r0 + i of a round into buffer i
+    auto request = [&](int r0) -> bool {
+        const int k0 = (r0 + threadIdx.x) * 32;
+        const int blk = table[k0 / BT];
+        if (blk < 0) {
+            atomicOr(dev_err, VLRF_DEVERR_NO_BLOCK);
+            s_bad = 1;
+            return false;
+        }
+        const size_t base = (((size_t)blk * Hkv + hk) * BT + (k0 % BT)) * DH;
+        dmbar_expect_tx(&bars[threadIdx.x], 2 * CHUNK_BYTES);
+        dbulk_g2s(kbuf + (size_t)threadIdx.x * CHUNK_BYTES, Kc + base, CHUNK_BYTES, &bars[threadIdx.x]);
+        dbulk_g2s(vbuf + (size_t)threadIdx.x * CHUNK_BYTES, Vc + base, CHUNK_BYTES, &bars[threadIdx.x]);
+        return true;
+    };
+    bool issued = false;
+    if ((int)threadIdx.x < min(CH_MAX, c_end - c_begin) && c_begin + (int)threadIdx.x != c_new) issued = request(c_begin);
+    pdl_wait();                                    // the new key and value and the query are written
+    pdl_launch_dependents();
     // this lane's piece of the query, scaled
     float q[E];
     {
@@ -292,7 +315,6 @@ attn_decode_bulk_kernel(const ET* __restrict__ qkv, int ld, int q_off, const ET*
 #pragma unroll
         for (int j = 0; j < E; ++j) q[j] = ElemIO<ET>::load(qsrc + j) * scale;
     }
-    __syncthreads();
 
     float acc[E];
 #pragma unroll
@@ -302,22 +324,11 @@ attn_decode_bulk_kernel(const ET* __restrict__ qkv, int ld, int q_off, const ET*
     uint32_t parity = 0;
     for (int r0 = c_begin; r0 < c_end; r0 += CH_MAX) {
         const int n_here = min(CH_MAX, c_end - r0);
-        bool issued = false;
-        if (r0 > c_begin) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // reads of the buffers before refilling them
-        if ((int)threadIdx.x < n_here) {
-            const int k0 = (r0 + threadIdx.x) * 32;
-            const int blk = table[k0 / BT];
-            if (blk < 0) {
-                atomicOr(dev_err, VLRF_DEVERR_NO_BLOCK);
-                s_bad = 1;
-            } else {
-                const size_t base = (((size_t)blk * Hkv + hk) * BT + (k0 % BT)) * DH;
-                dmbar_expect_tx(&bars[threadIdx.x], 2 * CHUNK_BYTES);
-                dbulk_g2s(kbuf + (size_t)threadIdx.x * CHUNK_BYTES, Kc + base, CHUNK_BYTES, &bars[threadIdx.x]);
-                dbulk_g2s(vbuf + (size_t)threadIdx.x * CHUNK_BYTES, Vc + base, CHUNK_BYTES, &bars[threadIdx.x]);
-                issued = true;
-            }
+        if (r0 > c_begin) {
+            issued = false;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // reads of the buffers before refilling them
         }
+        if ((int)threadIdx.x < n_here && (r0 > c_begin || r0 + (int)threadIdx.x == c_new)) issued = request(r0);
         __syncthreads();                           // s_bad is known
         if (s_bad) {                               // leave only after the copies already issued have landed
             if (issued) {

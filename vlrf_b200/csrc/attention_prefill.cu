@@ -91,8 +91,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int qt = blockIdx.x, h = blockIdx.y, seq = blockIdx.z;
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     const int row0 = seq_start[seq], n_new = seq_start[seq + 1] - row0;
     if (qt * PF_BQ >= n_new) return;                 // uniform: this sequence has fewer query tiles
     const int slot = seq_slot[seq];

@@ -39,8 +39,10 @@ int vlrf_check_launch(const char* what);
 // before it on the stream is still running.  It may do only what does not depend on that kernel (set up
 // shared memory, start fetching weights) until `pdl_wait()` returns, which happens once every earlier
 // kernel has finished and its writes are visible.  `pdl_launch_dependents()` lets the next kernel begin in
-// the same way.  Every kernel of the step calls both, so that the chain never lets a kernel overtake data
-// it needs.  `vlrf_set_chained_launch(0)` turns the launch attribute off (the calls then do nothing).
+// the same way.  Every kernel of the step calls both, the wait first: so when a kernel begins, everything
+// before the kernel ahead of it is complete, and it may already read what those wrote (cache blocks of
+// earlier positions, positions, tables), but nothing that the kernel ahead writes.
+// `vlrf_set_chained_launch(0)` turns the launch attribute off (the calls then do nothing).
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 extern "C" int vlrf_chained_launch_enabled();

@@ -12,8 +12,8 @@ __global__ void embed_pos_kernel(const WT* __restrict__ wte, const WT* __restric
                                  const int* __restrict__ tokens, const int* __restrict__ positions,
                                  float* __restrict__ x, int d, int V, int P, int* __restrict__ dev_err) {
     const int t = blockIdx.x;
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     int tok = tokens[t];
     if (tok < 0 || tok >= V) {
         if (threadIdx.x == 0) atomicOr(dev_err, VLRF_DEVERR_TOKEN_RANGE);
@@ -76,8 +76,8 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
     float* row = smem;          // d floats
     float* red = smem + d;      // 32 floats
     const int r = blockIdx.x;
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     const float* src = x + (size_t)(rows ? rows[r] : r) * d;
     float s = 0.f;
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
@@ -107,8 +107,8 @@ __global__ void __launch_bounds__(256) layernorm_warp_kernel(const float* __rest
                                                               int n_rows, int d, float eps) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = blockIdx.x * 8 + warp;
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     if (r >= n_rows) return;
     const float4* src = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * d);
     const int nv = d >> 2;                       // float4s in the row

@@ -142,8 +142,8 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             s_beta[i] = k < K ? beta[k] : 0.f;
         }
     }
-    pdl_launch_dependents();
     pdl_wait();                                    // the rows of X, the residual and the positions are ready
+    pdl_launch_dependents();
 
     // pieces of the tile that this warp will finish: (row m, 32-column segment), dealt to the 4·splits
     // epilogue warps of the cluster; what the first two need from global memory is fetched now

@@ -103,8 +103,8 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
     __shared__ int s_choice;
 
     const int row = blockIdx.x, tid = threadIdx.x;
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     const float* lg = logits + (size_t)row * ld;
 
     ArgMax am{-INFINITY, 0x7fffffff};
