@@ -426,14 +426,20 @@ PREFILL_CASES = [  # H, Hkv, dh, [(tokens already cached, new tokens)], window
     (2, 2, 64, [(0, 64)], 0), (3, 3, 64, [(0, 1), (0, 65), (0, 200)], 0), (4, 2, 64, [(37, 100), (128, 3), (0, 64)], 0),
     (2, 1, 128, [(0, 130), (64, 70)], 0), (12, 12, 64, [(0, 300), (250, 50)], 0), (2, 2, 64, [(0, 260), (100, 90)], 70),
     (2, 2, 128, [(5, 140)], 64),
+    # long rows: many key blocks per query tile, tiles of unequal length, a continuation across block pairs
+    (3, 3, 64, [(0, 1024), (0, 700)], 0), (2, 2, 64, [(0, 600), (300, 500)], 200), (2, 1, 64, [(127, 130), (129, 1), (63, 66)], 0),
 ]
 
 
+@pytest.mark.parametrize("kernel", ["tcgen05", "mma_sync"])
 @pytest.mark.parametrize("H,Hkv,dh,seqs,window", PREFILL_CASES)
-def test_attention_prefill_tensor_cores(H, Hkv, dh, seqs, window):
+def test_attention_prefill_tensor_cores(monkeypatch, kernel, H, Hkv, dh, seqs, window):
     """Ragged batches with unequal lengths and continuations, grouped heads, a window; the cache is NaN
     outside what the sequences hold, and freed-looking rows inside their last blocks are NaN too."""
     from vlrf_b200.csrc import ops
+    if kernel == "tcgen05" and dh != 64:
+        pytest.skip("the tcgen05 kernel takes head size 64")
+    monkeypatch.setattr(ops, "PREFILL_ATTENTION_TCGEN05", kernel == "tcgen05")
     dtype = torch.bfloat16
     scale = 0.8 / math.sqrt(dh)
     n_blocks = sum((p + n + 63) // 64 for p, n in seqs) + 2

@@ -55,6 +55,10 @@ _SIGNATURES = {
     "vlrf_attn_prefill": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
                           _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
                           _c_int, _c_void_p, _c_void_p],
+    "vlrf_attn_prefill_tc_takes": [_c_int, _c_int, _c_int, _c_int, _c_int],
+    "vlrf_attn_prefill_tc": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
+                             _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
+                             _c_int, _c_void_p, _c_void_p],
     "vlrf_attn_decode": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
                          _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int,
                          _c_void_p, _c_void_p, _c_void_p, _c_void_p],

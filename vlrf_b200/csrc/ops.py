@@ -101,6 +101,7 @@ def linear(x, w, bias, out, *, act=None, residual=None, rows: int | None = None,
 
 _SM_COUNT = None
 USE_TCGEN05 = True
+PREFILL_ATTENTION_TCGEN05 = True     # head size 64; off: the mma.sync kernel takes those too
 SKINNY_MAX_ROWS = 64
 FUSED_NORM_MAX_ROWS = 16
 SWAPPED_MIN_COLUMNS = 16384
@@ -421,6 +422,13 @@ def attention_prefill(qkv, q_off: int, k_cache, v_cache, block_table, seq_slot, 
     if seq_slot.shape[0] < n_seqs or seq_start.shape[0] < n_seqs + 1 or seq_pos0.shape[0] < n_seqs:
         raise KernelError("attention_prefill: sequence tables are too short")
     _written(out)
+    from . import library
+    if PREFILL_ATTENTION_TCGEN05 and library().vlrf_attn_prefill_tc_takes(head_dim, bt, qkv.shape[1], q_off, out.shape[1]):
+        # head size 64: S and O on the tcgen05 tensor cores, accumulators in tensor memory
+        call("vlrf_attn_prefill_tc", _ptr(qkv), qkv.shape[1], q_off, _ptr(k_cache), _ptr(v_cache), nb, _ptr(block_table),
+             block_table.shape[1], _ptr(seq_slot), _ptr(seq_start), _ptr(seq_pos0), _ptr(out), out.shape[1], n_tokens,
+             n_seqs, max_new, n_heads, n_kv_heads, head_dim, bt, float(scale), int(window), _ptr(dev_err), _stream())
+        return
     call("vlrf_attn_prefill", _ptr(qkv), qkv.shape[1], q_off, _ptr(k_cache), _ptr(v_cache), nb, _ptr(block_table),
          block_table.shape[1], _ptr(seq_slot), _ptr(seq_start), _ptr(seq_pos0), _ptr(out), out.shape[1], n_tokens, n_seqs,
          max_new, n_heads, n_kv_heads, head_dim, bt, float(scale), int(window), _ptr(dev_err), _stream())
