@@ -57,14 +57,27 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+    """Samples SM clocks and throttle reasons while a timed region runs: through NVML every few
+    milliseconds (read-only queries), or with nvidia-smi if the NVML module is missing."""
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
-    def __init__(self):
+    def __init__(self, period_s: float = 0.005):
         self.samples, self.proc, self.thread = [], None, None
+        self.period_s, self.stop = period_s, threading.Event()
 
     def __enter__(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            handle = pynvml.nvmlDeviceGetHandleByIndex(0)
+            pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)
+            self.thread = threading.Thread(target=self._poll, args=(pynvml, handle), daemon=True)
+            self.thread.start()
+            return self
+        except Exception:  # noqa: BLE001 - no NVML: ask nvidia-smi instead
+            pass
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
                                           "--format=csv,noheader,nounits", "-lms", "100"],
@@ -75,17 +88,35 @@ class ClockSampler:
             self.proc = None
         return self
 
+    def _poll(self, pynvml, handle):
+        reasons_of = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+        try:
+            mx = pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM)
+            while not self.stop.is_set():
+                sm = pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)
+                bits = int(reasons_of(handle))
+                flags = ["Active" if bits & self.REASON_BITS[n] else "Not Active"
+                         for n in ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")]
+                self.samples.append(", ".join([str(sm), str(mx)] + flags))
+                self.stop.wait(self.period_s)
+        except Exception:  # noqa: BLE001 - a failed query ends the sampling, not the benchmark
+            pass
+
     def _read(self):
         for line in self.proc.stdout:
             self.samples.append(line.strip())
 
     def __exit__(self, *exc):
+        self.stop.set()
         if self.proc is not None:
             self.proc.terminate()          # the exact process started above
             try:
                 self.proc.wait(timeout=5)
             except subprocess.TimeoutExpired:
                 self.proc.kill()
+        elif self.thread is not None:
+            self.thread.join(timeout=2)
 
     def summary(self) -> dict:
         sm, mx, reasons = [], [], set()

@@ -120,6 +120,20 @@ template <int ACT> __device__ __forceinline__ float apply_act(float x) {
     if (ACT == VLRF_ACT_GELU_ERF) return gelu_erf_f(x);
     return x;
 }
+// The tanh form for results that are rounded to bfloat16 anyway: tanh in one instruction (`tanh.approx.f32`,
+// relative error about 2^-11, below bfloat16's 2^-9).  Every bfloat16-output epilogue uses this one, so a
+// token's value does not depend on which product kernel its step took; float32 outputs keep tanhf.
+__device__ __forceinline__ float gelu_tanh_fast(float x) {
+    const float c1 = 0.7978845608028654f, c2 = 0.044715f;
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(c1 * (x + c2 * x * x * x)));
+    return 0.5f * x * (1.f + t);
+}
+template <typename OT> __device__ __forceinline__ float apply_act_out(float x, int act) {
+    if (act == VLRF_ACT_GELU_TANH) return sizeof(OT) == 2 ? gelu_tanh_fast(x) : gelu_tanh_f(x);
+    if (act == VLRF_ACT_GELU_ERF) return gelu_erf_f(x);
+    return x;
+}
 __device__ __forceinline__ float apply_act_rt(float x, int act) {
     if (act == VLRF_ACT_GELU_TANH) return gelu_tanh_f(x);
     if (act == VLRF_ACT_GELU_ERF) return gelu_erf_f(x);

@@ -25,7 +25,6 @@
 // include/model/kv_cache.hpp:215-251).
 #include "common.cuh"
 #include "tma.cuh"
-#include <cstdlib>
 
 namespace {
 
@@ -330,7 +329,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                 const int n = n0 + t + 4 * (j & 1);
                 if (n >= N || m >= M) continue;
                 float v = acc[mt][j] + pre_bias[j & 1];
-                v = apply_act_rt(v, act) + pre[mt][j];
+                v = apply_act_out<OT>(v, act) + pre[mt][j];
                 ElemIO<OT>::store(Y + (size_t)m * ldy + n, v);
                 if (kv.Kc != nullptr && n >= kv.k_off) {
                     const bool is_v = n >= kv.v_off;
@@ -461,16 +460,7 @@ extern "C" int vlrf_gemm_skinny(const void* X, int x_is_f32_ln, const void* W, c
     const int rounds = (groups + grid - 1) / grid;
     int S = rounds < MAX_STAGES ? rounds : MAX_STAGES;
     while (S > 1 && smem_bytes(mt16, M, xmode, K, CG, S) > SMEM_BUDGET) --S;
-    int grid_x = grid;
-    if (const char* e = getenv("VLRF_SK_DEBUG")) {   // experiment hook: "CG,S,grid"
-        int a = 0, b = 0, c = 0;
-        if (sscanf(e, "%d,%d,%d", &a, &b, &c) == 3) {
-            if (a > 0) CG = a;
-            if (b > 0) S = b;
-            const int gr = (N + 8 * CG - 1) / (8 * CG);
-            grid_x = c > 0 ? (c < gr ? c : gr) : (gr < sm_count ? gr : sm_count);
-        }
-    }
+    const int grid_x = grid;
 #define GO(XM, OT) return dispatch_mt<XM, OT>(mt16, X, W, bias, residual, Y, M, N, K, ldx, ldy, act, CG, S, grid_x, gamma, beta, eps, kv, dev_err, stream)
     if (out_dtype == VLRF_BF16) {
         if (xmode == 2) GO(2, __nv_bfloat16);

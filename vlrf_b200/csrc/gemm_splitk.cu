@@ -31,7 +31,6 @@
 #include "common.cuh"
 #include "tma.cuh"
 #include "tcgen05.cuh"
-#include <cstdlib>
 
 namespace {
 
@@ -320,7 +319,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                 if (j < 2) { res = j == 0 ? pre_res[0] : pre_res[1]; bv = j == 0 ? pre_bias[0] : pre_bias[1]; }
                 else { res = residual ? residual[(size_t)m * ldy + n] : 0.f; bv = bias ? bias[n] : 0.f; }
             }
-            const float y = apply_act_rt(acc + bv, act) + res;
+            const float y = apply_act_out<OT>(acc + bv, act) + res;
             if (n < N) ElemIO<OT>::store(Y + (size_t)m * ldy + n, y);
             if (stats_out != nullptr) {
                 // what a LayerNorm of these rows will need: this segment's sum and squared deviation from its
@@ -387,22 +386,12 @@ size_t sp_smem(int bm, int bn, bool ln, int stages, int kb_cap, int M, int split
 // give half as many CTAs again as 128-row tiles.
 SpPlan sp_plan(int M, int N, int K, int bn, bool ln) {
     const int n_kb = (K + SP_BK - 1) / SP_BK;
-    int target = sp_sm_count();
-    int force_bm = 0, max_splits = SP_MAX_SPLITS;
-    size_t budget = SP_SMEM_BUDGET;
-    if (const char* e = getenv("VLRF_SPLITK_PLAN")) {            // experiment hook: "ctas,bm,max splits,smem KiB"
-        int a = 0, b = 0, c = 0, d = 0;
-        if (sscanf(e, "%d,%d,%d,%d", &a, &b, &c, &d) >= 1) {
-            if (a > 0) target = a;
-            if (b == 64 || b == 128) force_bm = b;
-            if (c > 0 && c <= SP_MAX_SPLITS) max_splits = c;
-            if (d > 0 && d <= 200) budget = (size_t)d * 1024;
-        }
-    }
+    const int target = sp_sm_count();
+    const int max_splits = SP_MAX_SPLITS;
+    const size_t budget = SP_SMEM_BUDGET;
     SpPlan best{};
     int best_ctas = -1;
     for (int bm = 128; bm >= 64; bm -= 64) {
-        if (force_bm && bm != force_bm) continue;
         const int tiles = (N + bm - 1) / bm;
         int splits = (target + tiles / 2) / tiles;
         if (splits > max_splits) splits = max_splits;

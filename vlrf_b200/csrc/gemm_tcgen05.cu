@@ -22,7 +22,6 @@
 #include "common.cuh"
 #include "tma.cuh"
 #include "tcgen05.cuh"
-#include <cstdlib>
 
 namespace {
 
@@ -171,7 +170,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                             for (int j = 0; j < 16; ++j) {
                                 const int m = c0 + j;
                                 if (m < M) {
-                                    float x = apply_act_rt(__uint_as_float(r[j]) + bv, act);
+                                    float x = apply_act_out<OT>(__uint_as_float(r[j]) + bv, act);
                                     if (residual) x += residual[(size_t)m * ldy + n];
                                     ElemIO<OT>::store(Y + (size_t)m * ldy + n, x);
                                 }
@@ -235,14 +234,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     for (int j = 0; j < 32; j += 8) {
                         const float4 b0 = bq[j / 4], b1 = bq[j / 4 + 1], r0 = rq[j / 4], r1 = rq[j / 4 + 1];
                         float v[8];
-                        v[0] = apply_act_rt(__uint_as_float(r[j + 0]) + b0.x, act) + r0.x;
-                        v[1] = apply_act_rt(__uint_as_float(r[j + 1]) + b0.y, act) + r0.y;
-                        v[2] = apply_act_rt(__uint_as_float(r[j + 2]) + b0.z, act) + r0.z;
-                        v[3] = apply_act_rt(__uint_as_float(r[j + 3]) + b0.w, act) + r0.w;
-                        v[4] = apply_act_rt(__uint_as_float(r[j + 4]) + b1.x, act) + r1.x;
-                        v[5] = apply_act_rt(__uint_as_float(r[j + 5]) + b1.y, act) + r1.y;
-                        v[6] = apply_act_rt(__uint_as_float(r[j + 6]) + b1.z, act) + r1.z;
-                        v[7] = apply_act_rt(__uint_as_float(r[j + 7]) + b1.w, act) + r1.w;
+                        v[0] = apply_act_out<OT>(__uint_as_float(r[j + 0]) + b0.x, act) + r0.x;
+                        v[1] = apply_act_out<OT>(__uint_as_float(r[j + 1]) + b0.y, act) + r0.y;
+                        v[2] = apply_act_out<OT>(__uint_as_float(r[j + 2]) + b0.z, act) + r0.z;
+                        v[3] = apply_act_out<OT>(__uint_as_float(r[j + 3]) + b0.w, act) + r0.w;
+                        v[4] = apply_act_out<OT>(__uint_as_float(r[j + 4]) + b1.x, act) + r1.x;
+                        v[5] = apply_act_out<OT>(__uint_as_float(r[j + 5]) + b1.y, act) + r1.y;
+                        v[6] = apply_act_out<OT>(__uint_as_float(r[j + 6]) + b1.z, act) + r1.z;
+                        v[7] = apply_act_out<OT>(__uint_as_float(r[j + 7]) + b1.w, act) + r1.w;
                         if (sizeof(OT) == 4) {
                             *reinterpret_cast<float4*>(reinterpret_cast<float*>(yrow) + j) = make_float4(v[0], v[1], v[2], v[3]);
                             *reinterpret_cast<float4*>(reinterpret_cast<float*>(yrow) + j + 4) = make_float4(v[4], v[5], v[6], v[7]);
@@ -269,7 +268,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                         if (j >= n_here) break;
                         float x = __uint_as_float(r[j]);
                         if (bias) x += bias[n0 + c0 + j];
-                        x = apply_act_rt(x, act);
+                        x = apply_act_out<OT>(x, act);
                         if (rrow) x += rrow[j];
                         ElemIO<OT>::store(yrow + j, x);
                         const int n = n0 + c0 + j;
@@ -371,7 +370,6 @@ extern "C" int vlrf_gemm_tcgen05(const void* X, const void* W, const float* bias
             if (best < 0 || cost < best) { best = cost; best_bn = bn; }
         }
     }
-    if (const char* e = getenv("VLRF_TC_BN")) { const int v = atoi(e); if (v == 64 || v == 128 || v == 256) best_bn = v; }
 #define TILED(BNV, ST) (out_dtype == VLRF_BF16 ? launch_tc<BNV, ST, __nv_bfloat16>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, kv, dev_err, stream) \
                                               : launch_tc<BNV, ST, float>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, kv, dev_err, stream))
     VLRF_REQUIRE(out_dtype == VLRF_BF16 || out_dtype == VLRF_F32, "gemm_tcgen05: unknown output dtype %d", out_dtype);
