@@ -19,6 +19,7 @@ class _Batch:
     most_tokens: list                 # most tokens each sequence may come to hold
     session: DecodeSession | None = None
     staging: torch.Tensor | None = None   # pinned host int32: the tokens fed at a decode step
+    result: torch.Tensor | None = None    # pinned host int32: the tokens a decode step chose
 
 
 def _bucket(n: int) -> int:
@@ -59,6 +60,7 @@ class DeviceBackend:
                 self.engine.cache.reserve(s, most)
             self.engine.cache.sync_tables()
             batch.staging = torch.zeros(len(batch.slots), dtype=torch.int32, pin_memory=True)
+            batch.result = torch.zeros(len(batch.slots), dtype=torch.int32, pin_memory=True)
         if batch.session is not None:
             return self._run_decode(batch, rows, tokens)
         entries = [StepEntry(batch.slots[r], toks, [len(toks) - 1]) for r, toks in zip(rows, tokens)]
@@ -73,13 +75,31 @@ class DeviceBackend:
     def _run_decode(self, batch: _Batch, rows: list, tokens: list) -> list:
         sess = batch.session
         n = len(batch.slots)
-        st = batch.staging
+        st = batch.staging.numpy()                             # (a view of the pinned buffer)
         for r, toks in zip(rows, tokens):
             st[r] = toks[0]
-        sess.tokens[:n].copy_(st, non_blocking=True)          # this step's inputs, host → device
-        logits = sess.step(advance_on_device=False)            # the sampling kernel moves the positions on
-        out = batch.sampler.sample(logits[:n], list(range(n)), next_pos=sess.tok_pos, row_slot=sess.tok_slot)
-        host = out.tolist()                                    # this step's result, device → host; synchronises
+        sampler = batch.sampler
+        everyone = list(range(n))
+        if not sampler.any_penalties:
+            # One replayed graph a step: this step's inputs host → device, the model, the sampling kernel
+            # (which also moves the positions on), the result device → host.
+            def feed():
+                sess.tokens[:n].copy_(batch.staging, non_blocking=True)
+
+            def choose(logits):
+                sampler.sample(logits[:n], everyone, next_pos=sess.tok_pos, row_slot=sess.tok_slot)
+
+            def fetch():
+                batch.result.copy_(sampler.out[:n], non_blocking=True)
+
+            sess.step_sampled(choose, key=sampler, state=(sampler.rng_ctr,), before=feed, after=fetch)
+            torch.cuda.current_stream().synchronize()          # the step's result is in host memory
+            host = batch.result.tolist()
+        else:
+            sess.tokens[:n].copy_(batch.staging, non_blocking=True)    # this step's inputs, host → device
+            logits = sess.step(advance_on_device=False)            # the sampling kernel moves the positions on
+            out = sampler.sample(logits[:n], everyone, next_pos=sess.tok_pos, row_slot=sess.tok_slot)
+            host = out.tolist()                                    # this step's result, device → host; synchronises
         self.h2d_bytes += 4 * n
         self.d2h_bytes += 4 * n
         self.decode_steps += 1

@@ -56,35 +56,54 @@ class DecodeSession:
     def step_greedy(self, out: torch.Tensor) -> torch.Tensor:
         """A whole greedy decode step on the device: the model, the argmax, and the hand-over of token and
         position to the next step, captured together; `out` (int32 [rows]) receives the tokens."""
-        from ..csrc import launch_count, ops
+        from ..csrc import ops
+
+        def argmax(logits):
+            ops.sample(logits, self.rows, out, next_tokens=self.tokens, next_pos=self.tok_pos, row_slot=self.tok_slot)
+
+        return self.step_sampled(argmax, key=out)
+
+    def step_sampled(self, sample, *, key, state=(), before=None, after=None) -> torch.Tensor:
+        """A whole decode step captured as one graph: `before()` (say, a copy of the step's tokens from
+        pinned host memory), the model, `sample(logits)` — which must launch the sampling kernel with
+        `next_pos=self.tok_pos, row_slot=self.tok_slot` so that the positions move on — and `after()`
+        (say, a copy of the result to pinned host memory).  All of them may only enqueue work on tensors
+        that stay where they are.  The graph is kept as long as `key` is the same object; `state`:
+        tensors that `sample` changes in place (random counters), put back after the uncaptured run that
+        sizes the workspace."""
+        from ..csrc import launch_count
         c = self.engine.cache
         for s, live in zip(self.slots, self.live):
             if live and c.lengths[s] + 1 > self.model.max_seq_len:
                 raise ValueError(f"slot {s} is at the model's last position")
 
         def run():
+            if before is not None:
+                before()
             logits = self.model.forward(self._context(), c)
-            ops.sample(logits, self.rows, out, next_tokens=self.tokens, next_pos=self.tok_pos, row_slot=self.tok_slot)
+            sample(logits)
+            if after is not None:
+                after()
             return logits
 
         if not self.use_graph:
-            before = launch_count()
+            start = launch_count()
             self.logits = run()
-            self.kernels_per_step = launch_count() - before
+            self.kernels_per_step = launch_count() - start
         else:
-            if self._greedy_graph is None or self._greedy_out is not out:
-                pos = self.tok_pos.clone()             # the warm-up run must not advance anything
-                tok = self.tokens.clone()
-                before = launch_count()
+            if self._greedy_graph is None or self._greedy_out is not key:
+                kept = [t.clone() for t in (self.tok_pos, self.tokens, *state)]   # the warm-up run must not advance anything
+                start = launch_count()
                 self.logits = run()
-                self.kernels_per_step = launch_count() - before
+                self.kernels_per_step = launch_count() - start
                 torch.cuda.synchronize()
-                self.tok_pos.copy_(pos); self.tokens.copy_(tok)
+                for t, k in zip((self.tok_pos, self.tokens, *state), kept):
+                    t.copy_(k)
                 self.ws.frozen = True
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g):
                     self.logits = run()
-                self._greedy_graph, self._greedy_out = g, out
+                self._greedy_graph, self._greedy_out = g, key
             self._greedy_graph.replay()
         for s, live in zip(self.slots, self.live):
             if live:
