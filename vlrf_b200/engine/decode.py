@@ -31,7 +31,7 @@ class DecodeSession:
         self.logit_rows = torch.arange(self.rows, dtype=torch.int32, device=dev)
         self.one = torch.ones(self.rows, dtype=torch.int32, device=dev)
         self.ws = Workspace(dev)
-        self.use_graph = use_graph
+        self.use_graph = use_graph and self.model.replayable
         self.graph = None
         self._greedy_graph = None
         self._greedy_out = None

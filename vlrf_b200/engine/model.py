@@ -48,6 +48,20 @@ class DecoderModel:
                 if self.layers[self.schedule[j].layer].cache_need() != self.layers[call.layer].cache_need():
                     raise ValueError(f"schedule entry {i} reads a cache whose shape differs from its own need")
 
+    @property
+    def replayable(self) -> bool:
+        """Whether a step's launches may be captured in a CUDA graph and replayed: every part must enqueue the
+        same work for the same shapes without asking the device anything.  A part whose control flow
+        depends on device values (say, a feed-forward that gathers each expert's tokens on the host) says
+        so with a class or instance attribute `replayable = False`; steps then launch plainly."""
+        def ok(obj):
+            return getattr(obj, "replayable", True)
+        parts = [self.embedding, self.final_norm, self.head]
+        for layer in self.layers:
+            parts.append(layer)
+            parts.extend(v for v in vars(layer).values() if not isinstance(v, (int, float, str, torch.Tensor)))
+        return all(ok(p) for p in parts)
+
     def cache_needs(self) -> list:
         """For every schedule entry what it keeps per sequence (None for entries that read another's)."""
         return [None if c.reads_cache_of is not None else self.layers[c.layer].cache_need()

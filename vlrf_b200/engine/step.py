@@ -166,7 +166,7 @@ class Engine:
 
     def _forward(self, ctx: StepContext, signature) -> torch.Tensor:
         """Run the model on the step, replaying a captured graph when a step of the same shape ran before."""
-        if not self.capture_repeated_steps or ctx.max_new == 1:
+        if not self.capture_repeated_steps or ctx.max_new == 1 or not self.model.replayable:
             return self.model.forward(ctx, self.cache)     # single-token steps have DecodeSession's graph
         if self._graph_generation != self.ws.generation:
             self._graphs.clear()                           # scratch moved: captured addresses are stale
