@@ -312,7 +312,7 @@ def paged(k, v, n_blocks, order_seed, dtype):
     return kp, vp, perm.to(torch.int32)
 
 
-def run_attention(q, k, v, *, dtype, scale, window=0, past=None, impl="generic", n_split=1):
+def run_attention(q, k, v, *, dtype, scale, window=0, past=None, impl="generic", n_split=1, scratch=True):
     """q [H, T, dh] are the LAST T positions of a context of C = k.shape[1] tokens."""
     from vlrf_b200.csrc import ops
     H, T, dh = q.shape
@@ -326,7 +326,14 @@ def run_attention(q, k, v, *, dtype, scale, window=0, past=None, impl="generic",
     e = err_word()
     slot = torch.full((T,), 1, dtype=torch.int32)
     pos = torch.arange(C - T, C, dtype=torch.int32)
-    if impl == "decode":
+    if impl == "decode" and not scratch:
+        # the parts of a context merge inside a thread-block cluster: no scratch
+        assert not ops.attention_decode_needs_scratch(dh, n_split)
+        for _ in range(2):
+            out.fill_(float("nan"))
+            ops.attention_decode(qkv.to(DEV), 16, kp.to(DEV), vp.to(DEV), table.to(DEV), slot.to(DEV), pos.to(DEV), out,
+                                 T, H, Hkv, dh, scale, window, n_split, None, None, e)
+    elif impl == "decode":
         partials = torch.full((T * H * n_split * (dh + 2),), float("nan"), device=DEV)
         counters = torch.zeros(T * H, dtype=torch.int32, device=DEV)
         for _ in range(2):       # twice: the counters must be back at zero after a call
@@ -381,6 +388,10 @@ def test_attention_decode_split_context(H, Hkv, dh, T, C, n_split, dtype, tol):
     scale = 0.7 / math.sqrt(dh)
     got = run_attention(q, k, v, dtype=dtype, scale=scale, impl="decode", n_split=n_split)
     assert rel_err(got, plain_attention(q, k, v, scale)) < tol
+    from vlrf_b200.csrc import ops
+    if n_split > 1 and not ops.attention_decode_needs_scratch(dh, n_split):
+        again = run_attention(q, k, v, dtype=dtype, scale=scale, impl="decode", n_split=n_split, scratch=False)
+        assert torch.equal(again, got)                       # the same merge, in shared memory instead of scratch
 
 
 @pytest.mark.parametrize("far", [0, 63, 64, 257, 511])

@@ -42,6 +42,7 @@ constexpr int DEC_MAX_DH = 256;
 constexpr int DEC_ND = DEC_MAX_DH / 32;
 constexpr uint32_t DEC_WAIT_LIMIT = 4000000u;
 constexpr int DEC_STAGE_BYTES = 64 * 1024;       // shared memory for the keys and values in flight
+constexpr int DEC_MAX_CLUSTER = 16;              // CTAs of a cluster (more than 8 is "non-portable": B200 takes it)
 
 __device__ __forceinline__ uint32_t dsmem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void dmbar_init(uint64_t* bar, uint32_t count) {
@@ -147,6 +148,68 @@ __device__ void finish_cta(const float* wpart, int dh, int row, int h, int H, in
 }
 
 // Any head size that is a multiple of 16: ordinary loads, loops over the head size.
+// The same end for CTAs launched as a cluster over the parts of one (row, head): every CTA leaves the merge of
+// its warps in its own shared memory (`cpart`, dh + 2 floats), and after a cluster barrier the CTA of part 0
+// reads them all through distributed shared memory and merges them in the order of the parts.  No scratch in
+// global memory, no counter.  Every thread of every CTA of the cluster must come here.
+template <typename ET>
+__device__ void finish_cluster(const float* wpart, float* cpart, int dh, int row, int h, int split, int n_split,
+                               ET* __restrict__ out, int ld_out) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp == 0) {
+        float M = -INFINITY;
+        for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, wpart[w * (dh + 2)]);
+        float L = 0.f;
+        float o[DEC_ND];
+#pragma unroll
+        for (int i = 0; i < DEC_ND; ++i) o[i] = 0.f;
+        for (int w = 0; w < DEC_WARPS; ++w) {
+            const float* pw = wpart + w * (dh + 2);
+            const float f = (pw[0] == -INFINITY) ? 0.f : expf(pw[0] - M);
+            L += pw[1] * f;
+#pragma unroll
+            for (int i = 0; i < DEC_ND; ++i) {
+                const int cc = i * 32 + lane;
+                if (cc < dh) o[i] += pw[2 + cc] * f;
+            }
+        }
+        if (lane == 0) { cpart[0] = M; cpart[1] = L; }
+#pragma unroll
+        for (int i = 0; i < DEC_ND; ++i) {
+            const int cc = i * 32 + lane;
+            if (cc < dh) cpart[2 + cc] = o[i];
+        }
+    }
+    cluster_sync_all();                            // every part's merge is in its CTA's shared memory
+    if (split == 0 && warp == 0) {
+        const uint32_t base = (uint32_t)__cvta_generic_to_shared(cpart);
+        float M = -INFINITY;
+        for (int s = 0; s < n_split; ++s) M = fmaxf(M, ld_cluster_f32(base, (uint32_t)s));
+        float L = 0.f;
+        float o[DEC_ND];
+#pragma unroll
+        for (int i = 0; i < DEC_ND; ++i) o[i] = 0.f;
+        for (int s = 0; s < n_split; ++s) {
+            const float pm = ld_cluster_f32(base, (uint32_t)s);
+            const float f = (pm == -INFINITY) ? 0.f : expf(pm - M);
+            L += ld_cluster_f32(base + 4, (uint32_t)s) * f;
+#pragma unroll
+            for (int i = 0; i < DEC_ND; ++i) {
+                const int cc = i * 32 + lane;
+                if (cc < dh) o[i] += ld_cluster_f32(base + 4 * (2 + cc), (uint32_t)s) * f;
+            }
+        }
+        const float inv = (L > 0.f) ? 1.f / L : 0.f;
+        ET* dst = out + (size_t)row * ld_out + (size_t)h * dh;
+#pragma unroll
+        for (int i = 0; i < DEC_ND; ++i) {
+            const int cc = i * 32 + lane;
+            if (cc < dh) ElemIO<ET>::store(dst + cc, o[i] * inv);
+        }
+    }
+    cluster_sync_relaxed();                        // nobody leaves while its shared memory is being read
+}
+
 template <typename ET>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attn_decode_generic_kernel(const ET* __restrict__ qkv, int ld, int q_off, const ET* __restrict__ Kc,
@@ -240,7 +303,8 @@ attn_decode_generic_kernel(const ET* __restrict__ qkv, int ld, int q_off, const 
 // its own mbarrier.  A 16-byte piece of a key's row belongs to one lane: the PARTS lanes of a key add
 // their partial dot products with shuffles, and the same lanes then weigh the same key's value pieces,
 // so a quarter warp always reads 128 contiguous bytes of shared memory.
-template <typename ET, int DH>
+// CLUSTER: the CTAs of one (row, head) — grid z — are a thread-block cluster and merge through shared memory
+template <typename ET, int DH, bool CLUSTER>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attn_decode_bulk_kernel(const ET* __restrict__ qkv, int ld, int q_off, const ET* __restrict__ Kc,
                         const ET* __restrict__ Vc, const int* __restrict__ block_table, int max_blocks,
@@ -260,6 +324,7 @@ attn_decode_bulk_kernel(const ET* __restrict__ qkv, int ld, int q_off, const ET*
     unsigned char* kbuf = dsm + 128;                                         // [CH_MAX][CHUNK_BYTES]
     unsigned char* vbuf = kbuf + (size_t)CH_MAX * CHUNK_BYTES;
     float* wpart = reinterpret_cast<float*>(vbuf + (size_t)CH_MAX * CHUNK_BYTES);   // [DEC_WARPS][DH + 2]
+    float* cpart = wpart + DEC_WARPS * (DH + 2);                                    // [DH + 2] (CLUSTER)
     __shared__ int s_last;
     __shared__ int s_bad;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -408,7 +473,8 @@ attn_decode_bulk_kernel(const ET* __restrict__ qkv, int ld, int q_off, const ET*
         for (int j = 0; j < E; ++j) mine[2 + part * E + j] = acc[j];
     }
     __syncthreads();
-    finish_cta<ET>(wpart, DH, row, h, H, split, n_split, partials, counters, out, ld_out, &s_last);
+    if (CLUSTER) finish_cluster<ET>(wpart, cpart, DH, row, h, split, n_split, out, ld_out);
+    else finish_cta<ET>(wpart, DH, row, h, H, split, n_split, partials, counters, out, ld_out, &s_last);
 }
 
 template <typename ET, int DH>
@@ -418,21 +484,37 @@ int launch_bulk(dim3 grid, const void* qkv, int ld, int q_off, const void* Kc, c
                 cudaStream_t stream) {
     constexpr int CHUNK_BYTES = 32 * DH * (int)sizeof(ET);
     constexpr int CH_MAX = DEC_STAGE_BYTES / (2 * CHUNK_BYTES) < 8 ? DEC_STAGE_BYTES / (2 * CHUNK_BYTES) : 8;
-    const size_t smem = 128 + (size_t)2 * CH_MAX * CHUNK_BYTES + (size_t)DEC_WARPS * (DH + 2) * sizeof(float);
-    auto kern = attn_decode_bulk_kernel<ET, DH>;
-    static bool raised = false;
-    if (!raised && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "attn_decode: %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-        raised = true;
+    const size_t smem = 128 + (size_t)2 * CH_MAX * CHUNK_BYTES + (size_t)(DEC_WARPS + 1) * (DH + 2) * sizeof(float);
+    // without scratch from the caller, the parts of a (row, head) merge inside a cluster (at most 16 CTAs)
+    const bool cluster = n_split > 1 && n_split <= DEC_MAX_CLUSTER && partials == nullptr;
+    auto kern = cluster ? attn_decode_bulk_kernel<ET, DH, true> : attn_decode_bulk_kernel<ET, DH, false>;
+    static bool raised[2] = {false, false};
+    if (!raised[cluster]) {
+        cudaError_t e = cudaSuccess;
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess && cluster) e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "attn_decode: %zu bytes of shared memory, clusters: %s", smem, cudaGetErrorString(e));
+        raised[cluster] = true;
     }
-    cudaError_t e = launch_chained(kern, grid, dim3(DEC_WARPS * 32), smem, stream, (const ET*)qkv, ld, q_off,
+    cudaError_t e;
+    if (cluster)
+        e = launch_chained_cluster(kern, grid, dim3(DEC_WARPS * 32), smem, dim3(1, 1, n_split), stream, (const ET*)qkv, ld, q_off,
                                    (const ET*)Kc, (const ET*)Vc, block_table, max_blocks, tok_slot, tok_pos, (ET*)out,
                                    ld_out, H, Hkv, BT, scale, window, n_split, partials, counters, dev_err);
+    else
+        e = launch_chained(kern, grid, dim3(DEC_WARPS * 32), smem, stream, (const ET*)qkv, ld, q_off,
+                           (const ET*)Kc, (const ET*)Vc, block_table, max_blocks, tok_slot, tok_pos, (ET*)out,
+                           ld_out, H, Hkv, BT, scale, window, n_split, partials, counters, dev_err);
     if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "attn_decode: %s", cudaGetErrorString(e));
     return vlrf_check_launch("attn_decode");
 }
 }  // namespace
+
+// Whether a context cut into n_split parts needs scratch from the caller (else the parts' CTAs form a
+// cluster and merge through shared memory).
+extern "C" int vlrf_attn_decode_needs_scratch(int dh, int n_split) {
+    return (n_split > 1 && !((dh == 64 || dh == 128) && n_split <= DEC_MAX_CLUSTER)) ? 1 : 0;
+}
 
 // floats of scratch for the partials and ints for the counters
 extern "C" long long vlrf_attn_decode_scratch_floats(int rows, int H, int dh, int n_split) {
@@ -450,7 +532,10 @@ static int attn_decode_impl(const void* qkv, int dtype, int ld, int q_off, const
                  "attn_decode: head size %d is not a multiple of 16 up to %d", dh, DEC_MAX_DH);
     VLRF_REQUIRE(BT % 32 == 0, "attn_decode: cache blocks of %d tokens are not a multiple of 32", BT);
     VLRF_REQUIRE(n_split >= 1 && n_split <= 65535 && H <= 65535, "attn_decode: bad split %d", n_split);
-    VLRF_REQUIRE(n_split == 1 || (partials != nullptr && counters != nullptr), "attn_decode: a split context needs scratch");
+    const bool clustered = (dh == 64 || dh == 128) && n_split <= DEC_MAX_CLUSTER;    // merges in shared memory
+    VLRF_REQUIRE(n_split == 1 || clustered || (partials != nullptr && counters != nullptr),
+                 "attn_decode: this split context needs scratch");
+    if (partials == nullptr || counters == nullptr) partials = nullptr, counters = nullptr;
     VLRF_REQUIRE(window >= 0 && dev_err != nullptr, "attn_decode: bad window or no error word");
     if (rows == 0) return VLRF_OK;
     dim3 grid(rows, H, n_split);

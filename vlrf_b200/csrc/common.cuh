@@ -39,9 +39,12 @@ int vlrf_check_launch(const char* what);
 // before it on the stream is still running.  It may do only what does not depend on that kernel (set up
 // shared memory, start fetching weights) until `pdl_wait()` returns, which happens once every earlier
 // kernel has finished and its writes are visible.  `pdl_launch_dependents()` lets the next kernel begin in
-// the same way.  Every kernel of the step calls both, the wait first: so when a kernel begins, everything
-// before the kernel ahead of it is complete, and it may already read what those wrote (cache blocks of
-// earlier positions, positions, tables), but nothing that the kernel ahead writes.
+// the same way.  Every kernel of the step calls both.  The products, which read nothing but weights before
+// their wait, release their successor at once; every other kernel only after its own wait.  So when a
+// kernel begins, at least one kernel that is not a product lies complete between it and whatever wrote the
+// positions, the block tables and the cache of earlier positions (the sampling kernel of the step before,
+// host copies, the step before's projections): decode attention may fetch those before its wait, but
+// nothing that the kernels just ahead write (activations, the new position's key and value).
 // `vlrf_set_chained_launch(0)` turns the launch attribute off (the calls then do nothing).
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
@@ -63,10 +66,10 @@ cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
-// The same for a kernel whose CTAs form clusters of (1, cluster_y, 1): the CTAs of a cluster run at the same
+// The same for a kernel whose CTAs form clusters of the given shape: the CTAs of a cluster run at the same
 // time on neighbouring SMs and may read one another's shared memory.
 template <typename... KArgs, typename... Args>
-cudaError_t launch_chained_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, int cluster_y,
+cudaError_t launch_chained_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, dim3 cluster,
                                    cudaStream_t stream, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
@@ -75,14 +78,32 @@ cudaError_t launch_chained_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 blo
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = (unsigned)cluster_y;
-    attr[0].val.clusterDim.z = 1;
+    attr[0].val.clusterDim.x = cluster.x;
+    attr[0].val.clusterDim.y = cluster.y;
+    attr[0].val.clusterDim.z = cluster.z;
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = vlrf_chained_launch_enabled() ? 2 : 1;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// Thread-block clusters: a barrier of all threads of all CTAs of the cluster (with release/acquire ordering
+// of memory, shared memory of the other CTAs included), and reading another CTA's shared memory.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// the same without ordering of memory: for "everyone has finished reading", when what was read has been used
+__device__ __forceinline__ void cluster_sync_relaxed() {
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;\nbarrier.cluster.wait.aligned;" ::: "memory");
+}
+// the value at `own_addr` (a shared-memory address of this CTA) in the CTA of rank `rank` of the cluster
+__device__ __forceinline__ float ld_cluster_f32(uint32_t own_addr, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(own_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
 }
 
 template <typename T> struct ElemIO;

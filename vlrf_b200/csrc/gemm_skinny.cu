@@ -134,8 +134,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     // (when X comes by TMA too, the first slab's request waits for it; the others go now)
     if (warp == 0)
         for (int it = (XMODE == 1 ? 1 : 0); it < min(S, n_my); ++it) request(it, false);
-    pdl_wait();                   // from here on the rows that the kernel before wrote may be read
     pdl_launch_dependents();      // the next kernel may start fetching its weights behind ours
+    pdl_wait();                   // from here on the rows that the kernel before wrote may be read
     if (XMODE == 1 && warp == 0 && n_my > 0) request(0, true);
 
     if (XMODE == 2) {

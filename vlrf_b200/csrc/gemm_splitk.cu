@@ -49,22 +49,6 @@ struct SpKvScatter {
     int max_blocks, k_off, v_off, width, dh, Hkv, BT;
 };
 
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// the same without ordering of memory: for "everyone has finished reading", when what was read has been used
-__device__ __forceinline__ void cluster_sync_relaxed() {
-    asm volatile("barrier.cluster.arrive.relaxed.aligned;\nbarrier.cluster.wait.aligned;" ::: "memory");
-}
-// the value at `own_addr` (a shared-memory address of this CTA) in the CTA of rank `rank` of the cluster
-__device__ __forceinline__ float ld_cluster_f32(uint32_t own_addr, uint32_t rank) {
-    uint32_t remote;
-    float v;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(own_addr), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-    return v;
-}
-
 // bm: rows of W per tile (64 or 128); stages: depth of the ring; kb_cap: most k blocks of one part
 template <int BN, typename OT, bool LN>
 __global__ void __launch_bounds__(LN ? SP_THREADS_LN : SP_THREADS, 2)
@@ -141,8 +125,8 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             s_beta[i] = k < K ? beta[k] : 0.f;
         }
     }
-    pdl_wait();                                    // the rows of X, the residual and the positions are ready
     pdl_launch_dependents();
+    pdl_wait();                                    // the rows of X, the residual and the positions are ready
 
     // pieces of the tile that this warp will finish: (row m, 32-column segment), dealt to the 4·splits
     // epilogue warps of the cluster; what the first two need from global memory is fetched now
@@ -439,7 +423,7 @@ int launch_sp(const void* X, const void* W, const float* gamma, const float* bet
         allowed = plan.smem;
     }
     cudaError_t e = launch_chained_cluster(kern, dim3(plan.tiles, plan.splits), dim3(LN ? SP_THREADS_LN : SP_THREADS), plan.smem,
-                                           plan.splits, stream, tw, tx, (const float*)X, ldx, gamma, beta, eps, bias, residual,
+                                           dim3(1, plan.splits, 1), stream, tw, tx, (const float*)X, ldx, gamma, beta, eps, bias, residual,
                                            (OT*)Y, M, N, K, ldy, act, plan.bm, plan.stages, plan.kb_cap, kv, stats_in, stats_out,
                                            dev_err);
     if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "gemm_splitk: %s", cudaGetErrorString(e));

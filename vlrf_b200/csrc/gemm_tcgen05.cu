@@ -97,8 +97,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
-    pdl_wait();                                    // X (and the residual) come from the kernel before
     pdl_launch_dependents();
+    pdl_wait();                                    // X (and the residual) come from the kernel before
 
     if (warp == 8) {
         if (lane == 0) {

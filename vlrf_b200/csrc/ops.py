@@ -290,6 +290,13 @@ def decode_splits(n_rows: int, n_heads: int, max_context: int) -> int:
     return max(1, min(16, want, -(-max_context // 128)))
 
 
+def attention_decode_needs_scratch(head_dim: int, n_split: int) -> bool:
+    """Whether `attention_decode` with this split needs `partials` and `counters` (else the parts of a
+    context merge inside a thread-block cluster)."""
+    from . import library
+    return bool(library().vlrf_attn_decode_needs_scratch(head_dim, n_split))
+
+
 def attention_decode(qkv, q_off: int, k_cache, v_cache, block_table, tok_slot, tok_pos, out, n_rows: int,
                      n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int, n_split: int,
                      partials, counters, dev_err) -> None:
@@ -305,7 +312,7 @@ def attention_decode(qkv, q_off: int, k_cache, v_cache, block_table, tok_slot, t
         raise KernelError("attention_decode: cache shape does not match the heads")
     if out.shape[1] != n_heads * head_dim or out.shape[0] < n_rows or qkv.shape[0] < n_rows:
         raise KernelError("attention_decode: output does not match")
-    if n_split > 1:
+    if n_split > 1 and partials is not None:
         _dev(partials, "partials", torch.float32); _dev(counters, "counters", torch.int32)
         if partials.numel() < n_rows * n_heads * n_split * (head_dim + 2) or counters.numel() < n_rows * n_heads:
             raise KernelError("attention_decode: scratch is too small")

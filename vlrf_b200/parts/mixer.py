@@ -95,7 +95,7 @@ class CausalSelfAttention:
             # a decode step: few queries, long contexts → split every context across CTAs
             n_split = ops.decode_splits(T, self.n_heads, ctx.max_context)
             partials = counters = None
-            if n_split > 1:
+            if n_split > 1 and ops.attention_decode_needs_scratch(self.head_dim, n_split):
                 partials = ctx.ws.get("attn_partials", T * self.n_heads * n_split, self.head_dim + 2, torch.float32)
                 counters = ctx.ws.get_zeroed("attn_counters", T * self.n_heads, torch.int32)
             ops.attention_decode(qkv, self.q_off, view.k, view.v, view.block_table, ctx.tok_slot, ctx.tok_pos,
