@@ -105,6 +105,14 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t own_addr, uint32_t rank
     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
     return v;
 }
+// … and 16 bytes of it (own_addr a multiple of 16)
+__device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t own_addr, uint32_t rank) {
+    uint32_t remote;
+    float4 v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(own_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+    return v;
+}
 
 template <typename T> struct ElemIO;
 template <> struct ElemIO<float> {

@@ -50,7 +50,8 @@ struct SpKvScatter {
 };
 
 // bm: rows of W per tile (64 or 128); stages: depth of the ring; kb_cap: most k blocks of one part
-template <int BN, typename OT, bool LN>
+// WIDE: the pieces of the finished tile are 32 lanes × 4 columns (many rows) instead of 32 lanes × 1 column
+template <int BN, typename OT, bool LN, bool WIDE>
 __global__ void __launch_bounds__(LN ? SP_THREADS_LN : SP_THREADS, 2)
 gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                    const float* __restrict__ Xf, int ldx, const float* __restrict__ gamma,
@@ -72,7 +73,13 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     float* s_beta = s_gamma + (LN ? kb_cap * SP_BK : 0);
     // this CTA's part of the tile, written at the end: [m][bm] float32
     float* part = s_beta + (LN ? kb_cap * SP_BK : 0);
-    const int segs = bm >> 5, units = M * segs, ustride = 4 * (int)gridDim.y;
+    // The finished tile is dealt to the 4·splits epilogue warps of the cluster in pieces of 32 lanes × 4
+    // columns: one row of a 128-row tile, two rows of a 64-row tile.
+    const int lpr = bm >> 2, rpp = 32 / lpr;                         // lanes a row, rows a piece
+    const int units = (M + rpp - 1) / rpp, ustride = 4 * (int)gridDim.y;
+    // … unless that leaves most warps without a piece (few rows): then pieces of 32 lanes × 1 column
+    const int segs = bm >> 5, units_n = M * segs;
+    constexpr bool wide = WIDE;
     uint64_t* full = reinterpret_cast<uint64_t*>(part + (size_t)M * bm);
     uint64_t* empty = full + SP_MAX_STAGES;
     uint64_t* acc_full = empty + SP_MAX_STAGES;
@@ -131,7 +138,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     // pieces of the tile that this warp will finish: (row m, 32-column segment), dealt to the 4·splits
     // epilogue warps of the cluster; what the first two need from global memory is fetched now
     const int gw = split * 4 + warp;
-    float pre_res[2] = {0.f, 0.f}, pre_bias[2] = {0.f, 0.f};
+    float pre_res[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}}, pre_bias[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 
     if (warp == 4) {
         if (lane == 0) {
@@ -245,11 +252,21 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 const int u = gw + j * ustride;
-                if (u < units) {
+                if (wide) {
+                    const int m = u * rpp + lane / lpr, n = n0 + (lane % lpr) * 4;
+                    if (u < units && m < M) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            if (n + e < N) {
+                                if (residual) pre_res[j][e] = residual[(size_t)m * ldy + n + e];
+                                if (bias) pre_bias[j][e] = bias[n + e];
+                            }
+                    }
+                } else if (u < units_n) {
                     const int m = u / segs, n = n0 + (u % segs) * 32 + lane;
                     if (n < N) {
-                        if (residual) pre_res[j] = residual[(size_t)m * ldy + n];
-                        if (bias) pre_bias[j] = bias[n];
+                        if (residual) pre_res[j][0] = residual[(size_t)m * ldy + n];
+                        if (bias) pre_bias[j][0] = bias[n];
                     }
                 }
             }
@@ -286,9 +303,92 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     }
     __syncwarp();
     cluster_sync_all();                                        // every part of the tile is in shared memory
-    if (warp < 4 && !*(volatile int*)s_abort) {
+    if (warp < 4 && wide && !*(volatile int*)s_abort) {
         int j = 0;
         for (int u = gw; u < units; u += ustride, ++j) {
+            const int m = u * rpp + lane / lpr, colw = (lane % lpr) * 4;
+            const int n = n0 + colw;
+            const bool row_ok = m < M;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            if (row_ok) {
+                const uint32_t own = tsm(part + m * bm + colw);
+                float4 v[SP_MAX_SPLITS];
+#pragma unroll
+                for (int s = 0; s < SP_MAX_SPLITS; ++s)
+                    v[s] = s < splits ? ld_cluster_f32x4(own, (uint32_t)s) : make_float4(0.f, 0.f, 0.f, 0.f);
+                acc[0] = v[0].x; acc[1] = v[0].y; acc[2] = v[0].z; acc[3] = v[0].w;
+#pragma unroll
+                for (int s = 1; s < SP_MAX_SPLITS; ++s) {               // always in the order of the parts
+                    acc[0] += v[s].x; acc[1] += v[s].y; acc[2] += v[s].z; acc[3] += v[s].w;
+                }
+            }
+            float y[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float res = 0.f, bv = 0.f;
+                if (row_ok && n + e < N) {
+                    if (j < 2) { res = j == 0 ? pre_res[0][e] : pre_res[1][e]; bv = j == 0 ? pre_bias[0][e] : pre_bias[1][e]; }
+                    else { res = residual ? residual[(size_t)m * ldy + n + e] : 0.f; bv = bias ? bias[n + e] : 0.f; }
+                }
+                y[e] = apply_act_out<OT>(acc[e] + bv, act) + res;
+            }
+            const bool full = row_ok && n + 3 < N;
+            if (full && ((size_t)m * ldy + n) % 4 == 0) {
+                if (sizeof(OT) == 4) {
+                    *reinterpret_cast<float4*>(reinterpret_cast<float*>(Y) + (size_t)m * ldy + n) = make_float4(y[0], y[1], y[2], y[3]);
+                } else {
+                    uint2 pk;
+                    pk.x = pack2(y[0], y[1]); pk.y = pack2(y[2], y[3]);
+                    *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(Y) + (size_t)m * ldy + n) = pk;
+                }
+            } else if (row_ok) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (n + e < N) ElemIO<OT>::store(Y + (size_t)m * ldy + n + e, y[e]);
+            }
+            if (stats_out != nullptr) {
+                // What a LayerNorm of these rows will need, per 32-column segment (8 lanes): the sum and the
+                // squared deviation from the segment's own mean, of the values as stored (float32 rows only).
+                const int seg0 = n & ~31;
+                const int n_seg = min(32, N - seg0);
+                float sum = 0.f;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) sum += (row_ok && n + e < N) ? y[e] : 0.f;
+#pragma unroll
+                for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                const float mean = n_seg > 0 ? sum / (float)n_seg : 0.f;
+                float m2 = 0.f;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { const float d = (row_ok && n + e < N) ? y[e] - mean : 0.f; m2 += d * d; }
+#pragma unroll
+                for (int o = 1; o < 8; o <<= 1) m2 += __shfl_xor_sync(0xffffffffu, m2, o);
+                if ((lane & 7) == 0 && row_ok && seg0 < N) {
+                    float* so = stats_out + ((size_t)m * ((N + 31) >> 5) + (seg0 >> 5)) * 2;
+                    so[0] = sum; so[1] = m2;
+                }
+            }
+            if (kv.Kc != nullptr && row_ok) {
+                const int blk = s_kv_blk[m];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int ne = n + e;
+                    if (ne < N && ne >= kv.k_off && blk >= 0) {
+                        const bool is_v = ne >= kv.v_off;
+                        const int c = ne - (is_v ? kv.v_off : kv.k_off);
+                        if (c < kv.width) {
+                            const int hh = c / kv.dh, cc = c - hh * kv.dh;
+                            __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(is_v ? kv.Vc : kv.Kc);
+                            base[(((size_t)blk * kv.Hkv + hh) * kv.BT + s_kv_row[m]) * kv.dh + cc] = __float2bfloat16_rn(y[e]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (warp < 4 && !wide && !*(volatile int*)s_abort) {
+        // few pieces: 32 lanes × 1 column each, so that more warps share them
+        int j = 0;
+        for (int u = gw; u < units_n; u += ustride, ++j) {
             const int m = u / segs, colw = (u % segs) * 32 + lane;
             const int n = n0 + colw;
             const uint32_t own = tsm(part + m * bm + colw);
@@ -300,7 +400,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             for (int s = 1; s < SP_MAX_SPLITS; ++s) acc += v[s];    // always in the order of the parts
             float res = 0.f, bv = 0.f;
             if (n < N) {
-                if (j < 2) { res = j == 0 ? pre_res[0] : pre_res[1]; bv = j == 0 ? pre_bias[0] : pre_bias[1]; }
+                if (j < 2) { res = j == 0 ? pre_res[0][0] : pre_res[1][0]; bv = j == 0 ? pre_bias[0][0] : pre_bias[1][0]; }
                 else { res = residual ? residual[(size_t)m * ldy + n] : 0.f; bv = bias ? bias[n] : 0.f; }
             }
             const float y = apply_act_out<OT>(acc + bv, act) + res;
@@ -394,8 +494,8 @@ SpPlan sp_plan(int M, int N, int K, int bn, bool ln) {
     return best;
 }
 
-template <int BN, typename OT, bool LN>
-int launch_sp(const void* X, const void* W, const float* gamma, const float* beta, float eps, const float* bias,
+template <int BN, typename OT, bool LN, bool WIDE>
+int launch_sp_as(const void* X, const void* W, const float* gamma, const float* beta, float eps, const float* bias,
               const float* residual, void* Y, int M, int N, int K, int ldx, int ldy, int act, const SpKvScatter& kv,
               const float* stats_in, float* stats_out, int* dev_err, cudaStream_t stream) {
     const SpPlan plan = sp_plan(M, N, K, BN, LN);
@@ -409,7 +509,7 @@ int launch_sp(const void* X, const void* W, const float* gamma, const float* bet
     } else {
         tx = tw;   // unused
     }
-    auto kern = gemm_splitk_kernel<BN, OT, LN>;
+    auto kern = gemm_splitk_kernel<BN, OT, LN, WIDE>;
     static bool clusters_allowed = false;
     if (!clusters_allowed) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
@@ -428,6 +528,18 @@ int launch_sp(const void* X, const void* W, const float* gamma, const float* bet
                                            dev_err);
     if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "gemm_splitk: %s", cudaGetErrorString(e));
     return vlrf_check_launch("gemm_splitk");
+}
+// many rows: more than four one-column pieces a warp would be a long chain of reads of the other CTAs' memory
+template <int BN, typename OT, bool LN>
+int launch_sp(const void* X, const void* W, const float* gamma, const float* beta, float eps, const float* bias,
+              const float* residual, void* Y, int M, int N, int K, int ldx, int ldy, int act, const SpKvScatter& kv,
+              const float* stats_in, float* stats_out, int* dev_err, cudaStream_t stream) {
+    const SpPlan plan = sp_plan(M, N, K, BN, LN);
+    if (!LN && M * (plan.bm / 32) > 4 * 4 * plan.splits)
+        return launch_sp_as<BN, OT, LN, !LN>(X, W, gamma, beta, eps, bias, residual, Y, M, N, K, ldx, ldy, act, kv, stats_in,
+                                             stats_out, dev_err, stream);
+    return launch_sp_as<BN, OT, LN, false>(X, W, gamma, beta, eps, bias, residual, Y, M, N, K, ldx, ldy, act, kv, stats_in,
+                                           stats_out, dev_err, stream);
 }
 }  // namespace
 
