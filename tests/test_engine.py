@@ -170,3 +170,41 @@ def test_gpt2_real_widths_whole_tail_and_batch(wide_model, dtype, tol):
     compare(drive_tail_one_by_one(eng, reqs, 20), truth, tol, "GPT-2 widths, prefix + 20 single tokens")
     compare(drive_batches(eng, reqs, 3, [50, 130, 1]), truth, tol, "GPT-2 widths, unequal batch")
     assert eng.cache.slots.n_held == 0
+
+
+def test_launch_chaining_changes_no_bit(wide_model):
+    """Kernels that begin while those ahead still run (and fetch weights, earlier keys and values ahead of
+    their wait) must give exactly what plain stream order gives: the same logits, bit for bit, over prompt
+    steps, decode steps and a replayed decode session."""
+    from vlrf_b200.csrc import ops
+    from vlrf_b200.engine import Engine, StepEntry, load_model
+    from vlrf_b200.engine.decode import DecodeSession
+    d, reqs, _ = wide_model
+    model = load_model(d, "bfloat16")
+
+    def run():
+        eng = Engine(model, max_tokens=64 * 8)
+        poison(eng)
+        got = drive_tail_one_by_one(eng, reqs, 12)
+        long = [r for r in reqs if len(r) > 41]
+        slots = [eng.start_sequence() for _ in long]
+        eng.step([StepEntry(s, r[:40], []) for s, r in zip(slots, long)])
+        sess = DecodeSession(eng, slots, use_graph=True)
+        sess.reserve_ahead(8)
+        sess.set_tokens([r[40] for r in long])
+        out = torch.zeros(len(slots), dtype=torch.int32, device=eng.device)
+        for _ in range(6):
+            got.append(sess.step_greedy(out).float().cpu().clone())
+        for s in slots:
+            eng.end_sequence(s)
+        return got
+
+    try:
+        chained = run()
+        ops.set_chained_launch(False)
+        plain_order = run()
+    finally:
+        ops.set_chained_launch(True)
+    assert len(chained) == len(plain_order)
+    for a, b in zip(chained, plain_order):
+        assert torch.equal(a, b)
