@@ -233,9 +233,13 @@ def test_split_k_layernorm_from_row_statistics(split_k_always, M, N, K, out_dtyp
         assert rel_err(out.float().cpu(), want_for(x)) < tol
     ops.linear(x0.to(DEV), w0.to(DEV), None, x, residual=x)
     assert ops._row_stats_of(x, M, K) is not None
-    ops.embed(randn(50, K, seed=48).to(DEV), None, torch.zeros(M, dtype=torch.int32, device=DEV), None, x,
+    # the embedding leaves statistics of the rows it writes, too
+    table = (randn(50, K, seed=48) * 3 + 20).to(DEV)
+    ops.embed(table, None, torch.arange(M, dtype=torch.int32, device=DEV) * 3, None, x,
               torch.zeros(1, dtype=torch.int32, device=DEV))
-    assert ops._row_stats_of(x, M, K) is None
+    assert ops._row_stats_of(x, M, K) is not None
+    ops.linear_layernorm(x, gamma.to(DEV), beta.to(DEV), eps, w.to(DEV), b.to(DEV), out, act=act)
+    assert rel_err(out.float().cpu(), want_for(x)) < tol
     ops.linear(x0.to(DEV), w0.to(DEV), None, x, residual=x)
     ops.residual_written(x)
     assert ops._row_stats_of(x, M, K) is None

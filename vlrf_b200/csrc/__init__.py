@@ -26,7 +26,7 @@ _c_int, _c_float, _c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
 _SIGNATURES = {
     "vlrf_device_info": [ctypes.POINTER(_c_int)] * 4,
     "vlrf_embed": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
-                   _c_void_p, _c_void_p],
+                   _c_void_p, _c_void_p, _c_void_p],
     "vlrf_layernorm": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float,
                        _c_void_p],
     "vlrf_gemm_simt": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,

@@ -1,7 +1,9 @@
 // Embedding gather with learned positions, and LayerNorm.
 //
 // embed:      x[t,:] = wte[token[t],:] (+ wpe[position[t],:])          -> float32 residual stream
-//             (reference: include/model/ops.hpp:615-626, include/model/transformer.hpp:350-361)
+//             (reference: include/model/ops.hpp:615-626, include/model/transformer.hpp:350-361);
+//             optionally also the rows' statistics per 32-column segment (sum, squared deviation from the
+//             segment's mean), which a product with a fused LayerNorm then uses instead of reading rows whole
 // layernorm:  y = (x-mean) * 1/sqrt(var+eps) * gamma + beta, two passes over the row held in
 //             shared memory, statistics in float32, biased variance
 //             (reference: include/model/ops.hpp:443-476)
@@ -10,7 +12,8 @@
 template <typename WT>
 __global__ void embed_pos_kernel(const WT* __restrict__ wte, const WT* __restrict__ wpe,
                                  const int* __restrict__ tokens, const int* __restrict__ positions,
-                                 float* __restrict__ x, int d, int V, int P, int* __restrict__ dev_err) {
+                                 float* __restrict__ x, int d, int V, int P, float* __restrict__ stats,
+                                 int* __restrict__ dev_err) {
     const int t = blockIdx.x;
     pdl_wait();
     pdl_launch_dependents();
@@ -21,23 +24,39 @@ __global__ void embed_pos_kernel(const WT* __restrict__ wte, const WT* __restric
     }
     const WT* e = wte + (size_t)tok * d;
     float* out = x + (size_t)t * d;
+    const WT* p = nullptr;
     if (wpe != nullptr) {
         int pos = positions[t];
         if (pos < 0 || pos >= P) {
             if (threadIdx.x == 0) atomicOr(dev_err, VLRF_DEVERR_POSITION_RANGE);
             pos = min(max(pos, 0), P - 1);
         }
-        const WT* p = wpe + (size_t)pos * d;
-        for (int i = threadIdx.x; i < d; i += blockDim.x)
-            out[i] = ElemIO<WT>::load(e + i) + ElemIO<WT>::load(p + i);
-    } else {
-        for (int i = threadIdx.x; i < d; i += blockDim.x) out[i] = ElemIO<WT>::load(e + i);
+        p = wpe + (size_t)pos * d;
+    }
+    // a warp takes 32 consecutive columns at a time: one segment of the statistics
+    const int lane = threadIdx.x & 31;
+    for (int base = (threadIdx.x >> 5) * 32; base < d; base += blockDim.x) {
+        const int i = base + lane;
+        float v = 0.f;
+        if (i < d) {
+            v = ElemIO<WT>::load(e + i) + (p != nullptr ? ElemIO<WT>::load(p + i) : 0.f);
+            out[i] = v;
+        }
+        if (stats != nullptr) {
+            const float sum = warp_sum(v);
+            const float dev = i < d ? v - sum / (float)min(32, d - base) : 0.f;
+            const float m2 = warp_sum(dev * dev);
+            if (lane == 0) {
+                float* so = stats + ((size_t)t * ((d + 31) >> 5) + (base >> 5)) * 2;
+                so[0] = sum; so[1] = m2;
+            }
+        }
     }
 }
 
 extern "C" int vlrf_embed(const void* wte, const void* wpe, int w_dtype, const int* tokens,
-                          const int* positions, float* x, int T, int d, int V, int P, int* dev_err,
-                          cudaStream_t stream) {
+                          const int* positions, float* x, int T, int d, int V, int P,
+                          float* stats /* or null: [T][ceil(d/32)][2] */, int* dev_err, cudaStream_t stream) {
     VLRF_REQUIRE(T >= 0 && d > 0 && V > 0, "embed: bad sizes T=%d d=%d V=%d", T, d, V);
     VLRF_REQUIRE(wpe == nullptr || (positions != nullptr && P > 0), "embed: a position table needs positions");
     VLRF_REQUIRE(dev_err != nullptr, "embed: needs the device error word");
@@ -45,10 +64,10 @@ extern "C" int vlrf_embed(const void* wte, const void* wpe, int w_dtype, const i
     const int threads = d >= 256 ? 256 : 128;
     if (w_dtype == VLRF_F32)
         launch_chained(embed_pos_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)wte, (const float*)wpe,
-                       tokens, positions, x, d, V, P, dev_err);
+                       tokens, positions, x, d, V, P, stats, dev_err);
     else if (w_dtype == VLRF_BF16)
         launch_chained(embed_pos_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (const __nv_bfloat16*)wte,
-                       (const __nv_bfloat16*)wpe, tokens, positions, x, d, V, P, dev_err);
+                       (const __nv_bfloat16*)wpe, tokens, positions, x, d, V, P, stats, dev_err);
     else
         return vlrf_fail(VLRF_ERR_INVALID_ARG, "embed: unknown weight dtype %d", w_dtype);
     return vlrf_check_launch("embed");

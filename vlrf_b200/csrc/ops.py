@@ -54,8 +54,12 @@ def embed(wte, wpe, tokens, positions, out, dev_err) -> None:
     if out.shape[0] < T or out.shape[1] != d:
         raise KernelError("embed: output does not match")
     _written(out)
+    keep = 0 < T <= ROW_STATS_MAX_ROWS and d <= ROW_STATS_MAX_WIDTH     # few rows: a decode step; leave their statistics
     call("vlrf_embed", _ptr(wte), _ptr(wpe), dtype_code(wte.dtype), _ptr(tokens), _ptr(positions), _ptr(out),
-         T, d, V, P, _ptr(dev_err), _stream())
+         T, d, V, P, _ptr(_row_stats_buffer()) if keep else 0, _ptr(dev_err), _stream())
+    if keep:
+        global _ROW_STATS_OF
+        _ROW_STATS_OF = (out, out._version, T, d)
 
 
 def layernorm(x, gamma, beta, eps: float, out, rows=None) -> None:
@@ -105,11 +109,13 @@ PREFILL_ATTENTION_TCGEN05 = True     # head size 64; off: the mma.sync kernel ta
 SKINNY_MAX_ROWS = 64
 FUSED_NORM_MAX_ROWS = 16
 SWAPPED_MIN_COLUMNS = 16384
-#: Few-row products whose weight matrix has at least this many bytes go to the split-k tcgen05 kernel; below
-#: that the whole product is a handful of latencies, and the kernel whose CTAs need no cluster is as fast.
-#: With the LayerNorm fused in, the split-k kernel wins only for larger matrices (measured on B200).
-SPLITK_MIN_WEIGHT_BYTES = 3 << 20
-SPLITK_NORM_MIN_WEIGHT_BYTES = 12 << 20
+#: Few-row products whose weight matrix has at least this many bytes go to the split-k tcgen05 kernel (the
+#: second figure: with the LayerNorm fused in).  Measured on B200 inside whole decode steps, the split-k kernel
+#: wins at every size of GPT-2's: its CTAs leave room on an SM for the next kernel's to begin ahead, and it
+#: passes on the row statistics that the next LayerNorm needs.  The `mma.sync` kernel remains for the shapes
+#: the split-k kernel refuses and for a LayerNorm of rows whose statistics nobody left.
+SPLITK_MIN_WEIGHT_BYTES = 0
+SPLITK_NORM_MIN_WEIGHT_BYTES = 0
 _DEV_ERR = None
 
 
