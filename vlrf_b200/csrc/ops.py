@@ -291,8 +291,10 @@ def linear_layernorm(x, gamma, beta, eps: float, w, bias, out, *, act=None, rows
 
 
 def decode_splits(n_rows: int, n_heads: int, max_context: int) -> int:
-    """Into how many parts a decode step cuts each context so that every SM has work."""
-    want = -(-2 * sm_count() // max(1, n_rows * n_heads))
+    """Into how many parts a decode step cuts each context: about two CTAs an SM (measured inside whole
+    steps: more CTAs than that cost more than they hide), parts of at least 128 keys."""
+    pairs = max(1, n_rows * n_heads)
+    want = 2 * sm_count() // pairs if 2 * sm_count() >= 2 * pairs else -(-2 * sm_count() // pairs)
     return max(1, min(16, want, -(-max_context // 128)))
 
 
