@@ -608,10 +608,10 @@ extern "C" int vlrf_sample(const float* logits, int ld, int n_rows, int V, const
     VLRF_REQUIRE(temperature == nullptr || (rng_key != nullptr && rng_ctr != nullptr),
                  "sample: temperature sampling needs the rows' random keys and counters");
     if (n_rows == 0) return VLRF_OK;
-    // rows that may draw: a cluster of CTAs a row, if a CTA's share of e_i fits its shared memory
+    // a cluster of CTAs a row, if a CTA's share of e_i fits its shared memory
     const int S = (V + SC - 1) / SC;
     const size_t smem = (size_t)S * sizeof(unsigned int) + (size_t)(STC / 32) * 256 * 3 * sizeof(unsigned int);
-    if (temperature != nullptr && smem <= 160 * 1024) {
+    if (smem <= 160 * 1024) {
         static size_t allowed = 48 * 1024 - 16 * 1024;     // (the kernel's static shared memory comes on top)
         if (smem > allowed) {
             cudaError_t e = cudaFuncSetAttribute(sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
