@@ -13,6 +13,7 @@
 // Scratch: partials float32 [rows][heads][n_split][head_dim + 2], counters int32 [rows][heads] that are
 // zero between calls.  The caller provides both.
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace {
 
@@ -508,6 +509,254 @@ int launch_bulk(dim3 grid, const void* qkv, int ld, int q_off, const void* Kc, c
     if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "attn_decode: %s", cudaGetErrorString(e));
     return vlrf_check_launch("attn_decode");
 }
+// ---------------------------------------------------------------------------------------------------------
+// bfloat16, head size 64: the same split-context attention with the two products on the tensor cores.
+// A chunk of 32 keys (and values) arrives by a tiled TMA load with the 128-byte swizzle, so that `ldmatrix`
+// reads it without bank conflicts.  A warp takes a chunk: S = q·Kᵀ as `mma.sync.m16n8k16` with the query in
+// row 0 of the 16-row operand (the other rows are zeros), the softmax on the four lanes that hold row 0, P
+// packed to bfloat16 straight from the accumulator registers, O += P·V with V read through transposing
+// `ldmatrix`.  About a fifth of the instructions of the FMA kernel above, which stays for float32 and other
+// head sizes.  Prefetch before the wait, merge of the warps and of the parts: as above.
+__device__ __forceinline__ void dldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void dldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void dmma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t dpack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+// address of the 16-byte piece `piece` (0…7) of row `row` of a [32][128 B] tile written with the 128-byte swizzle
+__device__ __forceinline__ uint32_t dtile_addr(uint32_t base, int row, int piece) {
+    return base + row * 128 + ((piece ^ (row & 7)) << 4);
+}
+
+template <bool CLUSTER>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+attn_decode_mma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                       const __nv_bfloat16* __restrict__ qkv, int ld, int q_off, const int* __restrict__ block_table,
+                       int max_blocks, const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
+                       __nv_bfloat16* __restrict__ out, int ld_out, int H, int Hkv, int BT, float scale, int window,
+                       int n_split, float* __restrict__ partials, int* __restrict__ counters, int* __restrict__ dev_err) {
+    constexpr int DH = 64, CHUNK_BYTES = 32 * DH * 2, CH_MAX = 8;
+    extern __shared__ unsigned char dsm_raw[];
+    unsigned char* dsm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(dsm_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* kbuf = dsm;                                                // [CH_MAX][32][128 B]
+    unsigned char* vbuf = kbuf + (size_t)CH_MAX * CHUNK_BYTES;
+    float* wpart = reinterpret_cast<float*>(vbuf + (size_t)CH_MAX * CHUNK_BYTES);   // [DEC_WARPS][DH + 2]
+    float* cpart = wpart + DEC_WARPS * (DH + 2);                              // [DH + 2] (CLUSTER)
+    uint64_t* bars = reinterpret_cast<uint64_t*>(cpart + DH + 2);            // CH_MAX barriers
+    __shared__ int s_last;
+    __shared__ int s_bad;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int row = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
+    if (threadIdx.x == 0) { tma_prefetch_descriptor(&tmap_k); tma_prefetch_descriptor(&tmap_v); }   // under the table reads
+    // before the wait: positions, tables and the cache of earlier positions (see the kernel above)
+    const int slot = tok_slot[row];
+    if (slot < 0) return;                          // padding row: the whole CTA (and its cluster) leaves
+    const int pos = tok_pos[row];
+    const int hk = h / (H / Hkv);
+    const int first = (window > 0) ? max(0, pos - window + 1) : 0;
+    const int chunk0 = first / 32;
+    const int n_chunks = pos / 32 + 1 - chunk0;
+    const int per_split = (n_chunks + n_split - 1) / n_split;
+    const int c_begin = chunk0 + split * per_split;
+    const int c_end = min(chunk0 + n_chunks, c_begin + per_split);
+    const int c_new = pos / 32;                    // the chunk with the key that the kernel ahead writes
+    const int* table = block_table + (size_t)slot * max_blocks;
+
+    if (threadIdx.x == 0) {
+        s_bad = 0;
+        for (int i = 0; i < CH_MAX; ++i) dmbar_init(&bars[i], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    auto request = [&](int r0) -> bool {           // thread i requests chunk r0 + i of a round into buffer i
+        const int k0 = (r0 + threadIdx.x) * 32;
+        const int blk = table[k0 / BT];
+        if (blk < 0) {
+            atomicOr(dev_err, VLRF_DEVERR_NO_BLOCK);
+            s_bad = 1;
+            return false;
+        }
+        const int y = (blk * Hkv + hk) * BT + (k0 % BT);
+        dmbar_expect_tx(&bars[threadIdx.x], 2 * CHUNK_BYTES);
+        tma_load_2d(kbuf + (size_t)threadIdx.x * CHUNK_BYTES, &tmap_k, 0, y, &bars[threadIdx.x]);
+        tma_load_2d(vbuf + (size_t)threadIdx.x * CHUNK_BYTES, &tmap_v, 0, y, &bars[threadIdx.x]);
+        return true;
+    };
+    bool issued = false;
+    if ((int)threadIdx.x < min(CH_MAX, c_end - c_begin) && c_begin + (int)threadIdx.x != c_new) issued = request(c_begin);
+    pdl_wait();                                    // the new key and value and the query are written
+    pdl_launch_dependents();
+    // the query as rows 0 of the MMA's 16-row operand: only lanes 0-3 hold anything but zeros
+    uint32_t qa[4][2];
+    {
+        const __nv_bfloat16* qsrc = qkv + (size_t)row * ld + q_off + (size_t)h * DH;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            qa[ks][0] = g == 0 ? *reinterpret_cast<const uint32_t*>(qsrc + 16 * ks + 2 * t) : 0u;
+            qa[ks][1] = g == 0 ? *reinterpret_cast<const uint32_t*>(qsrc + 16 * ks + 8 + 2 * t) : 0u;
+        }
+    }
+    const float sl2 = scale * 1.4426950408889634f;       // scores in units of log2(e)
+
+    float o[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+    float m = -INFINITY, l = 0.f;
+    bool gave_up = false;
+    uint32_t parity = 0;
+    for (int r0 = c_begin; r0 < c_end; r0 += CH_MAX) {
+        const int n_here = min(CH_MAX, c_end - r0);
+        if (r0 > c_begin) {
+            issued = false;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // reads of the buffers before refilling them
+        }
+        if ((int)threadIdx.x < n_here && (r0 > c_begin || r0 + (int)threadIdx.x == c_new)) issued = request(r0);
+        __syncthreads();                           // s_bad is known
+        if (s_bad) {                               // leave only after the copies already issued have landed
+            if (issued) {
+                uint32_t polls = 0;
+                while (!dmbar_try_wait(&bars[threadIdx.x], parity) && ++polls <= DEC_WAIT_LIMIT) {}
+            }
+            __syncthreads();
+            break;
+        }
+        for (int i = warp; i < n_here && !gave_up; i += DEC_WARPS) {
+            uint32_t polls = 0;
+            while (!dmbar_try_wait(&bars[i], parity)) {
+                if (++polls > DEC_WAIT_LIMIT) { gave_up = true; break; }
+            }
+            if (gave_up) break;
+            const int k0 = (r0 + i) * 32;
+            const uint32_t kb = dsmem_u32(kbuf + (size_t)i * CHUNK_BYTES), vb = dsmem_u32(vbuf + (size_t)i * CHUNK_BYTES);
+            // Rows of the chunk behind the newest key hold whatever was there before; their scores are masked by
+            // assignment below, but 0 · V would let a stray NaN through the MMA: clear those rows of V.
+            const int valid = pos - k0 + 1;        // keys of this chunk that exist (at least 1)
+            if (valid < 32) {
+                unsigned char* vt = vbuf + (size_t)i * CHUNK_BYTES;
+                for (int idx = lane; idx < (32 - valid) * 8; idx += 32)
+                    *reinterpret_cast<uint4*>(vt + (valid + (idx >> 3)) * 128 + ((idx & 7) << 4)) = make_uint4(0, 0, 0, 0);
+                __syncwarp();
+            }
+            float s[4][4];
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f; }
+#pragma unroll
+            for (int ks = 0; ks < 4; ks += 2) {
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) {
+                    // matrices: (keys 8nt…, dims of k-step ks: low, high half), (same keys, k-step ks+1: low, high half)
+                    uint32_t b0, b1, b2, b3;
+                    dldsm_x4(dtile_addr(kb, nt * 8 + (lane & 7), ks * 2 + (lane >> 3)), b0, b1, b2, b3);
+                    dmma16816(s[nt], qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
+                    dmma16816(s[nt], qa[ks + 1][0], 0u, qa[ks + 1][1], 0u, b2, b3);
+                }
+            }
+            // row 0 of S lies in lanes 0-3: keys k0 + 8nt + 2t and + 1; the other lanes hold rows of zeros
+            float cmax = -INFINITY;
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int key = k0 + nt * 8 + 2 * t + e;
+                    const float v = (g == 0 && key >= first && key <= pos) ? s[nt][e] * sl2 : -INFINITY;
+                    s[nt][e] = v;
+                    cmax = fmaxf(cmax, v);
+                }
+            cmax = fmaxf(cmax, __shfl_xor_sync(0xffffffffu, cmax, 1));
+            cmax = fmaxf(cmax, __shfl_xor_sync(0xffffffffu, cmax, 2));
+            const float m_new = fmaxf(m, cmax);
+            const float m_use = (m_new == -INFINITY) ? 0.f : m_new;      // (lanes beside row 0: every p is 0)
+            const float corr = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
+            float psum = 0.f;
+            uint32_t pa[4];
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                const float p0 = exp2f(s[nt][0] - m_use), p1 = exp2f(s[nt][1] - m_use);
+                psum += p0 + p1;
+                pa[nt] = dpack_bf16(p0, p1);
+            }
+            psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+            psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+            l = l * corr + psum;
+            m = m_new;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { o[j][0] *= corr; o[j][1] *= corr; }
+#pragma unroll
+            for (int kk = 0; kk < 2; ++kk) {
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) {
+                    // transposed loads: (keys 16kk…+7, dims 8j…), (keys +8…, same dims), then the same for dims 8(j+1)…
+                    uint32_t b0, b1, b2, b3;
+                    dldsm_x4_trans(dtile_addr(vb, kk * 16 + (lane & 15), j + (lane >> 4)), b0, b1, b2, b3);
+                    dmma16816(o[j], pa[2 * kk], 0u, pa[2 * kk + 1], 0u, b0, b1);
+                    dmma16816(o[j + 1], pa[2 * kk], 0u, pa[2 * kk + 1], 0u, b2, b3);
+                }
+            }
+        }
+        if (gave_up) s_bad = 1;
+        parity ^= 1;
+        __syncthreads();                           // everyone is done with the buffers before they are refilled
+        if (s_bad) break;
+    }
+    if (gave_up && lane == 0) atomicOr(dev_err, VLRF_DEVERR_WAIT_TIMEOUT);
+
+    // this warp's (maximum, sum, outputs): row 0 lies in lanes 0-3, dimensions 8j + 2t and + 1; the merge
+    // works with natural logarithms
+    float* mine = wpart + warp * (DH + 2);
+    if (lane == 0) { mine[0] = m * 0.6931471805599453f; mine[1] = l; }
+    if (g == 0) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { mine[2 + 8 * j + 2 * t] = o[j][0]; mine[2 + 8 * j + 2 * t + 1] = o[j][1]; }
+    }
+    __syncthreads();
+    if (CLUSTER) finish_cluster<__nv_bfloat16>(wpart, cpart, DH, row, h, split, n_split, out, ld_out);
+    else finish_cta<__nv_bfloat16>(wpart, DH, row, h, H, split, n_split, partials, counters, out, ld_out, &s_last);
+}
+
+int launch_mma(dim3 grid, const void* qkv, int ld, int q_off, const void* Kc, const void* Vc, long long kv_rows,
+               const int* block_table, int max_blocks, const int* tok_slot, const int* tok_pos, void* out, int ld_out,
+               int H, int Hkv, int BT, float scale, int window, int n_split, float* partials, int* counters,
+               int* dev_err, cudaStream_t stream) {
+    CUtensorMap tk, tv;
+    int st = vlrf_make_tmap_bf16(Kc, kv_rows, 64, 64, 32, 64, &tk);
+    if (st != VLRF_OK) return st;
+    st = vlrf_make_tmap_bf16(Vc, kv_rows, 64, 64, 32, 64, &tv);
+    if (st != VLRF_OK) return st;
+    const size_t smem = 1024 + (size_t)2 * 8 * 4096 + (size_t)(DEC_WARPS + 1) * (64 + 2) * sizeof(float) + 8 * 8;
+    const bool cluster = n_split > 1 && n_split <= DEC_MAX_CLUSTER && partials == nullptr;
+    auto kern = cluster ? attn_decode_mma_kernel<true> : attn_decode_mma_kernel<false>;
+    static bool raised[2] = {false, false};
+    if (!raised[cluster]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess && cluster) e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "attn_decode: %zu bytes of shared memory, clusters: %s", smem, cudaGetErrorString(e));
+        raised[cluster] = true;
+    }
+    cudaError_t e;
+    if (cluster)
+        e = launch_chained_cluster(kern, grid, dim3(DEC_WARPS * 32), smem, dim3(1, 1, n_split), stream, tk, tv,
+                                   (const __nv_bfloat16*)qkv, ld, q_off, block_table, max_blocks, tok_slot, tok_pos,
+                                   (__nv_bfloat16*)out, ld_out, H, Hkv, BT, scale, window, n_split, partials, counters, dev_err);
+    else
+        e = launch_chained(kern, grid, dim3(DEC_WARPS * 32), smem, stream, tk, tv, (const __nv_bfloat16*)qkv, ld, q_off,
+                           block_table, max_blocks, tok_slot, tok_pos, (__nv_bfloat16*)out, ld_out, H, Hkv, BT, scale,
+                           window, n_split, partials, counters, dev_err);
+    if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "attn_decode: %s", cudaGetErrorString(e));
+    return vlrf_check_launch("attn_decode");
+}
 }  // namespace
 
 // Whether a context cut into n_split parts needs scratch from the caller (else the parts' CTAs form a
@@ -521,7 +770,8 @@ extern "C" long long vlrf_attn_decode_scratch_floats(int rows, int H, int dh, in
     return (long long)rows * H * n_split * (dh + 2);
 }
 
-static int attn_decode_impl(const void* qkv, int dtype, int ld, int q_off, const void* Kc, const void* Vc,
+// n_blocks: blocks of the cache (for the tensor-core kernel's tensor maps), or 0 if the caller does not say
+static int attn_decode_impl(const void* qkv, int dtype, int ld, int q_off, const void* Kc, const void* Vc, int n_blocks,
                             const int* block_table, int max_blocks, const int* tok_slot, const int* tok_pos,
                             void* out, int ld_out, int rows, int H, int Hkv, int dh, int BT, float scale,
                             int window, int n_split, float* partials, int* counters, int* dev_err,
@@ -539,6 +789,9 @@ static int attn_decode_impl(const void* qkv, int dtype, int ld, int q_off, const
     VLRF_REQUIRE(window >= 0 && dev_err != nullptr, "attn_decode: bad window or no error word");
     if (rows == 0) return VLRF_OK;
     dim3 grid(rows, H, n_split);
+    if (dtype == VLRF_BF16 && dh == 64 && n_blocks > 0 && ld % 2 == 0 && q_off % 2 == 0)
+        return launch_mma(grid, qkv, ld, q_off, Kc, Vc, (long long)n_blocks * Hkv * BT, block_table, max_blocks, tok_slot, tok_pos,
+                          out, ld_out, H, Hkv, BT, scale, window, n_split, partials, counters, dev_err, stream);
 #define BULK(ET, DHT) return launch_bulk<ET, DHT>(grid, qkv, ld, q_off, Kc, Vc, block_table, max_blocks, tok_slot, tok_pos, \
                                                   out, ld_out, H, Hkv, BT, scale, window, n_split, partials, counters, dev_err, stream)
     if (dtype == VLRF_BF16 && dh == 64) BULK(__nv_bfloat16, 64);
@@ -562,11 +815,11 @@ static int attn_decode_impl(const void* qkv, int dtype, int ld, int q_off, const
 }
 
 extern "C" int vlrf_attn_decode(const void* qkv, int dtype, int ld, int q_off, const void* Kc, const void* Vc,
-                                const int* block_table, int max_blocks, const int* tok_slot,
+                                int n_blocks, const int* block_table, int max_blocks, const int* tok_slot,
                                 const int* tok_pos, void* out, int ld_out, int rows, int H, int Hkv, int dh,
                                 int BT, float scale, int window, int n_split, float* partials, int* counters,
                                 int* dev_err, cudaStream_t stream) {
-    return attn_decode_impl(qkv, dtype, ld, q_off, Kc, Vc, block_table, max_blocks, tok_slot, tok_pos, out, ld_out,
+    return attn_decode_impl(qkv, dtype, ld, q_off, Kc, Vc, n_blocks, block_table, max_blocks, tok_slot, tok_pos, out, ld_out,
                             rows, H, Hkv, dh, BT, scale, window, n_split, partials, counters, dev_err, stream);
 }
 
@@ -626,6 +879,6 @@ extern "C" int vlrf_attn_decode_noalloc(const void* qkv, int dtype, int ld, int 
         e = cudaMemsetAsync(counters, 0, (size_t)rows * H * sizeof(int), stream);
         if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "attn_decode_noalloc: clearing the counters: %s", cudaGetErrorString(e));
     }
-    return attn_decode_impl(qkv, dtype, ld, q_off, Kc, Vc, block_table, max_blocks, tok_slot, tok_pos, out, ld_out,
+    return attn_decode_impl(qkv, dtype, ld, q_off, Kc, Vc, 0, block_table, max_blocks, tok_slot, tok_pos, out, ld_out,
                             rows, H, Hkv, dh, BT, scale, window, n_split, partials, counters, dev_err, stream);
 }

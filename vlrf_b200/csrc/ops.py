@@ -291,11 +291,12 @@ def linear_layernorm(x, gamma, beta, eps: float, w, bias, out, *, act=None, rows
 
 
 def decode_splits(n_rows: int, n_heads: int, max_context: int) -> int:
-    """Into how many parts a decode step cuts each context: about two CTAs an SM (measured inside whole
-    steps: more CTAs than that cost more than they hide), parts of at least 128 keys."""
+    """Into how many parts a decode step cuts each context.  Measured inside whole steps of GPT-2 small,
+    medium and XL: up to about 1.75 CTAs an SM in all, parts of at least 256 keys; more CTAs than that cost
+    more (shared memory that the next kernel's CTAs would use, clusters to place) than they hide."""
     pairs = max(1, n_rows * n_heads)
-    want = 2 * sm_count() // pairs if 2 * sm_count() >= 2 * pairs else -(-2 * sm_count() // pairs)
-    return max(1, min(16, want, -(-max_context // 128)))
+    want = (7 * sm_count()) // (4 * pairs)
+    return max(1, min(16, want, -(-max_context // 256)))
 
 
 def attention_decode_needs_scratch(head_dim: int, n_split: int) -> bool:
@@ -325,7 +326,7 @@ def attention_decode(qkv, q_off: int, k_cache, v_cache, block_table, tok_slot, t
         if partials.numel() < n_rows * n_heads * n_split * (head_dim + 2) or counters.numel() < n_rows * n_heads:
             raise KernelError("attention_decode: scratch is too small")
     _written(out)
-    call("vlrf_attn_decode", _ptr(qkv), dtype_code(qkv.dtype), qkv.shape[1], q_off, _ptr(k_cache), _ptr(v_cache),
+    call("vlrf_attn_decode", _ptr(qkv), dtype_code(qkv.dtype), qkv.shape[1], q_off, _ptr(k_cache), _ptr(v_cache), nb,
          _ptr(block_table), block_table.shape[1], _ptr(tok_slot), _ptr(tok_pos), _ptr(out), out.shape[1], n_rows,
          n_heads, n_kv_heads, head_dim, bt, float(scale), int(window), int(n_split), _ptr(partials), _ptr(counters),
          _ptr(dev_err), _stream())
