@@ -103,3 +103,17 @@ def test_get_logits_and_summary(model_dirs, plain_models):
     every = model.get_logits(ids, all_positions=True)
     assert every.shape == (33, 1000)
     assert "n_embd=96" in model.model_summary() and model.kv_cache_bytes() > 0
+
+
+def test_generation_inside_inference_mode(model_dirs):
+    """torch's inference mode keeps no version counters of tensors; whatever the kernels' dispatch derives
+    from them must fall back, and the tokens stay the same."""
+    from conftest import random_ids
+    from vlrf_b200 import Model, SamplingParams
+    prompts = [random_ids(1000, n, 900 + n) for n in (5, 21)]
+    params = SamplingParams(max_new_tokens=10, do_sample=False, stop_token_ids=())
+    want = Model.load(model_dirs["tiny_b"], dtype="bfloat16", max_tokens=256).generate_ids(prompts, params)
+    with torch.inference_mode():
+        model = Model.load(model_dirs["tiny_b"], dtype="bfloat16", max_tokens=256)
+        got = model.generate_ids(prompts, params)
+    assert [r.new_tokens for r in got] == [r.new_tokens for r in want]

@@ -58,8 +58,7 @@ def embed(wte, wpe, tokens, positions, out, dev_err) -> None:
     call("vlrf_embed", _ptr(wte), _ptr(wpe), dtype_code(wte.dtype), _ptr(tokens), _ptr(positions), _ptr(out),
          T, d, V, P, _ptr(_row_stats_buffer()) if keep else 0, _ptr(dev_err), _stream())
     if keep:
-        global _ROW_STATS_OF
-        _ROW_STATS_OF = (out, out._version, T, d)
+        _keep_row_stats(out, T, d)
 
 
 def layernorm(x, gamma, beta, eps: float, out, rows=None) -> None:
@@ -136,6 +135,21 @@ def _row_stats_buffer() -> torch.Tensor:
     return _ROW_STATS
 
 
+def _version_of(t) -> int:
+    """torch's count of in-place changes of a tensor, or −1 where it is not kept (inference mode): then no
+    statistics are kept either, since a change behind their back could not be seen."""
+    try:
+        return t._version
+    except RuntimeError:
+        return -1
+
+
+def _keep_row_stats(t, rows: int, width: int) -> None:
+    global _ROW_STATS_OF
+    v = _version_of(t)
+    _ROW_STATS_OF = (t, v, rows, width) if v >= 0 else None
+
+
 def _written(t) -> None:
     """Every function here that writes a tensor says so: statistics kept of it are stale then."""
     global _ROW_STATS_OF
@@ -154,7 +168,7 @@ def _row_stats_of(x, rows: int, width: int):
     if _ROW_STATS_OF is None:
         return None
     held, version, n_rows, n_cols = _ROW_STATS_OF
-    if held.data_ptr() == x.data_ptr() and x._version == version and (n_rows, n_cols) == (rows, width):
+    if held.data_ptr() == x.data_ptr() and _version_of(x) == version and (n_rows, n_cols) == (rows, width):
         return _ROW_STATS
     return None
 
@@ -234,8 +248,7 @@ def _linear_dispatch(x, w, bias, out, act, residual, M, N, K, kv_scatter=None) -
              M, N, K, K, N, act, 0, 0, 0.0, *_kv_args(kv_scatter if scatter else None, N), 0,
              _ptr(_row_stats_buffer()) if keep else 0, _ptr(_dev_err()), _stream())
         if keep:
-            global _ROW_STATS_OF
-            _ROW_STATS_OF = (out, out._version, M, N)
+            _keep_row_stats(out, M, N)
         return scatter
     if x.dtype == torch.bfloat16 and M <= SKINNY_MAX_ROWS and K % 32 == 0:
         # few rows: the product is bound by streaming w once
