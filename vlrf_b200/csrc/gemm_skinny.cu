@@ -359,7 +359,7 @@ size_t smem_bytes(int MT16, int M, int xmode, int K, int CG, int S) {
            (size_t)2 * SK_WARPS * MT16 * 4 * 32 * sizeof(float) + MAX_STAGES * MAX_SEG * 8;
 }
 
-constexpr size_t SMEM_BUDGET = 200 * 1024;
+constexpr size_t SMEM_LIMIT = 200 * 1024;
 
 template <int MT16, int XMODE, typename OT>
 int launch(const void* X, const void* W, const float* bias, const float* residual, void* Y, int M, int N, int K,
@@ -405,7 +405,7 @@ int tiles16(int M) { return M <= 16 ? 1 : (M <= 32 ? 2 : 4); }
 // Whether the LayerNorm-fused form holds M normalised rows of width K in shared memory.
 extern "C" int vlrf_gemm_skinny_ln_fits(int M, int K) {
     if (M < 1 || M > 64 || K % 32 != 0) return 0;
-    return smem_bytes(tiles16(M), M, 2, K, 1, 1) <= SMEM_BUDGET ? 1 : 0;
+    return smem_bytes(tiles16(M), M, 2, K, 1, 1) <= SMEM_LIMIT ? 1 : 0;
 }
 
 extern "C" int vlrf_gemm_skinny(const void* X, int x_is_f32_ln, const void* W, const float* bias,
@@ -424,7 +424,7 @@ extern "C" int vlrf_gemm_skinny(const void* X, int x_is_f32_ln, const void* W, c
     VLRF_REQUIRE(dev_err != nullptr, "gemm_skinny: needs the device error word");
     VLRF_REQUIRE(!x_is_f32_ln || (gamma && beta), "gemm_skinny: the fused LayerNorm needs weight and bias");
     VLRF_REQUIRE(!x_is_f32_ln || vlrf_gemm_skinny_ln_fits(M, K), "gemm_skinny: %d rows of width %d do not fit the fused LayerNorm", M, K);
-    VLRF_REQUIRE(smem_bytes(1, 1, 0, K, 1, 1) <= SMEM_BUDGET, "gemm_skinny: K=%d is too wide for shared memory", K);
+    VLRF_REQUIRE(smem_bytes(1, 1, 0, K, 1, 1) <= SMEM_LIMIT, "gemm_skinny: K=%d is too wide for shared memory", K);
     KvScatter kv{};
     if (Kc != nullptr) {
         VLRF_REQUIRE(Vc && block_table && tok_slot && tok_pos && Hkv > 0 && dh > 0 && BT > 0 && max_blocks > 0,
@@ -435,7 +435,7 @@ extern "C" int vlrf_gemm_skinny(const void* X, int x_is_f32_ln, const void* W, c
     const int mt16 = tiles16(M);
     // X in shared memory when it fits beside a slab; else read per fragment through L1/L2
     int xmode = x_is_f32_ln ? 2 : ((size_t)tiling(K).n_tiles * 16 * mt16 * 128 <= 100 * 1024 ? 1 : 0);
-    if (smem_bytes(mt16, M, xmode, K, 1, 1) > SMEM_BUDGET) {
+    if (smem_bytes(mt16, M, xmode, K, 1, 1) > SMEM_LIMIT) {
         VLRF_REQUIRE(xmode != 2, "gemm_skinny: fused LayerNorm does not fit");
         xmode = 0;
     }
@@ -447,7 +447,7 @@ extern "C" int vlrf_gemm_skinny(const void* X, int x_is_f32_ln, const void* W, c
     for (int cg = SK_WARPS; cg >= 1; cg /= 2) {
         const double slab = (double)8 * cg * tiling(K).n_tiles * 128;
         if (cg > 1 && slab > 64 * 1024) continue;
-        if (smem_bytes(mt16, M, xmode, K, cg, 1) > SMEM_BUDGET) continue;
+        if (smem_bytes(mt16, M, xmode, K, cg, 1) > SMEM_LIMIT) continue;
         const int groups = (N + 8 * cg - 1) / (8 * cg);
         const int ctas = groups < sm_count ? groups : sm_count;
         const int rounds = (groups + ctas - 1) / ctas;
@@ -459,7 +459,7 @@ extern "C" int vlrf_gemm_skinny(const void* X, int x_is_f32_ln, const void* W, c
     const int grid = groups < sm_count ? groups : sm_count;
     const int rounds = (groups + grid - 1) / grid;
     int S = rounds < MAX_STAGES ? rounds : MAX_STAGES;
-    while (S > 1 && smem_bytes(mt16, M, xmode, K, CG, S) > SMEM_BUDGET) --S;
+    while (S > 1 && smem_bytes(mt16, M, xmode, K, CG, S) > SMEM_LIMIT) --S;
     const int grid_x = grid;
 #define GO(XM, OT) return dispatch_mt<XM, OT>(mt16, X, W, bias, residual, Y, M, N, K, ldx, ldy, act, CG, S, grid_x, gamma, beta, eps, kv, dev_err, stream)
     if (out_dtype == VLRF_BF16) {

@@ -41,7 +41,7 @@ constexpr int SP_MAX_STAGES = 16;
 constexpr int SP_MAX_SPLITS = 16;        // the largest cluster (more than 8 is "non-portable": B200 takes it)
 constexpr int SP_LN_MAX_KB = 16;         // k blocks of one part with the fused norm (a lane holds 8 float4 of a row)
 constexpr int SP_STAT_SEGS = 256;        // most 32-column segments of a row whose statistics are kept (width ≤ 8192)
-constexpr size_t SP_SMEM_BUDGET = 111 * 1024;   // two CTAs fit an SM: this product's and the next one's, fetching ahead
+constexpr size_t SP_SMEM_LIMIT = 111 * 1024;   // two CTAs fit an SM: this product's and the next one's, fetching ahead
 
 struct SpKvScatter {
     void* Kc; void* Vc;
@@ -472,7 +472,7 @@ SpPlan sp_plan(int M, int N, int K, int bn, bool ln) {
     const int n_kb = (K + SP_BK - 1) / SP_BK;
     const int target = sp_sm_count();
     const int max_splits = SP_MAX_SPLITS;
-    const size_t budget = SP_SMEM_BUDGET;
+    const size_t limit = SP_SMEM_LIMIT;
     SpPlan best{};
     int best_ctas = -1;
     for (int bm = 128; bm >= 64; bm -= 64) {
@@ -483,7 +483,7 @@ SpPlan sp_plan(int M, int N, int K, int bn, bool ln) {
         if (splits < 1) splits = 1;
         const int kb_cap = (n_kb + splits - 1) / splits;
         int stages = kb_cap < SP_MAX_STAGES ? kb_cap : SP_MAX_STAGES;
-        while (stages > 1 && sp_smem(bm, bn, ln, stages, kb_cap, M, splits) > budget) --stages;
+        while (stages > 1 && sp_smem(bm, bn, ln, stages, kb_cap, M, splits) > limit) --stages;
         const int ctas = tiles * splits;
         const int useful = ctas < target ? ctas : target;
         if (best_ctas < 0 || useful * 2 >= best_ctas * 3) {      // 64-row tiles only for half as many CTAs again
