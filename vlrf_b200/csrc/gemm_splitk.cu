@@ -470,7 +470,9 @@ size_t sp_smem(int bm, int bn, bool ln, int stages, int kb_cap, int M, int split
 // give half as many CTAs again as 128-row tiles.
 SpPlan sp_plan(int M, int N, int K, int bn, bool ln) {
     const int n_kb = (K + SP_BK - 1) / SP_BK;
-    const int target = sp_sm_count();
+    // (large matrices: a third more CTAs, i.e. fewer k blocks and MMA issues a CTA, measured to pay from about
+    // 12 MB of weights on)
+    const int target = (long long)N * K * 2 >= (12ll << 20) ? sp_sm_count() * 4 / 3 : sp_sm_count();
     const int max_splits = SP_MAX_SPLITS;
     const size_t limit = SP_SMEM_LIMIT;
     SpPlan best{};
