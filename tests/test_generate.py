@@ -48,6 +48,7 @@ def test_stop_token_context_end_and_more_requests_than_slots(model_dirs, plain_m
     prompts = [random_ids(512, n, 80 + n) for n in (3, 30, 120, 7, 64)]
     free_run = model.generate_ids(prompts, SamplingParams(max_new_tokens=20, do_sample=False, stop_token_ids=()))
     assert free_run[2].finish_reason == "context" and len(free_run[2].token_ids) == 128
+    model.engine.check_device_errors()        # the ended row, now padding, must not look like a bad position
     stop = free_run[0].new_tokens[4]
     res = model.generate_ids(prompts, SamplingParams(max_new_tokens=20, do_sample=False, stop_token_ids=(stop,)))
     first = free_run[0].new_tokens.index(stop)

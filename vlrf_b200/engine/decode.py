@@ -115,6 +115,8 @@ class DecodeSession:
         """The sequence of this row has ended; its row becomes padding.  (The slot is the caller's to free.)"""
         self.live[row] = False
         self.tok_slot[row] = -1
+        self.tok_pos[row] = 0            # a padding row must not look like a position beyond the table
+        self.tokens[row] = 0
 
     def reserve_ahead(self, n_steps: int) -> None:
         """Make sure every live sequence has blocks for its next n_steps tokens, so that the replayed
