@@ -208,3 +208,39 @@ def test_launch_chaining_changes_no_bit(wide_model):
     assert len(chained) == len(plain_order)
     for a, b in zip(chained, plain_order):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+def test_decoding_to_the_last_position_at_xl_width(tmp_path, dtype, tol):
+    """A prompt step, then a replayed decode session up to the model's last position, with a shorter sequence
+    that ends on the way and stays in the batch as padding."""
+    from vlrf_b200.engine import Engine, StepEntry, load_model
+    from vlrf_b200.engine.decode import DecodeSession
+    from vlrf_b200.weights import write_random_model
+    d = write_random_model(GPT2_XL_WIDE, 77, tmp_path / "xl_wide")
+    cfg, w = plain.read_model_dir(d)
+    last = GPT2_XL_WIDE["n_positions"]
+    reqs = [random_ids(1003, last, 500), random_ids(1003, 300, 501)]
+    truth = [plain.logits_all_positions(cfg, w, ids) for ids in reqs]
+    eng = Engine(load_model(d, dtype), max_tokens=2 * last)
+    poison(eng)
+    slots = [eng.start_sequence() for _ in reqs]
+    pos = [400, 250]
+    got = eng.step([StepEntry(s, r[:n], [n - 1]) for s, r, n in zip(slots, reqs, pos)]).float().cpu()
+    for i, n in enumerate(pos):
+        assert rel_err(got[i], truth[i][n - 1]) < tol
+    sess = DecodeSession(eng, slots, use_graph=True)
+    sess.reserve_ahead(last)
+    while any(p < len(r) for p, r in zip(pos, reqs)):
+        sess.set_tokens([r[min(p, len(r) - 1)] for r, p in zip(reqs, pos)])
+        lg = sess.step().float().cpu()
+        for i, r in enumerate(reqs):
+            if pos[i] < len(r):
+                assert rel_err(lg[i], truth[i][pos[i]]) < tol, (i, pos[i])
+                pos[i] += 1
+                if pos[i] == len(r):
+                    sess.end_row(i)
+    eng.check_device_errors()
+    for s in slots:
+        eng.end_sequence(s)
+    assert eng.cache.slots.n_held == 0
