@@ -191,6 +191,67 @@ __global__ void __launch_bounds__(256) layernorm_warp_kernel(const float* __rest
     }
 }
 
+// One warp per row of at most NV·128 values.  The norm's weight and bias do not depend on the kernel ahead:
+// the CTA copies them to shared memory before the wait on it.  The row is read once and stays in registers.
+template <typename OT, int NV>
+__global__ void __launch_bounds__(256) layernorm_warp_small_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                                                                    const float* __restrict__ gamma,
+                                                                    const float* __restrict__ beta, OT* __restrict__ out,
+                                                                    int n_rows, int d, float eps) {
+    __shared__ float4 s_gamma[NV * 32], s_beta[NV * 32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.x * 8 + warp;
+    const int nv = d >> 2;
+    for (int i = threadIdx.x; i < nv; i += 256) {
+        s_gamma[i] = reinterpret_cast<const float4*>(gamma)[i];
+        s_beta[i] = reinterpret_cast<const float4*>(beta)[i];
+    }
+    __syncthreads();
+    pdl_wait();
+    pdl_launch_dependents();
+    if (r >= n_rows) return;
+    const float* src = x + (size_t)(rows ? rows[r] : r) * d;
+    float4 v[NV];
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int i = j * 32 + lane;
+        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < nv)      // an explicit load: the values stay in registers for all three passes
+            asm volatile("ld.global.v4.f32 {%0, %1, %2, %3}, [%4];"
+                         : "=f"(v[j].x), "=f"(v[j].y), "=f"(v[j].z), "=f"(v[j].w) : "l"(src + 4 * i));
+        s += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+    }
+    const float mean = warp_sum(s) / (float)d;
+    float q = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+        if (j * 32 + lane < nv) {
+            const float a = v[j].x - mean, b = v[j].y - mean, c = v[j].z - mean, e = v[j].w - mean;
+            q += (a * a + b * b) + (c * c + e * e);
+        }
+    const float inv = 1.f / sqrtf(warp_sum(q) / (float)d + eps);
+    OT* dst = out + (size_t)r * d;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int i = j * 32 + lane;
+        if (i < nv) {
+            const float4 gm = s_gamma[i], bt = s_beta[i];
+            const float y0 = (v[j].x - mean) * inv * gm.x + bt.x, y1 = (v[j].y - mean) * inv * gm.y + bt.y;
+            const float y2 = (v[j].z - mean) * inv * gm.z + bt.z, y3 = (v[j].w - mean) * inv * gm.w + bt.w;
+            if (sizeof(OT) == 4) {
+                reinterpret_cast<float4*>(dst)[i] = make_float4(y0, y1, y2, y3);
+            } else {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(y0, y1), hi = __floats2bfloat162_rn(y2, y3);
+                uint2 pk;
+                pk.x = *reinterpret_cast<uint32_t*>(&lo);
+                pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                reinterpret_cast<uint2*>(dst)[i] = pk;
+            }
+        }
+    }
+}
+
 extern "C" int vlrf_layernorm(const float* x, const int* rows, const float* gamma, const float* beta,
                               void* out, int out_dtype, int n_rows, int d, float eps,
                               cudaStream_t stream) {
@@ -200,7 +261,17 @@ extern "C" int vlrf_layernorm(const float* x, const int* rows, const float* gamm
     if (n_rows == 0) return VLRF_OK;
     if (d % 4 == 0 && n_rows >= 8) {
         const dim3 grid((n_rows + 7) / 8);
-        if (out_dtype == VLRF_F32)
+        if (d <= 1024 && out_dtype == VLRF_F32)
+            launch_chained(layernorm_warp_small_kernel<float, 8>, grid, dim3(256), 0, stream, x, rows, gamma, beta, (float*)out, n_rows, d, eps);
+        else if (d <= 1024 && out_dtype == VLRF_BF16)
+            launch_chained(layernorm_warp_small_kernel<__nv_bfloat16, 8>, grid, dim3(256), 0, stream, x, rows, gamma, beta,
+                           (__nv_bfloat16*)out, n_rows, d, eps);
+        else if (d <= 2048 && out_dtype == VLRF_F32)
+            launch_chained(layernorm_warp_small_kernel<float, 16>, grid, dim3(256), 0, stream, x, rows, gamma, beta, (float*)out, n_rows, d, eps);
+        else if (d <= 2048 && out_dtype == VLRF_BF16)
+            launch_chained(layernorm_warp_small_kernel<__nv_bfloat16, 16>, grid, dim3(256), 0, stream, x, rows, gamma, beta,
+                           (__nv_bfloat16*)out, n_rows, d, eps);
+        else if (out_dtype == VLRF_F32)
             launch_chained(layernorm_warp_kernel<float>, grid, dim3(256), 0, stream, x, rows, gamma, beta, (float*)out, n_rows, d, eps);
         else if (out_dtype == VLRF_BF16)
             launch_chained(layernorm_warp_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, x, rows, gamma, beta,
