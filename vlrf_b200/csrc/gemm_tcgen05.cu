@@ -97,6 +97,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    // The weights do not depend on the kernel ahead: the first tile's weight operand (the 128-row one when the
+    // roles are exchanged, else the BN-row one) is requested for as many k blocks as the ring holds before the
+    // wait; the rows of X follow after it.
+    const int early = (int)blockIdx.x < n_tiles ? min(STAGES, n_kb) : 0;
+    if (warp == 8 && lane == 0) {
+        const int tile = blockIdx.x;
+        const int m0 = SWAP ? tile * TC_BM : (tile / tiles_n) * TC_BM, n0 = SWAP ? 0 : (tile % tiles_n) * BN;
+        for (int kb = 0; kb < early; ++kb) {
+            tbar_expect_tx(&full[kb], A_BYTES + B_BYTES);
+            if (SWAP) tma_load_2d(a_tiles + (size_t)kb * A_BYTES, &tmap_x, kb * TC_BK, m0, &full[kb]);
+            else tma_load_2d(b_tiles + (size_t)kb * B_BYTES, &tmap_w, kb * TC_BK, n0, &full[kb]);
+        }
+    }
     pdl_launch_dependents();
     pdl_wait();                                    // X (and the residual) come from the kernel before
 
@@ -108,6 +121,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 for (int kb = 0; kb < n_kb; ++kb, ++kc) {
                     const int s = kc % STAGES;
                     const uint32_t use = kc / STAGES;
+                    if ((int)kc < early) {         // the weight half of this stage is already on its way
+                        if (SWAP) tma_load_2d(b_tiles + (size_t)s * B_BYTES, &tmap_w, kb * TC_BK, n0, &full[s]);
+                        else tma_load_2d(a_tiles + (size_t)s * A_BYTES, &tmap_x, kb * TC_BK, m0, &full[s]);
+                        continue;
+                    }
                     if (use >= 1 && !tbar_wait_or_abort(&empty[s], (use - 1) & 1, s_abort)) { atomicExch(s_abort, 1); break; }
                     tbar_expect_tx(&full[s], A_BYTES + B_BYTES);
                     tma_load_2d(a_tiles + (size_t)s * A_BYTES, &tmap_x, kb * TC_BK, m0, &full[s]);
