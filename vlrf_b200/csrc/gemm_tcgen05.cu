@@ -64,7 +64,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     extern __shared__ unsigned char tc_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
-    constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;     // two accumulators; allocation is a power of two ≥ 32
+    // two accumulators, ACC_STRIDE columns apart; the allocation is a power of two ≥ 32
+    constexpr int ACC_STRIDE = BN <= 16 ? 16 : (BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256)));
+    constexpr int TMEM_COLS = 2 * ACC_STRIDE < 32 ? 32 : 2 * ACC_STRIDE;
     unsigned char* a_tiles = smem;                                   // [STAGES][128][128 B]
     unsigned char* b_tiles = smem + (size_t)STAGES * A_BYTES;        // [STAGES][BN][128 B]
     uint64_t* full = reinterpret_cast<uint64_t*>(b_tiles + (size_t)STAGES * B_BYTES);
@@ -141,7 +143,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 const uint32_t b = tc & 1, use = tc >> 1;
                 if (use >= 1 && !tbar_wait_or_abort(&acc_empty[b], (use - 1) & 1, s_abort)) { atomicExch(s_abort, 1); break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t tmem_d = tmem_base + b * BN;
+                const uint32_t tmem_d = tmem_base + b * ACC_STRIDE;
                 bool ok = true;
                 for (int kb = 0; kb < n_kb; ++kb, ++kc) {
                     const int s = kc % STAGES;
@@ -167,7 +169,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             const int m0 = SWAP ? tile * TC_BM : (tile / tiles_n) * TC_BM, n0 = SWAP ? 0 : (tile % tiles_n) * BN;
             if (*(volatile int*)s_abort || !tbar_wait_or_abort(&acc_full[b], (tc >> 1) & 1, s_abort)) { atomicExch(s_abort, 1); break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t tmem_d = tmem_base + b * BN + ((uint32_t)(q * 32) << 16);
+            const uint32_t tmem_d = tmem_base + b * ACC_STRIDE + ((uint32_t)(q * 32) << 16);
             if (SWAP) {
                 const int n = m0 + q * 32 + lane;             // this thread's output column = row of W
                 const float bv = (bias && n < N) ? bias[n] : 0.f;
@@ -213,9 +215,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     if (kv_blk < 0) atomicOr(dev_err, VLRF_DEVERR_NO_BLOCK);
                 }
             }
-            constexpr int HALF_COLS = BN / 2;
+            // the two warps of a lane group share the columns in runs of 32: half and half, or 64 + 32 of 96
+            constexpr int SPLIT_AT = BN % 64 == 0 ? BN / 2 : 64;
+            const int c_begin = half ? SPLIT_AT : 0, c_end = half ? BN : SPLIT_AT;
 #pragma unroll 1
-            for (int c0 = half * HALF_COLS; c0 < (half + 1) * HALF_COLS; c0 += 32) {
+            for (int c0 = c_begin; c0 < c_end; c0 += 32) {
                 uint32_t r[32];
                 tmem_ld32(tmem_d + (uint32_t)c0, r);          // in flight while the bias and the residual are fetched
                 const bool live = m < M && n0 + c0 < N;
@@ -241,7 +245,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     }
                 }
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (c0 + 32 >= (half + 1) * HALF_COLS) {      // this warp's last columns are in registers
+                if (c0 + 32 >= c_end) {                       // this warp's last columns are in registers
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) tbar_arrive(&acc_empty[b]);
@@ -378,12 +382,13 @@ extern "C" int vlrf_gemm_tcgen05(const void* X, const void* W, const float* bias
     {
         const int sms = sm_count_cached();
         long long best = -1;
-        const int widths[3] = {256, 128, 64};
-        for (int i = 0; i < 3; ++i) {
+        const int widths[4] = {256, 128, 96, 64};
+        for (int i = 0; i < 4; ++i) {
             const int bn = widths[i];
             if (bn > 64 && N <= bn / 2) continue;
             const long long tiles = (long long)((N + bn - 1) / bn) * ((M + 127) / 128);
             const long long rounds = (tiles + sms - 1) / sms;
+            if (bn == 96 && rounds > 1) continue;      // the odd width only where it puts every tile on an SM of its own
             const long long cost = rounds * (bn + 32);
             if (best < 0 || cost < best) { best = cost; best_bn = bn; }
         }
@@ -393,6 +398,7 @@ extern "C" int vlrf_gemm_tcgen05(const void* X, const void* W, const float* bias
     VLRF_REQUIRE(out_dtype == VLRF_BF16 || out_dtype == VLRF_F32, "gemm_tcgen05: unknown output dtype %d", out_dtype);
     if (best_bn == 256) return TILED(256, 4);
     if (best_bn == 128) return TILED(128, 6);
+    if (best_bn == 96) return TILED(96, 7);
     return TILED(64, 8);
 #undef TILED
 }
