@@ -244,3 +244,33 @@ def test_decoding_to_the_last_position_at_xl_width(tmp_path, dtype, tol):
     for s in slots:
         eng.end_sequence(s)
     assert eng.cache.slots.n_held == 0
+
+
+def test_prompt_attention_dealt_to_parts_inside_the_engine(tmp_path, monkeypatch):
+    """Long query tiles whose keys are dealt to several CTAs (forced here; the choice is by size otherwise):
+    the mixer hands the scratch, the step is run three times so that it is captured and replayed, and every
+    run gives the plain implementation's logits and the same bits."""
+    from vlrf_b200.csrc import ops
+    from vlrf_b200.engine import Engine, StepEntry, load_model
+    from vlrf_b200.weights import write_random_model
+    d = write_random_model(GPT2_XL_WIDE, 78, tmp_path / "xl_wide")
+    cfg, w = plain.read_model_dir(d)
+    reqs = [random_ids(1003, 512, 510), random_ids(1003, 300, 511)]
+    rows = [[0, 127, 128, 400, 511], [5, 255, 299]]
+    truth = [plain.logits_all_positions(cfg, w, ids) for ids in reqs]
+    monkeypatch.setattr(ops, "PREFILL_ATTENTION_PARTS", 2)
+    eng = Engine(load_model(d, "bfloat16"), max_tokens=1024)
+    poison(eng)
+    runs = []
+    for _ in range(3):
+        slots = [eng.start_sequence() for _ in reqs]
+        runs.append(eng.step([StepEntry(s, r, want) for s, r, want in zip(slots, reqs, rows)]).float().cpu().clone())
+        for s in slots:
+            eng.end_sequence(s)
+    eng.check_device_errors()
+    at = 0
+    for i, want in enumerate(rows):
+        for r in want:
+            assert rel_err(runs[0][at], truth[i][r]) < TOL_BF16, (i, r)
+            at += 1
+    assert torch.equal(runs[0], runs[1]) and torch.equal(runs[0], runs[2])

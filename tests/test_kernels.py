@@ -443,18 +443,22 @@ PREFILL_CASES = [  # H, Hkv, dh, [(tokens already cached, new tokens)], window
     (2, 2, 128, [(5, 140)], 64),
     # long rows: many key blocks per query tile, tiles of unequal length, a continuation across block pairs
     (3, 3, 64, [(0, 1024), (0, 700)], 0), (2, 2, 64, [(0, 600), (300, 500)], 200), (2, 1, 64, [(127, 130), (129, 1), (63, 66)], 0),
+    (2, 2, 64, [(900, 300), (0, 513)], 0), (1, 1, 64, [(0, 800)], 520),
 ]
 
 
-@pytest.mark.parametrize("kernel", ["tcgen05", "mma_sync"])
+@pytest.mark.parametrize("kernel", ["tcgen05", "tcgen05_parts2", "tcgen05_parts3", "mma_sync"])
 @pytest.mark.parametrize("H,Hkv,dh,seqs,window", PREFILL_CASES)
 def test_attention_prefill_tensor_cores(monkeypatch, kernel, H, Hkv, dh, seqs, window):
     """Ragged batches with unequal lengths and continuations, grouped heads, a window; the cache is NaN
-    outside what the sequences hold, and freed-looking rows inside their last blocks are NaN too."""
+    outside what the sequences hold, and freed-looking rows inside their last blocks are NaN too.  With
+    parts, long tiles' keys are dealt to several CTAs that meet in scratch: it starts as NaN, is used twice,
+    and both runs give the same bits whichever CTA came last."""
     from vlrf_b200.csrc import ops
-    if kernel == "tcgen05" and dh != 64:
+    if kernel.startswith("tcgen05") and dh != 64:
         pytest.skip("the tcgen05 kernel takes head size 64")
-    monkeypatch.setattr(ops, "PREFILL_ATTENTION_TCGEN05", kernel == "tcgen05")
+    monkeypatch.setattr(ops, "PREFILL_ATTENTION_TCGEN05", kernel.startswith("tcgen05"))
+    n_parts = int(kernel[-1]) if "parts" in kernel else 1
     dtype = torch.bfloat16
     scale = 0.8 / math.sqrt(dh)
     n_blocks = sum((p + n + 63) // 64 for p, n in seqs) + 2
@@ -488,10 +492,22 @@ def test_attention_prefill_tensor_cores(monkeypatch, kernel, H, Hkv, dh, seqs, w
     e = err_word()
     i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)  # noqa: E731
     assert ops.attention_prefill_takes(dtype, dh, 64, W, 0)
-    ops.attention_prefill(qkv.to(DEV), 0, kc.to(DEV), vc.to(DEV), table.to(DEV), i32(list(range(1, len(seqs) + 1))),
-                          i32(starts), i32([p for p, _ in seqs]), out, T, len(seqs), max(n for _, n in seqs), H, Hkv, dh,
-                          scale, window, e)
+    max_new = max(n for _, n in seqs)
+    partials = counters = None
+    if n_parts > 1:
+        n_floats, n_counters = ops.attention_prefill_scratch(len(seqs), max_new, H, n_parts)
+        partials = torch.full((n_floats,), float("nan"), device=DEV)
+        counters = torch.zeros(n_counters, dtype=torch.int32, device=DEV)
+    args = (qkv.to(DEV), 0, kc.to(DEV), vc.to(DEV), table.to(DEV), i32(list(range(1, len(seqs) + 1))), i32(starts),
+            i32([p for p, _ in seqs]))
+    ops.attention_prefill(*args, out, T, len(seqs), max_new, H, Hkv, dh, scale, window, e, n_parts, partials, counters)
     assert int(e.item()) == 0
+    if n_parts > 1:
+        assert int(counters.abs().sum()) == 0
+        again = torch.full_like(out, float("nan"))
+        ops.attention_prefill(*args, again, T, len(seqs), max_new, H, Hkv, dh, scale, window, e, n_parts, partials, counters)
+        assert int(e.item()) == 0 and int(counters.abs().sum()) == 0
+        assert torch.equal(again.view(torch.int16), out.view(torch.int16))
     got = out.float().cpu()
     assert torch.isfinite(got).all()
     for i, (p0, n) in enumerate(seqs):

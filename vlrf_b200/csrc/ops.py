@@ -105,6 +105,7 @@ def linear(x, w, bias, out, *, act=None, residual=None, rows: int | None = None,
 _SM_COUNT = None
 USE_TCGEN05 = True
 PREFILL_ATTENTION_TCGEN05 = True     # head size 64; off: the mma.sync kernel takes those too
+PREFILL_ATTENTION_PARTS = None       # a number here overrides attention_prefill_parts (for measurements)
 SKINNY_MAX_ROWS = 64
 FUSED_NORM_MAX_ROWS = 16
 SWAPPED_MIN_COLUMNS = 16384
@@ -433,12 +434,43 @@ def attention_prefill_takes(dtype: torch.dtype, head_dim: int, block_tokens: int
     return bool(library().vlrf_attn_prefill_takes(head_dim, block_tokens, row_width, q_off))
 
 
+def attention_prefill_parts(dtype: torch.dtype, n_seqs: int, max_new: int, n_heads: int, head_dim: int, block_tokens: int,
+                            row_width: int, q_off: int) -> int:
+    """Into how many parts `attention_prefill` best deals the keys of a long tile of queries (1: not at all;
+    more want scratch, see there).  A tile's key blocks are a chain, so a step with few tiles is bound by its
+    longest one (`tiles` blocks, for sequences that start at 0), not by the SMs: all blocks together, spread
+    over the two CTAs that an SM holds, come to `even` blocks each, and parts pay when the chain is the longer
+    of the two."""
+    from . import library
+    lib = library()
+    if not PREFILL_ATTENTION_TCGEN05 or dtype != torch.bfloat16 \
+            or not lib.vlrf_attn_prefill_tc_takes(head_dim, block_tokens, row_width, q_off, n_heads * head_dim):
+        return 1
+    tiles = -(-max_new // lib.vlrf_attn_prefill_tc_tile())
+    even = tiles * (tiles + 1) / 2 * n_heads * n_seqs / (2 * sm_count())
+    parts = int(tiles / (1.3 * max(even, lib.vlrf_attn_prefill_tc_min_part_blocks())) + 0.5)   # 1.3: a part's own cost
+    if PREFILL_ATTENTION_PARTS is not None:
+        parts = PREFILL_ATTENTION_PARTS
+    return max(1, min(parts, lib.vlrf_attn_prefill_tc_max_parts()))
+
+
+def attention_prefill_scratch(n_seqs: int, max_new: int, n_heads: int, n_parts: int) -> tuple[int, int]:
+    """(float32 elements of `partials`, int32 elements of `counters`) that `attention_prefill` wants for
+    n_parts > 1."""
+    from . import library
+    lib = library()
+    tiles = -(-max_new // lib.vlrf_attn_prefill_tc_tile()) * n_seqs * n_heads
+    return tiles * n_parts * lib.vlrf_attn_prefill_tc_part_floats(), tiles
+
+
 def attention_prefill(qkv, q_off: int, k_cache, v_cache, block_table, seq_slot, seq_start, seq_pos0, out,
                       n_tokens: int, n_seqs: int, max_new: int, n_heads: int, n_kv_heads: int, head_dim: int,
-                      scale: float, window: int, dev_err) -> None:
+                      scale: float, window: int, dev_err, n_parts: int = 1, partials=None, counters=None) -> None:
     """Causal attention of every sequence's new tokens (rows seq_start[i] … seq_start[i+1]−1 of qkv, the
     first of them at position seq_pos0[i]) over the sequence's cache, which already holds these tokens'
-    keys and values.  bfloat16, head size 64 or 128."""
+    keys and values.  bfloat16, head size 64 or 128.  n_parts > 1 (see attention_prefill_parts) deals the keys
+    of long tiles to several CTAs and wants float32 `partials` and zeroed int32 `counters` of the sizes that
+    attention_prefill_scratch gives; the counters are left zero."""
     _dev(qkv, "qkv", torch.bfloat16); _dev(k_cache, "k_cache", torch.bfloat16); _dev(v_cache, "v_cache", torch.bfloat16)
     _dev(out, "out", torch.bfloat16); _dev(block_table, "block_table", torch.int32)
     _dev(seq_slot, "seq_slot", torch.int32); _dev(seq_start, "seq_start", torch.int32)
@@ -454,9 +486,15 @@ def attention_prefill(qkv, q_off: int, k_cache, v_cache, block_table, seq_slot, 
     from . import library
     if PREFILL_ATTENTION_TCGEN05 and library().vlrf_attn_prefill_tc_takes(head_dim, bt, qkv.shape[1], q_off, out.shape[1]):
         # head size 64: S and O on the tcgen05 tensor cores, accumulators in tensor memory
+        if n_parts > 1:
+            _dev(partials, "partials", torch.float32); _dev(counters, "counters", torch.int32)
+            want = attention_prefill_scratch(n_seqs, max_new, n_heads, n_parts)
+            if partials.numel() < want[0] or counters.numel() < want[1]:
+                raise KernelError("attention_prefill: scratch is too small for %d parts" % n_parts)
         call("vlrf_attn_prefill_tc", _ptr(qkv), qkv.shape[1], q_off, _ptr(k_cache), _ptr(v_cache), nb, _ptr(block_table),
              block_table.shape[1], _ptr(seq_slot), _ptr(seq_start), _ptr(seq_pos0), _ptr(out), out.shape[1], n_tokens,
-             n_seqs, max_new, n_heads, n_kv_heads, head_dim, bt, float(scale), int(window), _ptr(dev_err), _stream())
+             n_seqs, max_new, n_heads, n_kv_heads, head_dim, bt, float(scale), int(window), int(n_parts),
+             _ptr(partials) if n_parts > 1 else 0, _ptr(counters) if n_parts > 1 else 0, _ptr(dev_err), _stream())
         return
     call("vlrf_attn_prefill", _ptr(qkv), qkv.shape[1], q_off, _ptr(k_cache), _ptr(v_cache), nb, _ptr(block_table),
          block_table.shape[1], _ptr(seq_slot), _ptr(seq_start), _ptr(seq_pos0), _ptr(out), out.shape[1], n_tokens, n_seqs,

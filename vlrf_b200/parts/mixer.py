@@ -104,9 +104,16 @@ class CausalSelfAttention:
             return
         if ops.attention_prefill_takes(qkv.dtype, self.head_dim, view.k.shape[2], qkv.shape[1], self.q_off):
             # a prompt step in bfloat16: tiles of 64 queries on the tensor cores
+            n_parts = ops.attention_prefill_parts(qkv.dtype, ctx.n_seqs, ctx.max_new, self.n_heads, self.head_dim,
+                                                  view.k.shape[2], qkv.shape[1], self.q_off)
+            partials = counters = None
+            if n_parts > 1:
+                n_floats, n_counters = ops.attention_prefill_scratch(ctx.n_seqs, ctx.max_new, self.n_heads, n_parts)
+                partials = ctx.ws.get("attn_partials", n_floats, 1, torch.float32)
+                counters = ctx.ws.get_zeroed("attn_counters", n_counters, torch.int32)
             ops.attention_prefill(qkv, self.q_off, view.k, view.v, view.block_table, ctx.seq_slot, ctx.seq_start,
                                   ctx.seq_pos0, merged, T, ctx.n_seqs, ctx.max_new, self.n_heads, self.n_kv_heads,
-                                  self.head_dim, self.scale, self.window, ctx.dev_err)
+                                  self.head_dim, self.scale, self.window, ctx.dev_err, n_parts, partials, counters)
             return
         ops.attention_generic(qkv, self.q_off, view.k, view.v, view.block_table, ctx.tok_slot, ctx.tok_pos,
                               merged, T, self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
