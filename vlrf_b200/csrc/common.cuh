@@ -163,6 +163,23 @@ template <typename OT> __device__ __forceinline__ float apply_act_out(float x, i
     if (act == VLRF_ACT_GELU_ERF) return gelu_erf_f(x);
     return x;
 }
+// 32 bytes a thread in one instruction (sm_100): a thread that writes its own row piece by piece fills a whole
+// 32-byte sector at a time this way; with 16-byte pieces every sector goes to L2 twice, half full
+__device__ __forceinline__ void st_global_32B(void* p, const uint32_t (&w)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+                 "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+}
+__device__ __forceinline__ void ld_global_32B(const void* p, float (&v)[8]) {
+    asm volatile("ld.global.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];" : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]),
+                 "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]) : "l"(p) : "memory");
+}
+// the same with the activation known at compile time (a run-time `act` per element costs issue slots: the
+// branches become predicates, and the paths not taken are still issued)
+template <typename OT, int ACT> __device__ __forceinline__ float apply_act_const(float x) {
+    if (ACT == VLRF_ACT_GELU_TANH) return sizeof(OT) == 2 ? gelu_tanh_fast(x) : gelu_tanh_f(x);
+    if (ACT == VLRF_ACT_GELU_ERF) return gelu_erf_f(x);
+    return x;
+}
 __device__ __forceinline__ float apply_act_rt(float x, int act) {
     if (act == VLRF_ACT_GELU_TANH) return gelu_tanh_f(x);
     if (act == VLRF_ACT_GELU_ERF) return gelu_erf_f(x);

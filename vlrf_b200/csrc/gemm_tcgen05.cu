@@ -19,6 +19,7 @@
 // frees its tensor memory and returns.
 //
 // The product is the reference's linear(x, W) = x · Wᵀ (include/model/compute.hpp:64-68).
+#include <type_traits>
 #include "common.cuh"
 #include "tma.cuh"
 #include "tcgen05.cuh"
@@ -186,15 +187,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                             : "r"(tmem_d + (uint32_t)c0));
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                         if (n < N) {
+                            auto rows = [&](auto act_c) {                 // the activation as a compile-time constant
+                                constexpr int ACT = decltype(act_c)::value;
 #pragma unroll
-                            for (int j = 0; j < 16; ++j) {
-                                const int m = c0 + j;
-                                if (m < M) {
-                                    float x = apply_act_out<OT>(__uint_as_float(r[j]) + bv, act);
-                                    if (residual) x += residual[(size_t)m * ldy + n];
-                                    ElemIO<OT>::store(Y + (size_t)m * ldy + n, x);
+                                for (int j = 0; j < 16; ++j) {
+                                    const int m = c0 + j;
+                                    if (m < M) {
+                                        float x = apply_act_const<OT, ACT>(__uint_as_float(r[j]) + bv);
+                                        if (residual) x += residual[(size_t)m * ldy + n];
+                                        ElemIO<OT>::store(Y + (size_t)m * ldy + n, x);
+                                    }
                                 }
-                            }
+                            };
+                            if (act == VLRF_ACT_NONE) rows(std::integral_constant<int, VLRF_ACT_NONE>{});
+                            else if (act == VLRF_ACT_GELU_TANH) rows(std::integral_constant<int, VLRF_ACT_GELU_TANH>{});
+                            else rows(std::integral_constant<int, VLRF_ACT_GELU_ERF>{});
                         }
                     }
                 }
@@ -218,6 +225,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             // the two warps of a lane group share the columns in runs of 32: half and half, or 64 + 32 of 96
             constexpr int SPLIT_AT = BN % 64 == 0 ? BN / 2 : 64;
             const int c_begin = half ? SPLIT_AT : 0, c_end = half ? BN : SPLIT_AT;
+            // whether rows of Y, and heads in the cache, lie so that 32-byte stores are aligned
+            const bool wide = (reinterpret_cast<uintptr_t>(Y) & 31) == 0 && (ldy % (32 / (int)sizeof(OT))) == 0;
+            const bool kv_wide = kv.Kc != nullptr && kv.dh % 16 == 0 && kv.k_off % 16 == 0 && kv.v_off % 16 == 0 &&
+                                 ((reinterpret_cast<uintptr_t>(kv.Kc) | reinterpret_cast<uintptr_t>(kv.Vc)) & 31) == 0;
 #pragma unroll 1
             for (int c0 = c_begin; c0 < c_end; c0 += 32) {
                 uint32_t r[32];
@@ -239,9 +250,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                             bq[i] = make_float4(bias[n0 + c0 + 4 * i], bias[n0 + c0 + 4 * i + 1], bias[n0 + c0 + 4 * i + 2], bias[n0 + c0 + 4 * i + 3]);
                     }
                     if (residual) {
-                        const float4* rr = reinterpret_cast<const float4*>(residual + (size_t)m * ldy + n0 + c0);
+                        const float* rr = residual + (size_t)m * ldy + n0 + c0;
+                        if ((reinterpret_cast<uintptr_t>(residual) & 31) == 0 && ldy % 8 == 0) {
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) rq[i] = rr[i];
+                            for (int i = 0; i < 8; i += 2) {
+                                float v8[8];
+                                ld_global_32B(rr + 4 * i, v8);
+                                rq[i] = make_float4(v8[0], v8[1], v8[2], v8[3]);
+                                rq[i + 1] = make_float4(v8[4], v8[5], v8[6], v8[7]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) rq[i] = reinterpret_cast<const float4*>(rr)[i];
+                        }
                     }
                 }
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -252,37 +273,66 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 }
                 if (!live) continue;
                 if (fast) {
+                    // 16 columns at a time: 32 bytes of bfloat16 (one store where rows and heads are aligned for it),
+                    // or twice 32 bytes of float32; the activation is a compile-time constant inside
+                    auto fast_body = [&](auto act_c) {
+                        constexpr int ACT = decltype(act_c)::value;
 #pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
-                        const float4 b0 = bq[j / 4], b1 = bq[j / 4 + 1], r0 = rq[j / 4], r1 = rq[j / 4 + 1];
-                        float v[8];
-                        v[0] = apply_act_out<OT>(__uint_as_float(r[j + 0]) + b0.x, act) + r0.x;
-                        v[1] = apply_act_out<OT>(__uint_as_float(r[j + 1]) + b0.y, act) + r0.y;
-                        v[2] = apply_act_out<OT>(__uint_as_float(r[j + 2]) + b0.z, act) + r0.z;
-                        v[3] = apply_act_out<OT>(__uint_as_float(r[j + 3]) + b0.w, act) + r0.w;
-                        v[4] = apply_act_out<OT>(__uint_as_float(r[j + 4]) + b1.x, act) + r1.x;
-                        v[5] = apply_act_out<OT>(__uint_as_float(r[j + 5]) + b1.y, act) + r1.y;
-                        v[6] = apply_act_out<OT>(__uint_as_float(r[j + 6]) + b1.z, act) + r1.z;
-                        v[7] = apply_act_out<OT>(__uint_as_float(r[j + 7]) + b1.w, act) + r1.w;
-                        if (sizeof(OT) == 4) {
-                            *reinterpret_cast<float4*>(reinterpret_cast<float*>(yrow) + j) = make_float4(v[0], v[1], v[2], v[3]);
-                            *reinterpret_cast<float4*>(reinterpret_cast<float*>(yrow) + j + 4) = make_float4(v[4], v[5], v[6], v[7]);
-                        } else {
-                            uint4 pk;
-                            pk.x = pack2(v[0], v[1]); pk.y = pack2(v[2], v[3]); pk.z = pack2(v[4], v[5]); pk.w = pack2(v[6], v[7]);
-                            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(yrow) + j) = pk;
-                            const int n = n0 + c0 + j;                 // 8 columns: one head, one of q / k / v
-                            if (kv_blk >= 0 && n >= kv.k_off) {
-                                const bool is_v = n >= kv.v_off;
-                                const int col = n - (is_v ? kv.v_off : kv.k_off);
-                                if (col < kv.width) {
-                                    const int hh = col / kv.dh, cc = col - hh * kv.dh;
-                                    __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(is_v ? kv.Vc : kv.Kc);
-                                    *reinterpret_cast<uint4*>(base + (((size_t)kv_blk * kv.Hkv + hh) * kv.BT + kv_row) * kv.dh + cc) = pk;
+                        for (int j = 0; j < 32; j += 16) {
+                            float v[16];
+#pragma unroll
+                            for (int i = 0; i < 16; i += 4) {
+                                const float4 bb = bq[(j + i) / 4], rr = rq[(j + i) / 4];
+                                v[i + 0] = apply_act_const<OT, ACT>(__uint_as_float(r[j + i + 0]) + bb.x) + rr.x;
+                                v[i + 1] = apply_act_const<OT, ACT>(__uint_as_float(r[j + i + 1]) + bb.y) + rr.y;
+                                v[i + 2] = apply_act_const<OT, ACT>(__uint_as_float(r[j + i + 2]) + bb.z) + rr.z;
+                                v[i + 3] = apply_act_const<OT, ACT>(__uint_as_float(r[j + i + 3]) + bb.w) + rr.w;
+                            }
+                            if (sizeof(OT) == 4) {
+                                float* dst = reinterpret_cast<float*>(yrow) + j;
+                                if (wide) {
+                                    uint32_t w0[8], w1[8];
+#pragma unroll
+                                    for (int i = 0; i < 8; ++i) { w0[i] = __float_as_uint(v[i]); w1[i] = __float_as_uint(v[8 + i]); }
+                                    st_global_32B(dst, w0);
+                                    st_global_32B(dst + 8, w1);
+                                } else {
+#pragma unroll
+                                    for (int i = 0; i < 16; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                                }
+                            } else {
+                                uint32_t w[8];
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) w[i] = pack2(v[2 * i], v[2 * i + 1]);
+                                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(yrow) + j;
+                                if (wide) {
+                                    st_global_32B(dst, w);
+                                } else {
+                                    *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+                                    *reinterpret_cast<uint4*>(dst + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+                                }
+                                if (kv_blk >= 0) {
+#pragma unroll
+                                    for (int h8 = 0; h8 < 2; ++h8) {      // 8 columns are one head's, and one of q / k / v
+                                        if (kv_wide && h8 == 1) break;   // … and so are 16, which then went out in one piece
+                                        const int n = n0 + c0 + j + 8 * h8;
+                                        if (n < kv.k_off) continue;
+                                        const bool is_v = n >= kv.v_off;
+                                        const int col = n - (is_v ? kv.v_off : kv.k_off);
+                                        if (col >= kv.width) continue;
+                                        const int hh = col / kv.dh, cc = col - hh * kv.dh;
+                                        __nv_bfloat16* to = reinterpret_cast<__nv_bfloat16*>(is_v ? kv.Vc : kv.Kc) +
+                                                            (((size_t)kv_blk * kv.Hkv + hh) * kv.BT + kv_row) * kv.dh + cc;
+                                        if (kv_wide) st_global_32B(to, w);
+                                        else *reinterpret_cast<uint4*>(to) = h8 ? make_uint4(w[4], w[5], w[6], w[7]) : make_uint4(w[0], w[1], w[2], w[3]);
+                                    }
                                 }
                             }
                         }
-                    }
+                    };
+                    if (act == VLRF_ACT_NONE) fast_body(std::integral_constant<int, VLRF_ACT_NONE>{});
+                    else if (act == VLRF_ACT_GELU_TANH) fast_body(std::integral_constant<int, VLRF_ACT_GELU_TANH>{});
+                    else fast_body(std::integral_constant<int, VLRF_ACT_GELU_ERF>{});
                 } else {
                     const float* rrow = residual ? residual + (size_t)m * ldy + n0 + c0 : nullptr;
 #pragma unroll
