@@ -38,7 +38,12 @@ int sm_count_cached() {                          // asked once: the query is slo
 }
 
 constexpr int TC_BM = 128;
-constexpr int TC_BK = 64;
+constexpr int TC_BK = 64;           // elements of K in one 128-byte swizzle atom: what one TMA load and one descriptor cover
+// Atoms of K in a stage of the ring.  One thread issues the MMAs, and a stage costs it about 550 cycles whatever
+// the tile's width: some 63 for each of an atom's four MMAs, the rest for the wait, the commit and the loop.  The
+// tensor pipe needs 4 x 186 cycles for an atom of a 256-wide tile but only 4 x 70 of a 96-wide one, so narrow
+// tiles take two atoms a stage and pay the fixed part half as often.
+__host__ __device__ constexpr int tc_atoms(int bn) { return bn <= 128 ? 2 : 1; }
 constexpr int TC_THREADS = 320;      // warps 0-7: epilogue (two per 32 accumulator lanes), 8: producer, 9: MMA issue
 
 // Optional scatter of the K and V columns of a fused q/k/v projection into one layer's paged cache
@@ -64,12 +69,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     int act, TcKvScatter kv, int* __restrict__ dev_err) {
     extern __shared__ unsigned char tc_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_raw) + 1023) & ~(uintptr_t)1023);
-    constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
+    constexpr int KA = tc_atoms(BN);
+    constexpr int A_ATOM = TC_BM * TC_BK * 2, B_ATOM = BN * TC_BK * 2;           // bytes of one atom of each operand
+    constexpr int A_BYTES = KA * A_ATOM, B_BYTES = KA * B_ATOM;
     // two accumulators, ACC_STRIDE columns apart; the allocation is a power of two ≥ 32
     constexpr int ACC_STRIDE = BN <= 16 ? 16 : (BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256)));
     constexpr int TMEM_COLS = 2 * ACC_STRIDE < 32 ? 32 : 2 * ACC_STRIDE;
-    unsigned char* a_tiles = smem;                                   // [STAGES][128][128 B]
-    unsigned char* b_tiles = smem + (size_t)STAGES * A_BYTES;        // [STAGES][BN][128 B]
+    unsigned char* a_tiles = smem;                                   // [STAGES][KA][128][128 B]
+    unsigned char* b_tiles = smem + (size_t)STAGES * A_BYTES;        // [STAGES][KA][BN][128 B]
     uint64_t* full = reinterpret_cast<uint64_t*>(b_tiles + (size_t)STAGES * B_BYTES);
     uint64_t* empty = full + STAGES;
     uint64_t* acc_full = empty + STAGES;                             // [2] MMAs of a tile are complete
@@ -78,7 +85,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_kb = (K + TC_BK - 1) / TC_BK;
+    const int n_kb = (K + KA * TC_BK - 1) / (KA * TC_BK);             // stages of K (atoms behind K's end are read as zeros)
     // tiles: not swapped — 128 rows of X by BN rows of W, neighbours in N first (they share the rows of X in
     // L2); swapped — 128 rows of W by all rows of X
     const int tiles_n = SWAP ? 1 : (N + BN - 1) / BN;
@@ -109,8 +116,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         const int m0 = SWAP ? tile * TC_BM : (tile / tiles_n) * TC_BM, n0 = SWAP ? 0 : (tile % tiles_n) * BN;
         for (int kb = 0; kb < early; ++kb) {
             tbar_expect_tx(&full[kb], A_BYTES + B_BYTES);
-            if (SWAP) tma_load_2d(a_tiles + (size_t)kb * A_BYTES, &tmap_x, kb * TC_BK, m0, &full[kb]);
-            else tma_load_2d(b_tiles + (size_t)kb * B_BYTES, &tmap_w, kb * TC_BK, n0, &full[kb]);
+#pragma unroll
+            for (int a = 0; a < KA; ++a) {
+                if (SWAP) tma_load_2d(a_tiles + (size_t)kb * A_BYTES + a * A_ATOM, &tmap_x, (kb * KA + a) * TC_BK, m0, &full[kb]);
+                else tma_load_2d(b_tiles + (size_t)kb * B_BYTES + a * B_ATOM, &tmap_w, (kb * KA + a) * TC_BK, n0, &full[kb]);
+            }
         }
     }
     pdl_launch_dependents();
@@ -125,14 +135,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     const int s = kc % STAGES;
                     const uint32_t use = kc / STAGES;
                     if ((int)kc < early) {         // the weight half of this stage is already on its way
-                        if (SWAP) tma_load_2d(b_tiles + (size_t)s * B_BYTES, &tmap_w, kb * TC_BK, n0, &full[s]);
-                        else tma_load_2d(a_tiles + (size_t)s * A_BYTES, &tmap_x, kb * TC_BK, m0, &full[s]);
+#pragma unroll
+                        for (int a = 0; a < KA; ++a) {
+                            if (SWAP) tma_load_2d(b_tiles + (size_t)s * B_BYTES + a * B_ATOM, &tmap_w, (kb * KA + a) * TC_BK, n0, &full[s]);
+                            else tma_load_2d(a_tiles + (size_t)s * A_BYTES + a * A_ATOM, &tmap_x, (kb * KA + a) * TC_BK, m0, &full[s]);
+                        }
                         continue;
                     }
                     if (use >= 1 && !tbar_wait_or_abort(&empty[s], (use - 1) & 1, s_abort)) { atomicExch(s_abort, 1); break; }
                     tbar_expect_tx(&full[s], A_BYTES + B_BYTES);
-                    tma_load_2d(a_tiles + (size_t)s * A_BYTES, &tmap_x, kb * TC_BK, m0, &full[s]);
-                    tma_load_2d(b_tiles + (size_t)s * B_BYTES, &tmap_w, kb * TC_BK, n0, &full[s]);
+#pragma unroll
+                    for (int a = 0; a < KA; ++a) {
+                        tma_load_2d(a_tiles + (size_t)s * A_BYTES + a * A_ATOM, &tmap_x, (kb * KA + a) * TC_BK, m0, &full[s]);
+                        tma_load_2d(b_tiles + (size_t)s * B_BYTES + a * B_ATOM, &tmap_w, (kb * KA + a) * TC_BK, n0, &full[s]);
+                    }
                 }
             }
         }
@@ -153,8 +169,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                     const uint64_t da = umma_desc_k128(a_tiles + (size_t)s * A_BYTES);
                     const uint64_t db = umma_desc_k128(b_tiles + (size_t)s * B_BYTES);
 #pragma unroll
-                    for (int k = 0; k < TC_BK / 16; ++k)      // 16 elements = 32 bytes = 2 descriptor units along K
-                        umma_bf16(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    for (int a = 0; a < KA; ++a) {
+#pragma unroll
+                        for (int k = 0; k < TC_BK / 16; ++k)  // 16 elements = 32 bytes = 2 descriptor units along K
+                            umma_bf16(tmem_d, da + (uint64_t)(a * (A_ATOM >> 4) + 2 * k), db + (uint64_t)(a * (B_ATOM >> 4) + 2 * k), idesc,
+                                      (kb > 0 || a > 0 || k > 0) ? 1u : 0u);
+                    }
                     umma_commit(&empty[s]);                   // the stage is free once these MMAs have read it
                 }
                 if (!ok) break;
@@ -376,7 +396,7 @@ int launch_tc(const void* X, const void* W, const float* bias, const float* resi
     if (st != VLRF_OK) return st;
     st = SWAP ? vlrf_make_tmap_bf16(X, M, K, ldx, BN, TC_BK, &tw) : vlrf_make_tmap_bf16(W, N, K, K, BN, TC_BK, &tw);
     if (st != VLRF_OK) return st;
-    const size_t smem = 1024 + (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 4) * 8 + 16;
+    const size_t smem = 1024 + (size_t)STAGES * tc_atoms(BN) * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 4) * 8 + 16;
     auto kern = gemm_tcgen05_kernel<BN, STAGES, OT, SWAP>;
     static bool raised = false;
     if (!raised) {
@@ -418,8 +438,8 @@ extern "C" int vlrf_gemm_tcgen05(const void* X, const void* W, const float* bias
     }
     if (M <= 64 && Kc == nullptr) {
         // few rows: W fills the 128-row operand, the rows of X are the MMA's N
-#define SWAPPED(BNV) (out_dtype == VLRF_BF16 ? launch_tc<BNV, 8, __nv_bfloat16, true>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, kv, dev_err, stream) \
-                                             : launch_tc<BNV, 8, float, true>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, kv, dev_err, stream))
+#define SWAPPED(BNV) (out_dtype == VLRF_BF16 ? launch_tc<BNV, 4, __nv_bfloat16, true>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, kv, dev_err, stream) \
+                                             : launch_tc<BNV, 4, float, true>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, kv, dev_err, stream))
         VLRF_REQUIRE(out_dtype == VLRF_BF16 || out_dtype == VLRF_F32, "gemm_tcgen05: unknown output dtype %d", out_dtype);
         if (M <= 16) return SWAPPED(16);
         if (M <= 32) return SWAPPED(32);
@@ -447,9 +467,9 @@ extern "C" int vlrf_gemm_tcgen05(const void* X, const void* W, const float* bias
                                               : launch_tc<BNV, ST, float>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, kv, dev_err, stream))
     VLRF_REQUIRE(out_dtype == VLRF_BF16 || out_dtype == VLRF_F32, "gemm_tcgen05: unknown output dtype %d", out_dtype);
     if (best_bn == 256) return TILED(256, 4);
-    if (best_bn == 128) return TILED(128, 6);
-    if (best_bn == 96) return TILED(96, 7);
-    return TILED(64, 8);
+    if (best_bn == 128) return TILED(128, 3);
+    if (best_bn == 96) return TILED(96, 4);
+    return TILED(64, 4);
 #undef TILED
 }
 
