@@ -188,6 +188,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tc) {
             const uint32_t b = tc & 1;
             const int m0 = SWAP ? tile * TC_BM : (tile / tiles_n) * TC_BM, n0 = SWAP ? 0 : (tile % tiles_n) * BN;
+            const int m = m0 + q * 32 + lane;                 // this thread's row (when the roles are not exchanged)
+            // where this thread's row goes in the cache, if the product feeds one: three loads, each waiting for
+            // the one before, so they go out while the MMAs still run
+            int kv_blk = -2, kv_row = 0;                      // −2: nothing to write
+            if (!SWAP && kv.Kc != nullptr && m < M) {
+                const int slot = kv.tok_slot[m];
+                if (slot >= 0) {
+                    const int pos = kv.tok_pos[m];
+                    kv_blk = kv.block_table[(size_t)slot * kv.max_blocks + pos / kv.BT];
+                    kv_row = pos % kv.BT;
+                    if (kv_blk < 0) atomicOr(dev_err, VLRF_DEVERR_NO_BLOCK);
+                }
+            }
             if (*(volatile int*)s_abort || !tbar_wait_or_abort(&acc_full[b], (tc >> 1) & 1, s_abort)) { atomicExch(s_abort, 1); break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t tmem_d = tmem_base + b * ACC_STRIDE + ((uint32_t)(q * 32) << 16);
@@ -229,18 +242,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 __syncwarp();
                 if (lane == 0) tbar_arrive(&acc_empty[b]);    // this warp has read all it needs of the accumulator
                 continue;
-            }
-            const int m = m0 + q * 32 + lane;                 // this thread's row
-            // where this thread's row goes in the cache, if the product feeds one
-            int kv_blk = -2, kv_row = 0;                      // −2: nothing to write
-            if (kv.Kc != nullptr && m < M) {
-                const int slot = kv.tok_slot[m];
-                if (slot >= 0) {
-                    const int pos = kv.tok_pos[m];
-                    kv_blk = kv.block_table[(size_t)slot * kv.max_blocks + pos / kv.BT];
-                    kv_row = pos % kv.BT;
-                    if (kv_blk < 0) atomicOr(dev_err, VLRF_DEVERR_NO_BLOCK);
-                }
             }
             // the two warps of a lane group share the columns in runs of 32: half and half, or 64 + 32 of 96
             constexpr int SPLIT_AT = BN % 64 == 0 ? BN / 2 : 64;
