@@ -279,6 +279,50 @@ def test_split_k_projection_writes_keys_and_values_into_the_cache(split_k_always
     assert ops.device_errors() == 0
 
 
+@pytest.mark.parametrize("width", [64, 96, 128, 160, 192, 224, 256])
+def test_tcgen05_tile_widths(width):
+    """Every tile width of the tcgen05 product, forced (the choice by size would pick one): tails in M, N and K,
+    float32 with the residual in place, bfloat16 with an activation, and the cache scatter with heads of 8 columns
+    (16-byte pieces) and of 16 and 64 (32-byte pieces)."""
+    from vlrf_b200.csrc import library, ops
+    lib = library()
+    assert lib.vlrf_gemm_tcgen05_force_width(width) == 0
+    try:
+        M, N, K = 300, 1000, 200
+        x, w = randn(M, K, seed=90, dtype=torch.bfloat16), randn(N, K, seed=91, dtype=torch.bfloat16, scale=0.3)
+        bias, res = randn(N, seed=92), randn(M, N, seed=93)
+        want = x.double() @ w.double().T + bias.double()
+        acc = res.clone().to(DEV)
+        ops.linear(x.to(DEV), w.to(DEV), bias.to(DEV), acc, residual=acc)
+        assert rel_err(acc.cpu(), want + res.double()) < f32_sum_tol(K)
+        out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.linear(x.to(DEV), w.to(DEV), bias.to(DEV), out, act="gelu_tanh")
+        assert rel_err(out.float().cpu(), plain.gelu_tanh(want)) < 5e-3
+        for H, Hkv, dh in ((6, 3, 8), (4, 2, 16), (3, 3, 64)):
+            Nq = (H + 2 * Hkv) * dh
+            T = 150
+            wq, bq = randn(Nq, K, seed=94, dtype=torch.bfloat16, scale=0.2), randn(Nq, seed=95)
+            table = torch.tensor([[3, 1, 4], [5, 0, -1]], dtype=torch.int32)
+            slot = torch.tensor([0] * 100 + [-1] * 10 + [1] * 40, dtype=torch.int32)
+            pos = torch.tensor(list(range(60, 160)) + [0] * 10 + list(range(30, 70)), dtype=torch.int32)
+            kc = torch.full((6, Hkv, 64, dh), float("nan"), dtype=torch.bfloat16, device=DEV)
+            vc = torch.full_like(kc, float("nan"))
+            o = torch.empty(T, Nq, dtype=torch.bfloat16, device=DEV)
+            assert ops.linear(randn(T, K, seed=96, dtype=torch.bfloat16).to(DEV), wq.to(DEV), bq.to(DEV), o,
+                              kv_scatter=(kc, vc, table.to(DEV), slot.to(DEV), pos.to(DEV), H * dh, (H + Hkv) * dh, Hkv, dh))
+            oc = o.cpu()
+            for m in range(T):
+                if slot[m] < 0:
+                    continue
+                blk = int(table[slot[m], pos[m] // 64])
+                assert torch.equal(kc[blk, :, pos[m] % 64].cpu().reshape(-1), oc[m, H * dh:(H + Hkv) * dh])
+                assert torch.equal(vc[blk, :, pos[m] % 64].cpu().reshape(-1), oc[m, (H + Hkv) * dh:])
+            assert (~torch.isnan(kc.float())).sum().item() == 140 * Hkv * dh     # nothing else was touched
+        assert ops.device_errors() == 0
+    finally:
+        lib.vlrf_gemm_tcgen05_force_width(0)
+
+
 def test_split_k_rows_do_not_depend_on_the_batch(split_k_always):
     ops = split_k_always
     x, w, b = randn(64, 320, seed=56, dtype=torch.bfloat16), randn(1000, 320, seed=57, dtype=torch.bfloat16), randn(1000, seed=58)

@@ -56,6 +56,7 @@ _SIGNATURES = {
                           _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
                           _c_int, _c_void_p, _c_void_p],
     "vlrf_attn_prefill_tc_takes": [_c_int, _c_int, _c_int, _c_int, _c_int],
+    "vlrf_gemm_tcgen05_force_width": [_c_int],
     "vlrf_attn_prefill_tc_part_floats": [],
     "vlrf_attn_prefill_tc_max_parts": [],
     "vlrf_attn_prefill_tc_min_part_blocks": [],

@@ -244,7 +244,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 continue;
             }
             // the two warps of a lane group share the columns in runs of 32: half and half, or 64 + 32 of 96
-            constexpr int SPLIT_AT = BN % 64 == 0 ? BN / 2 : 64;
+            constexpr int SPLIT_AT = ((BN / 32 + 1) / 2) * 32;
             const int c_begin = half ? SPLIT_AT : 0, c_end = half ? BN : SPLIT_AT;
             // whether rows of Y, and heads in the cache, lie so that 32-byte stores are aligned
             const bool wide = (reinterpret_cast<uintptr_t>(Y) & 31) == 0 && (ldy % (32 / (int)sizeof(OT))) == 0;
@@ -415,6 +415,15 @@ int launch_tc(const void* X, const void* W, const float* bias, const float* resi
 }
 }  // namespace
 
+// A tile width (64, 96, 128, 160, 192, 224 or 256) for every product that is not given to the exchanged roles,
+// instead of the choice by size; 0 gives the choice back.  For measurements.
+namespace { int g_forced_width = 0; }
+extern "C" int vlrf_gemm_tcgen05_force_width(int bn) {
+    VLRF_REQUIRE(bn == 0 || bn == 64 || bn == 96 || bn == 128 || bn == 160 || bn == 192 || bn == 224 || bn == 256, "gemm_tcgen05: no tiles %d wide", bn);
+    g_forced_width = bn;
+    return VLRF_OK;
+}
+
 // Whether this kernel takes the shape (bfloat16 only): rows must start on 16-byte boundaries for TMA.
 extern "C" int vlrf_gemm_tcgen05_takes(int M, int N, int K, int ldx) {
     return (M >= 1 && N >= 1 && K >= 8 && K % 8 == 0 && ldx % 8 == 0) ? 1 : 0;
@@ -447,27 +456,32 @@ extern "C" int vlrf_gemm_tcgen05(const void* X, const void* W, const float* bias
         return SWAPPED(64);
 #undef SWAPPED
     }
-    // tile width: the fewest rounds of the persistent CTAs weighted by a tile's length (MMA time grows with
-    // the width; a fixed part per tile does not)
+    // tile width: the fewest rounds of the persistent CTAs, each weighted by the bytes a tile's stage pulls through
+    // L2 (128 rows of one operand and the tile's width of the other): that, not the MMAs, is what a round's time
+    // follows when all SMs run (measured over the products of GPT-2 small to XL at 512 to 8,192 rows)
     int best_bn = 128;
     {
         const int sms = sm_count_cached();
         long long best = -1;
-        const int widths[4] = {256, 128, 96, 64};
-        for (int i = 0; i < 4; ++i) {
+        const int widths[7] = {256, 224, 192, 160, 128, 96, 64};
+        for (int i = 0; i < 7; ++i) {
             const int bn = widths[i];
             if (bn > 64 && N <= bn / 2) continue;
             const long long tiles = (long long)((N + bn - 1) / bn) * ((M + 127) / 128);
             const long long rounds = (tiles + sms - 1) / sms;
             if (bn == 96 && rounds > 1) continue;      // the odd width only where it puts every tile on an SM of its own
-            const long long cost = rounds * (bn + 32);
+            const long long cost = rounds * (bn + 128);
             if (best < 0 || cost < best) { best = cost; best_bn = bn; }
         }
+        if (g_forced_width > 0) best_bn = g_forced_width;
     }
 #define TILED(BNV, ST) (out_dtype == VLRF_BF16 ? launch_tc<BNV, ST, __nv_bfloat16>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, kv, dev_err, stream) \
                                               : launch_tc<BNV, ST, float>(X, W, bias, residual, Y, M, N, K, ldx, ldy, act, kv, dev_err, stream))
     VLRF_REQUIRE(out_dtype == VLRF_BF16 || out_dtype == VLRF_F32, "gemm_tcgen05: unknown output dtype %d", out_dtype);
     if (best_bn == 256) return TILED(256, 4);
+    if (best_bn == 224) return TILED(224, 4);
+    if (best_bn == 192) return TILED(192, 5);
+    if (best_bn == 160) return TILED(160, 5);
     if (best_bn == 128) return TILED(128, 3);
     if (best_bn == 96) return TILED(96, 4);
     return TILED(64, 4);
