@@ -556,7 +556,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     float* cpart = wpart + DEC_WARPS * (DH + 2);                              // [DH + 2] (CLUSTER)
     uint64_t* bars = reinterpret_cast<uint64_t*>(cpart + DH + 2);            // CH_MAX barriers
     __shared__ int s_last;
-    __shared__ int s_bad;
+    static_assert(CH_MAX == DEC_WARPS, "a buffer and a barrier for every warp");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int row = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
@@ -576,27 +576,30 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     const int* table = block_table + (size_t)slot * max_blocks;
 
     if (threadIdx.x == 0) {
-        s_bad = 0;
         for (int i = 0; i < CH_MAX; ++i) dmbar_init(&bars[i], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    auto request = [&](int r0) -> bool {           // thread i requests chunk r0 + i of a round into buffer i
-        const int k0 = (r0 + threadIdx.x) * 32;
-        const int blk = table[k0 / BT];
+    // Warp w streams the chunks c_begin + w, + 8, + 16, … through buffer w on barrier w, on its own: it asks for
+    // its next chunk as soon as it has read the one before, and waits for no other warp until the merge.
+    unsigned char* my_k = kbuf + (size_t)warp * CHUNK_BYTES;
+    unsigned char* my_v = vbuf + (size_t)warp * CHUNK_BYTES;
+    uint64_t* my_bar = &bars[warp];
+    auto request = [&](int c, int blk) -> bool {   // one lane: chunk c, which lies in cache block blk, into this warp's buffer
         if (blk < 0) {
             atomicOr(dev_err, VLRF_DEVERR_NO_BLOCK);
-            s_bad = 1;
             return false;
         }
+        const int k0 = c * 32;
         const int y = (blk * Hkv + hk) * BT + (k0 % BT);
-        dmbar_expect_tx(&bars[threadIdx.x], 2 * CHUNK_BYTES);
-        tma_load_2d(kbuf + (size_t)threadIdx.x * CHUNK_BYTES, &tmap_k, 0, y, &bars[threadIdx.x]);
-        tma_load_2d(vbuf + (size_t)threadIdx.x * CHUNK_BYTES, &tmap_v, 0, y, &bars[threadIdx.x]);
+        dmbar_expect_tx(my_bar, 2 * CHUNK_BYTES);
+        tma_load_2d(my_k, &tmap_k, 0, y, my_bar);
+        tma_load_2d(my_v, &tmap_v, 0, y, my_bar);
         return true;
     };
-    bool issued = false;
-    if ((int)threadIdx.x < min(CH_MAX, c_end - c_begin) && c_begin + (int)threadIdx.x != c_new) issued = request(c_begin);
+    const int my_first = c_begin + warp;
+    int ok_first = 1;
+    if (lane == 0 && my_first < c_end && my_first != c_new) ok_first = request(my_first, table[my_first * 32 / BT]) ? 1 : 0;
     pdl_wait();                                    // the new key and value and the query are written
     pdl_launch_dependents();
     // the query as rows 0 of the MMA's 16-row operand: only lanes 0-3 hold anything but zeros
@@ -615,31 +618,23 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
 #pragma unroll
     for (int j = 0; j < 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
     float m = -INFINITY, l = 0.f;
-    bool gave_up = false;
+    bool gave_up = false, bad = false;
     uint32_t parity = 0;
-    for (int r0 = c_begin; r0 < c_end; r0 += CH_MAX) {
-        const int n_here = min(CH_MAX, c_end - r0);
-        if (r0 > c_begin) {
-            issued = false;
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // reads of the buffers before refilling them
-        }
-        if ((int)threadIdx.x < n_here && (r0 > c_begin || r0 + (int)threadIdx.x == c_new)) issued = request(r0);
-        __syncthreads();                           // s_bad is known
-        if (s_bad) {                               // leave only after the copies already issued have landed
-            if (issued) {
-                uint32_t polls = 0;
-                while (!dmbar_try_wait(&bars[threadIdx.x], parity) && ++polls <= DEC_WAIT_LIMIT) {}
-            }
-            __syncthreads();
-            break;
-        }
-        for (int i = warp; i < n_here && !gave_up; i += DEC_WARPS) {
+    if (lane == 0 && my_first < c_end && my_first == c_new) ok_first = request(my_first, table[my_first * 32 / BT]) ? 1 : 0;
+    if (!__shfl_sync(0xffffffffu, ok_first, 0)) bad = true;           // nothing of this warp's is in flight
+    {
+        for (int c = my_first; c < c_end && !bad; c += DEC_WARPS) {
+            // the table entry of the chunk after this one, looked up while this one is on its way
+            const int c_next = c + DEC_WARPS;
+            int blk_next = 0;
+            if (lane == 0 && c_next < c_end) blk_next = table[c_next * 32 / BT];
             uint32_t polls = 0;
-            while (!dmbar_try_wait(&bars[i], parity)) {
+            while (!dmbar_try_wait(my_bar, parity)) {
                 if (++polls > DEC_WAIT_LIMIT) { gave_up = true; break; }
             }
             if (gave_up) break;
-            const int k0 = (r0 + i) * 32;
+            const int i = warp;
+            const int k0 = c * 32;
             const uint32_t kb = dsmem_u32(kbuf + (size_t)i * CHUNK_BYTES), vb = dsmem_u32(vbuf + (size_t)i * CHUNK_BYTES);
             // Rows of the chunk behind the newest key hold whatever was there before; their scores are masked by
             // assignment below, but 0 · V would let a stray NaN through the MMA: clear those rows of V.
@@ -705,11 +700,16 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
                     dmma16816(o[j + 1], pa[2 * kk], 0u, pa[2 * kk + 1], 0u, b2, b3);
                 }
             }
+            parity ^= 1;
+            if (c_next < c_end) {
+                // the warp's reads of its buffer (and the rows of V it cleared) come before the copy that refills it
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                int ok_next = 1;
+                if (lane == 0) ok_next = request(c_next, blk_next) ? 1 : 0;
+                if (!__shfl_sync(0xffffffffu, ok_next, 0)) bad = true;      // (the loop ends with nothing in flight)
+            }
         }
-        if (gave_up) s_bad = 1;
-        parity ^= 1;
-        __syncthreads();                           // everyone is done with the buffers before they are refilled
-        if (s_bad) break;
     }
     if (gave_up && lane == 0) atomicOr(dev_err, VLRF_DEVERR_WAIT_TIMEOUT);
 
