@@ -254,7 +254,9 @@ def prefill_device(model_dir, dtype="bfloat16", reps=5):
     cfg = model.config
     n_seq, length = 2, min(1024, cfg.n_positions)
     engine = Engine(model, max_tokens=n_seq * length, n_slots=n_seq)
-    prompts = random_prompts(cfg.vocab_size, n_seq, length, 2)
+    import numpy as np
+    # host token ids as int32 arrays (a Python list of a thousand ids costs about 30 us to convert, inside the step)
+    prompts = [np.asarray(p, dtype=np.int32) for p in random_prompts(cfg.vocab_size, n_seq, length, 2)]
     times = []
     for r in range(reps + 2):
         slots = [engine.start_sequence() for _ in range(n_seq)]

@@ -61,8 +61,34 @@ class _KVGroup:
         shape = (len(self.entries), n_blocks, need.n_kv_heads, BLOCK_TOKENS, need.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
         self.v = torch.zeros(shape, dtype=dtype, device=device)
-        self.table_host = np.full((n_slots, max_blocks), -1, dtype=np.int32)
+        # the host's copy of the table lies in pinned memory where there is a GPU, so that bringing the device's
+        # copy up to date is an asynchronous copy; `before_write` waits for a copy still reading it
+        self._pinned = None
+        if torch.device(device).type == "cuda":
+            self._pinned = torch.full((n_slots, max_blocks), -1, dtype=torch.int32, pin_memory=True)
+            self.table_host = self._pinned.numpy()
+        else:
+            self.table_host = np.full((n_slots, max_blocks), -1, dtype=np.int32)
         self.table_dev = torch.full((n_slots, max_blocks), -1, dtype=torch.int32, device=device)
+        self.dirty = False
+        self._copied = None            # event behind the latest copy of the table, while it may still be running
+
+    def before_write(self) -> None:
+        """Call before changing `table_host`: a copy to the device that is still under way reads it."""
+        if self._copied is not None:
+            self._copied.synchronize()
+            self._copied = None
+        self.dirty = True
+
+    def sync(self) -> None:
+        if not self.dirty:
+            return
+        if self._pinned is not None:
+            self.table_dev.copy_(self._pinned, non_blocking=True)
+            self._copied = torch.cuda.Event()
+            self._copied.record()
+        else:
+            self.table_dev.copy_(torch.from_numpy(self.table_host), non_blocking=False)
         self.dirty = False
 
     def blocks_of(self, slot) -> list[int]:
@@ -185,9 +211,9 @@ class SequenceCache:
         for g, idx in zip(kv, wanted):
             if not idx:
                 continue
+            g.before_write()
             for i, b in zip(idx, g.pool.take(len(idx))):
                 g.table_host[slot, i] = b
-            g.dirty = True
 
     def advance(self, slot: int, n_tokens: int) -> None:
         self._check_slot(slot)
@@ -202,9 +228,9 @@ class SequenceCache:
                 row = g.table_host[slot]
                 old = [int(row[i]) for i in range(keep_from) if row[i] >= 0]
                 if old:
+                    g.before_write()
                     row[:keep_from] = -1
                     g.pool.give(old)
-                    g.dirty = True
 
     def release(self, slot: int) -> None:
         self._check_slot(slot)
@@ -212,18 +238,17 @@ class SequenceCache:
             if isinstance(g, _KVGroup):
                 blocks = g.blocks_of(slot)
                 if blocks:
+                    g.before_write()
                     g.pool.give(blocks)
                     g.table_host[slot, :] = -1
-                    g.dirty = True
         self.lengths[slot] = 0
         self.slots.give([slot])
 
     def sync_tables(self) -> None:
         """Bring the device's block tables up to date (a copy on the current stream)."""
         for g in self._groups:
-            if isinstance(g, _KVGroup) and g.dirty:
-                g.table_dev.copy_(torch.from_numpy(g.table_host), non_blocking=False)
-                g.dirty = False
+            if isinstance(g, _KVGroup):
+                g.sync()
 
     # -- invariants ---------------------------------------------------------------------------
     def check(self) -> None:

@@ -26,7 +26,7 @@ DEVERR_TEXT = {1: "a token id outside the vocabulary", 2: "a position outside th
 @dataclasses.dataclass
 class StepEntry:
     slot: int
-    tokens: list
+    tokens: list                 # token ids: a list, or an integer numpy array (which spares the step the conversion)
     want: list = dataclasses.field(default_factory=list)   # indices into `tokens`
 
 
@@ -84,7 +84,7 @@ class Engine:
         changes nothing if the step cannot run."""
         if not entries:
             raise StepError("a step needs at least one sequence")
-        vocab, seen = self.model.vocab_size, set()
+        vocab, seen, arrays = self.model.vocab_size, set(), []
         for e in entries:
             if e.slot in seen:
                 raise StepError(f"slot {e.slot} appears twice in one step")
@@ -96,10 +96,11 @@ class Engine:
             if self.cache.lengths[e.slot] + len(e.tokens) > self.model.max_seq_len:
                 raise StepError(f"slot {e.slot}: {self.cache.lengths[e.slot]} + {len(e.tokens)} tokens exceed the "
                                 f"{self.model.max_seq_len} positions of the model")
-            arr = np.asarray(e.tokens, dtype=np.int64)
+            arr = np.asarray(e.tokens, dtype=np.int64)         # (a list is converted once: this is most of a long prompt's host time)
             if arr.min() < 0 or arr.max() >= vocab:
                 bad = int(arr[(arr < 0) | (arr >= vocab)][0])
                 raise StepError(f"slot {e.slot}: token id {bad} lies outside the vocabulary of {vocab}")
+            arrays.append(arr)
             for w in e.want:
                 if not (0 <= int(w) < len(e.tokens)):
                     raise StepError(f"slot {e.slot}: wanted place {w} is not among its {len(e.tokens)} tokens")
@@ -116,7 +117,7 @@ class Engine:
         at, r = 0, 0
         for i, e in enumerate(entries):
             n, p0 = len(e.tokens), self.cache.lengths[e.slot]
-            tokens[at:at + n] = e.tokens
+            tokens[at:at + n] = arrays[i]
             tok_slot[at:at + n] = e.slot
             tok_pos[at:at + n] = np.arange(p0, p0 + n, dtype=np.int32)
             seq_slot[i], seq_start[i], seq_pos0[i] = e.slot, at, p0
