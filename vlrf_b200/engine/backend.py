@@ -20,6 +20,8 @@ class _Batch:
     session: DecodeSession | None = None
     staging: torch.Tensor | None = None   # pinned host int32: the tokens fed at a decode step
     result: torch.Tensor | None = None    # pinned host int32: the tokens a decode step chose
+    staging_np: object = None             # numpy view of `staging`
+    graph_calls: tuple | None = None      # (feed, choose, fetch) of the replayed step, made once
 
 
 def _bucket(n: int) -> int:
@@ -61,6 +63,7 @@ class DeviceBackend:
             self.engine.cache.sync_tables()
             batch.staging = torch.zeros(len(batch.slots), dtype=torch.int32, pin_memory=True)
             batch.result = torch.zeros(len(batch.slots), dtype=torch.int32, pin_memory=True)
+            batch.staging_np = batch.staging.numpy()
         if batch.session is not None:
             return self._run_decode(batch, rows, tokens)
         entries = [StepEntry(batch.slots[r], toks, [len(toks) - 1]) for r, toks in zip(rows, tokens)]
@@ -75,7 +78,7 @@ class DeviceBackend:
     def _run_decode(self, batch: _Batch, rows: list, tokens: list) -> list:
         sess = batch.session
         n = len(batch.slots)
-        st = batch.staging.numpy()                             # (a view of the pinned buffer)
+        st = batch.staging_np                                  # (a view of the pinned buffer)
         for r, toks in zip(rows, tokens):
             st[r] = toks[0]
         sampler = batch.sampler
@@ -83,15 +86,18 @@ class DeviceBackend:
         if not sampler.any_penalties:
             # One replayed graph a step: this step's inputs host → device, the model, the sampling kernel
             # (which also moves the positions on), the result device → host.
-            def feed():
-                sess.tokens[:n].copy_(batch.staging, non_blocking=True)
+            if batch.graph_calls is None:
+                def feed():
+                    sess.tokens[:n].copy_(batch.staging, non_blocking=True)
 
-            def choose(logits):
-                sampler.sample(logits[:n], everyone, next_pos=sess.tok_pos, row_slot=sess.tok_slot)
+                def choose(logits):
+                    sampler.sample(logits[:n], everyone, next_pos=sess.tok_pos, row_slot=sess.tok_slot)
 
-            def fetch():
-                batch.result.copy_(sampler.out[:n], non_blocking=True)
+                def fetch():
+                    batch.result.copy_(sampler.out[:n], non_blocking=True)
 
+                batch.graph_calls = (feed, choose, fetch)
+            feed, choose, fetch = batch.graph_calls
             sess.step_sampled(choose, key=sampler, state=(sampler.rng_ctr,), before=feed, after=fetch)
             torch.cuda.current_stream().synchronize()          # the step's result is in host memory
             host = batch.result.tolist()
