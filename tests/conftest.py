@@ -21,7 +21,12 @@ TINY_B = dict(model_type="gpt2", n_layer=3, n_embd=96, n_head=3, n_inner=320, vo
 TINY_C = dict(model_type="gpt2", n_layer=2, n_embd=192, n_head=3, n_inner=None, vocab_size=777, n_positions=320,
               layer_norm_epsilon=1e-5, activation_function="gelu_new", scale_attn_by_inverse_layer_idx=False,
               tie_word_embeddings=True, bos_token_id=5, eos_token_id=6)
-TINY = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C}
+#: a fourth one whose width (80 = 5 heads of 16) and inner size (136) are no multiples of 32 and whose vocabulary
+#: is odd: tails in every product, no fused norm, row statistics with a short last segment
+TINY_D = dict(model_type="gpt2", n_layer=2, n_embd=80, n_head=5, n_inner=136, vocab_size=333, n_positions=160,
+              layer_norm_epsilon=1e-5, activation_function="gelu_new", scale_attn_by_inverse_layer_idx=True,
+              tie_word_embeddings=True, bos_token_id=3, eos_token_id=4)
+TINY = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C, "tiny_d": TINY_D}
 
 #: tolerances, fixed before the first measurement: the largest absolute logit error over the logit scale
 #: (largest absolute logit of the plain implementation)

@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 DTYPES = [("float32", TOL_F32), ("bfloat16", TOL_BF16)]
 #: request lengths per model: prompts of 5/17/31 and 1/9/40/100 tokens with their decode steps added, and longer ones
 LENGTHS = {"tiny_a": [5 + 16, 17 + 16, 31 + 16, 70, 128], "tiny_b": [1 + 24, 9 + 24, 40 + 24, 100 + 24, 200, 256],
-           "tiny_c": [3 + 20, 64 + 20, 65 + 20, 127 + 20, 250, 320]}
+           "tiny_c": [3 + 20, 64 + 20, 65 + 20, 127 + 20, 250, 320], "tiny_d": [2 + 12, 33 + 12, 64 + 12, 100, 160]}
 
 
 @pytest.fixture(scope="module")
@@ -47,7 +47,7 @@ def compare(got, truth, tol, what):
 
 
 @pytest.mark.parametrize("dtype,tol", DTYPES)
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d"])
 def test_each_request_alone_and_whole(model_dirs, requests_and_truth, name, dtype, tol):
     reqs, truth = requests_and_truth[name]
     eng = make_engine(model_dirs, name, dtype, 320)
@@ -57,7 +57,7 @@ def test_each_request_alone_and_whole(model_dirs, requests_and_truth, name, dtyp
 
 
 @pytest.mark.parametrize("dtype,tol", DTYPES)
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d"])
 def test_last_32_tokens_one_by_one(model_dirs, requests_and_truth, name, dtype, tol):
     reqs, truth = requests_and_truth[name]
     eng = make_engine(model_dirs, name, dtype, 320)
@@ -65,10 +65,10 @@ def test_last_32_tokens_one_by_one(model_dirs, requests_and_truth, name, dtype, 
 
 
 @pytest.mark.parametrize("dtype,tol", DTYPES)
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d"])
 def test_unequal_batches_one_after_another(model_dirs, requests_and_truth, name, dtype, tol):
     reqs, truth = requests_and_truth[name]
-    decode = {"tiny_a": 16, "tiny_b": 24, "tiny_c": 20}[name]
+    decode = {"tiny_a": 16, "tiny_b": 24, "tiny_c": 20, "tiny_d": 12}[name]
     prompt_lens = [max(1, len(r) - decode) for r in reqs]
     # a cache just large enough for one batch: the second batch must reuse slots and blocks of the first
     batch = 3 if name == "tiny_a" else 4
@@ -98,7 +98,7 @@ def test_long_decoding_from_one_token(model_dirs, plain_models, dtype, tol):
 
 
 @pytest.mark.parametrize("dtype,tol", DTYPES)
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d"])
 def test_first_tokens(model_dirs, plain_models, name, dtype, tol):
     cfg, w = plain_models[name]
     reqs = [random_ids(cfg["vocab_size"], n, 50 + n) for n in (1, 2, 3, 1)]

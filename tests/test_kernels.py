@@ -455,6 +455,25 @@ def test_attention_decode_finds_one_far_key_and_respects_a_window(far, n_split):
         assert rel_err(got, plain_attention(q, k, v, 1.0, window)) < 2e-5
 
 
+@pytest.mark.parametrize("far", [0, 31, 32, 255, 256, 511, 639])
+@pytest.mark.parametrize("n_split", [1, 3])
+def test_attention_decode_bf16_finds_one_far_key_and_respects_a_window(far, n_split):
+    """The same for the tensor-core decode kernel (bfloat16, head size 64) over 20 chunks of 32 keys, so that a
+    warp reads up to three chunks through its buffer: a chunk dropped, read twice or read before it has landed
+    shows as a wrong value, not as a small error."""
+    H, dh, C = 3, 64, 640
+    q, k, v = (t.to(torch.bfloat16).float() for t in (randn(H, 1, dh, seed=66), randn(H, C, dh, seed=67) * 0.1, randn(H, C, dh, seed=68)))
+    k[:, far] = (q[:, 0] * 4.0).to(torch.bfloat16).float()
+    got = run_attention(q, k, v, dtype=torch.bfloat16, scale=1.0, impl="decode", n_split=n_split)
+    assert rel_err(got[:, 0], v[:, far]) < 1e-2
+    for window in (1, 33, 200, C - far, C - 1 - far):
+        if window < 1:
+            continue
+        got = run_attention(q, k, v, dtype=torch.bfloat16, scale=1.0, window=window, impl="decode", n_split=n_split,
+                            scratch=(n_split == 1))
+        assert rel_err(got, plain_attention(q, k, v, 1.0, window)) < 1.5e-2
+
+
 @pytest.mark.parametrize("window", [1, 31, 32, 33, 64, 100])
 def test_attention_window_edges(window):
     H, dh, T, C = 2, 32, 150, 150
