@@ -108,6 +108,20 @@ def test_first_tokens(model_dirs, plain_models, name, dtype, tol):
     compare(drive_batches(eng, reqs, 4, [1, 1, 1, 1]), truth, tol, "first tokens, batch")
 
 
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+@pytest.mark.parametrize("name", ["tiny_c", "tiny_d"])
+def test_a_batch_of_a_hundred_sequences(model_dirs, plain_models, name, dtype, tol):
+    """More sequences in a decode step than the few-row kernels take (64): prompts of 1 to 40 tokens in one
+    step, then ten single-token steps of a hundred rows that shrink as the short requests end."""
+    cfg, w = plain_models[name]
+    reqs = [random_ids(cfg["vocab_size"], 3 + (i * 7) % 40, 100 + i) for i in range(100)]
+    truth = [plain.logits_all_positions(cfg, w, ids) for ids in reqs]
+    eng = make_engine(model_dirs, name, dtype, 64 * len(reqs))
+    got = drive_batches(eng, reqs, len(reqs), [max(1, len(r) - 10) for r in reqs])
+    compare(got, truth, tol, "a batch of 100")
+    assert eng.cache.slots.n_held == 0
+
+
 def test_step_refuses_what_it_cannot_run(model_dirs):
     from vlrf_b200.cache import CacheError
     from vlrf_b200.engine import StepEntry, StepError
