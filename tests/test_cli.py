@@ -1,0 +1,74 @@
+"""The command line: `init` and `info` on the CPU, `run` on the GPU against the plain implementation."""
+import json
+
+import pytest
+
+import plain_gpt2 as plain
+from conftest import TINY_B
+
+
+def run_cli(argv, capsys):
+    from vlrf_b200.cli import main
+    assert main(argv) == 0
+    return capsys.readouterr().out
+
+
+def test_init_writes_a_model_folder_and_info_reads_it(tmp_path, capsys):
+    cfg_file = tmp_path / "cfg.json"
+    cfg_file.write_text(json.dumps(TINY_B))
+    out = run_cli(["init", "--config", str(cfg_file), "--out", str(tmp_path / "m"), "--seed", "9"], capsys)
+    assert "seed 9" in out
+    assert (tmp_path / "m" / "config.json").exists() and (tmp_path / "m" / "model.safetensors").exists()
+    # the same seed gives the same bytes, another seed others
+    run_cli(["init", "--config", str(cfg_file), "--out", str(tmp_path / "m2"), "--seed", "9"], capsys)
+    run_cli(["init", "--config", str(cfg_file), "--out", str(tmp_path / "m3"), "--seed", "10"], capsys)
+    same = (tmp_path / "m" / "model.safetensors").read_bytes()
+    assert same == (tmp_path / "m2" / "model.safetensors").read_bytes()
+    assert same != (tmp_path / "m3" / "model.safetensors").read_bytes()
+    info = run_cli(["info", "--model", str(tmp_path / "m")], capsys)
+    assert "architecture: gpt2" in info
+    shown = json.loads(info[info.index("{"):info.rindex("}") + 1])
+    for key in ("n_layer", "n_embd", "n_head", "n_inner", "vocab_size", "n_positions", "layer_norm_epsilon"):
+        assert shown[key] == TINY_B[key]
+    cfg, w = plain.read_model_dir(tmp_path / "m")
+    n_params = sum(int(t.numel()) for t in w.values())
+    assert f"parameters: {n_params:,}" in info
+
+
+def test_init_takes_a_preset_name(tmp_path, capsys):
+    run_cli(["init", "--config", "tiny-a", "--out", str(tmp_path / "a")], capsys)
+    assert json.loads((tmp_path / "a" / "config.json").read_text())["n_embd"] == 64
+
+
+def test_prompts_from_text_ids_and_file(tmp_path):
+    import argparse
+
+    from vlrf_b200.cli import _prompts
+    ns = argparse.Namespace(prompts_file=None, prompt_ids=None, prompt="Hi!")
+    assert _prompts(ns, 512) == [[ord("H") + 4, ord("i") + 4, ord("!") + 4]]         # byte + 4, as the reference without a tokenizer
+    assert _prompts(argparse.Namespace(prompts_file=None, prompt_ids=None, prompt="\xff"), 100) == [[99, 99]]   # capped at the vocabulary
+    assert _prompts(argparse.Namespace(prompts_file=None, prompt_ids="5, 17,3", prompt=None), 512) == [[5, 17, 3]]
+    f = tmp_path / "p.txt"
+    f.write_text("1 2 3\n\n4,5\n")
+    assert _prompts(argparse.Namespace(prompts_file=str(f), prompt_ids=None, prompt=None), 512) == [[1, 2, 3], [4, 5]]
+    with pytest.raises(SystemExit):
+        _prompts(argparse.Namespace(prompts_file=None, prompt_ids=None, prompt=None), 512)
+
+
+@pytest.mark.gpu
+def test_run_generates_what_the_plain_implementation_would(model_dirs, plain_models, tmp_path, capsys):
+    cfg, w = plain_models["tiny_b"]
+    f = tmp_path / "prompts.txt"
+    f.write_text("5 17 3 900 44\n7\n")
+    out = run_cli(["run", "--model", str(model_dirs["tiny_b"]), "--prompts-file", str(f), "--tokens", "6", "--greedy",
+                   "--stop-id", "999", "--dtype", "float32"], capsys)
+    outputs = [line for prev, line in zip(out.splitlines(), out.splitlines()[1:]) if prev.startswith("--- Output")]
+    assert len(outputs) == 2
+    for prompt, line in zip(([5, 17, 3, 900, 44], [7]), outputs):
+        ids = list(prompt)
+        for tok in (int(t) for t in line.split()):
+            lg = plain.logits_all_positions(cfg, w, ids)[-1]
+            assert float(lg.max() - lg[tok]) <= 2e-4 * float(lg.abs().max())
+            ids.append(tok)
+        assert len(ids) == len(prompt) + 6
+    assert "12 generated" in out

@@ -22,7 +22,14 @@ def dtype_code(dt: torch.dtype) -> int:
     raise KernelError(f"kernels take float32 or bfloat16, not {dt}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current CUDA stream's handle.  Asked for at every launch, so by the short way where torch has one
+    (`torch.cuda.current_stream()` builds a Stream object: about 5 us, a quarter of a launch's host time)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 

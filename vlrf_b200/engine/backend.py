@@ -87,14 +87,18 @@ class DeviceBackend:
             # One replayed graph a step: this step's inputs host → device, the model, the sampling kernel
             # (which also moves the positions on), the result device → host.
             if batch.graph_calls is None:
+                # (the three name the tensors, not the batch: a batch that held functions that hold the batch would
+                # be cyclic garbage, and its graph would wait for a collection at some later, arbitrary moment)
+                staging, result = batch.staging, batch.result
+
                 def feed():
-                    sess.tokens[:n].copy_(batch.staging, non_blocking=True)
+                    sess.tokens[:n].copy_(staging, non_blocking=True)
 
                 def choose(logits):
                     sampler.sample(logits[:n], everyone, next_pos=sess.tok_pos, row_slot=sess.tok_slot)
 
                 def fetch():
-                    batch.result.copy_(sampler.out[:n], non_blocking=True)
+                    result.copy_(sampler.out[:n], non_blocking=True)
 
                 batch.graph_calls = (feed, choose, fetch)
             feed, choose, fetch = batch.graph_calls

@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import torch
 
+from .capture import capture_into
 from ..parts.context import StepContext, Workspace
 from .step import Engine
 
@@ -101,7 +102,7 @@ class DecodeSession:
                     t.copy_(k)
                 self.ws.frozen = True
                 g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g):
+                with capture_into(g):
                     self.logits = run()
                 self._greedy_graph, self._greedy_out = g, key
             self._greedy_graph.replay()
@@ -156,7 +157,7 @@ class DecodeSession:
             torch.cuda.synchronize()
             self.ws.frozen = True
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            with capture_into(g):
                 self.logits = self.model.forward(self._context(), c)
             self.graph = g
         if self.use_graph:

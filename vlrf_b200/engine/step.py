@@ -16,6 +16,7 @@ import torch
 
 from ..cache import CacheError, SequenceCache
 from ..csrc import KernelError, library
+from .capture import capture_into
 from ..parts.context import StepContext, Workspace
 from .model import DecoderModel
 
@@ -184,7 +185,7 @@ class Engine:
             return logits
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        with capture_into(graph):
             logits = self.model.forward(ctx, self.cache)
         if self.ws.generation != self._graph_generation:   # the capture itself had to allocate: do not keep it
             self._graph_generation = self.ws.generation

@@ -20,10 +20,15 @@ class Workspace:
     def __init__(self, device):
         self.device = torch.device(device)
         self._bufs: dict[str, torch.Tensor] = {}
+        self._views: dict = {}   # (name, rows, cols, dtype) -> the view handed out last time (making one costs 2 to 3 us)
         self.frozen = False  # set while a captured graph depends on the addresses
         self.generation = 0  # counts (re)allocations: captured steps are valid for one generation only
 
     def get(self, name: str, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
+        key = (name, rows, cols, dtype)
+        view = self._views.get(key)
+        if view is not None:
+            return view
         n = rows * cols
         buf = self._bufs.get(name)
         if buf is None or buf.dtype != dtype or buf.numel() < n:
@@ -35,7 +40,12 @@ class Workspace:
             buf = torch.empty(cap, dtype=dtype, device=self.device)
             self._bufs[name] = buf
             self.generation += 1
-        return buf[:n].view(rows, cols)
+            self._views.clear()                  # views of the buffer that went
+        if len(self._views) > 1024:
+            self._views.clear()
+        view = buf[:n].view(rows, cols)
+        self._views[key] = view
+        return view
 
     def get_zeroed(self, name: str, n: int, dtype: torch.dtype) -> torch.Tensor:
         """A flat buffer that is zero when first handed out (and again after it had to grow); whoever uses
