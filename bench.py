@@ -12,7 +12,10 @@ One JSON line is printed:
              the sampled tokens feed the next step on the device
   e2e        the same through the Python entry point (`Model.generate_ids`): every step copies its input
              tokens from pinned host memory to the device and reads the sampled tokens back
-  prefill    one step of 2 x 1,024 prompt tokens: tokens a second, and its flops / time / the bf16 peak
+  prefill    one step of 2 x 1,024 prompt tokens: tokens a second, and its flops / time / the bf16 peak; the
+             engine replays a captured graph for a step of a shape it has run before, which the timed
+             repetitions are; `ms_new_shape` is the same step launched kernel by kernel from the host, as
+             the first step of a new shape is
   roofline   decode: bytes the step has to read (every weight it uses once, the cache of the live
              sequences) / its time, against the HBM copy peak
   points     decode tokens a second at batch 1 and 64
@@ -247,13 +250,16 @@ def decode_e2e(model_dir, batch, steps, warmup, dtype="bfloat16"):
                 d2h=(marks["d2h1"] - marks["d2h0"]) / steps, steps=steps)
 
 
-def prefill_device(model_dir, dtype="bfloat16", reps=5):
+def prefill_device(model_dir, dtype="bfloat16", reps=5, replay=True):
+    """One step of 2 x 1,024 prompt tokens.  replay: the engine replays a captured graph for a step whose shape
+    it has seen before (the default); without it every kernel is launched from the host, as for a new shape."""
     import torch
     from vlrf_b200.engine import Engine, StepEntry, load_model
     model = load_model(model_dir, dtype)
     cfg = model.config
     n_seq, length = 2, min(1024, cfg.n_positions)
     engine = Engine(model, max_tokens=n_seq * length, n_slots=n_seq)
+    engine.capture_repeated_steps = replay
     import numpy as np
     # host token ids as int32 arrays (a Python list of a thousand ids costs about 30 us to convert, inside the step)
     prompts = [np.asarray(p, dtype=np.int32) for p in random_prompts(cfg.vocab_size, n_seq, length, 2)]
@@ -317,6 +323,7 @@ def main() -> int:
         dec = decode_device(model_dir, args.batch, args.steps, warmup)
         e2e = decode_e2e(model_dir, args.batch, dec["steps"], warmup)
         pre = prefill_device(model_dir)
+        pre_new_shape = prefill_device(model_dir, replay=False)
         points = {}
         if not args.skip_points:
             for b in (1, 64):
@@ -344,7 +351,8 @@ def main() -> int:
                 "d2h_bytes_per_step": e2e["d2h"]},
         "gpu_launches": dec["launches"],
         "prefill": {"value": round(pre["tokens"] / (pre["ms"] / 1e3), 1), "tokens": pre["tokens"],
-                    "ms": round(pre["ms"], 4), "frac": round(pre_tflops / bf16_tflops, 4)},
+                    "ms": round(pre["ms"], 4), "frac": round(pre_tflops / bf16_tflops, 4),
+                    "ms_new_shape": round(pre_new_shape["ms"], 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s",
                      "frac": round(achieved / hbm_gbs, 4)},
         "points": points,
