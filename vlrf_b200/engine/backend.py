@@ -22,6 +22,7 @@ class _Batch:
     result: torch.Tensor | None = None    # pinned host int32: the tokens a decode step chose
     staging_np: object = None             # numpy view of `staging`
     graph_calls: tuple | None = None      # (feed, choose, fetch) of the replayed step, made once
+    stream: object = None                 # the stream the batch's steps run on (the current one when decoding began)
 
 
 def _bucket(n: int) -> int:
@@ -64,6 +65,7 @@ class DeviceBackend:
             batch.staging = torch.zeros(len(batch.slots), dtype=torch.int32, pin_memory=True)
             batch.result = torch.zeros(len(batch.slots), dtype=torch.int32, pin_memory=True)
             batch.staging_np = batch.staging.numpy()
+            batch.stream = torch.cuda.current_stream()
         if batch.session is not None:
             return self._run_decode(batch, rows, tokens)
         entries = [StepEntry(batch.slots[r], toks, [len(toks) - 1]) for r, toks in zip(rows, tokens)]
@@ -82,7 +84,6 @@ class DeviceBackend:
         for r, toks in zip(rows, tokens):
             st[r] = toks[0]
         sampler = batch.sampler
-        everyone = list(range(n))
         if not sampler.any_penalties:
             # One replayed graph a step: this step's inputs host → device, the model, the sampling kernel
             # (which also moves the positions on), the result device → host.
@@ -90,6 +91,7 @@ class DeviceBackend:
                 # (the three name the tensors, not the batch: a batch that held functions that hold the batch would
                 # be cyclic garbage, and its graph would wait for a collection at some later, arbitrary moment)
                 staging, result = batch.staging, batch.result
+                everyone = list(range(n))
 
                 def feed():
                     sess.tokens[:n].copy_(staging, non_blocking=True)
@@ -103,12 +105,12 @@ class DeviceBackend:
                 batch.graph_calls = (feed, choose, fetch)
             feed, choose, fetch = batch.graph_calls
             sess.step_sampled(choose, key=sampler, state=(sampler.rng_ctr,), before=feed, after=fetch)
-            torch.cuda.current_stream().synchronize()          # the step's result is in host memory
+            batch.stream.synchronize()                         # the step's result is in host memory
             host = batch.result.tolist()
         else:
             sess.tokens[:n].copy_(batch.staging, non_blocking=True)    # this step's inputs, host → device
             logits = sess.step(advance_on_device=False)            # the sampling kernel moves the positions on
-            out = sampler.sample(logits[:n], everyone, next_pos=sess.tok_pos, row_slot=sess.tok_slot)
+            out = sampler.sample(logits[:n], list(range(n)), next_pos=sess.tok_pos, row_slot=sess.tok_slot)
             host = out.tolist()                                    # this step's result, device → host; synchronises
         self.h2d_bytes += 4 * n
         self.d2h_bytes += 4 * n

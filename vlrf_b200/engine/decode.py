@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import torch
 
+from ..csrc import launch_count
 from .capture import capture_into
 from ..parts.context import StepContext, Workspace
 from .step import Engine
@@ -72,7 +73,6 @@ class DecodeSession:
         that stay where they are.  The graph is kept as long as `key` is the same object; `state`:
         tensors that `sample` changes in place (random counters), put back after the uncaptured run that
         sizes the workspace."""
-        from ..csrc import launch_count
         c = self.engine.cache
         for s, live in zip(self.slots, self.live):
             if live and c.lengths[s] + 1 > self.model.max_seq_len:
@@ -144,7 +144,6 @@ class DecodeSession:
         the device too unless `advance_on_device` is False — then whoever samples must pass
         `next_pos=self.tok_pos, row_slot=self.tok_slot` (and `next_tokens=self.tokens`) to the sampling
         kernel, which does it in the same launch."""
-        from ..csrc import launch_count
         c = self.engine.cache
         for s, live in zip(self.slots, self.live):
             if live and c.lengths[s] + 1 > self.model.max_seq_len:

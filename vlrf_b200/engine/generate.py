@@ -112,19 +112,22 @@ def run_batch(backend, batch: list, default_stop: tuple, max_seq_len: int, on_to
     handle = backend.open_batch([batch[r] for r in live])
     local = {row: i for i, row in enumerate(live)}   # row of the batch → row of the backend's batch
     feed = {row: list(batch[row].prompt) for row in live}
+    # what a row's decision needs, looked up once (this loop runs between every two steps of the device)
+    stops = {row: (batch[row].params.stop_token_ids if batch[row].params.stop_token_ids is not None else default_stop)
+             for row in live}
     try:
         while live:
             sampled = backend.run(handle, [local[r] for r in live], [feed[r] for r in live])
             still = []
             for row, tok in zip(live, sampled):
                 req = batch[row]
-                new[row].append(int(tok))
-                stop_ids = req.params.stop_token_ids if req.params.stop_token_ids is not None else default_stop
-                reason = finish_reason(req, new[row], stop_ids, max_seq_len)
-                if on_token is not None and reason is None and on_token(req.index, int(tok)) is False:
+                tok = int(tok)
+                new[row].append(tok)
+                reason = finish_reason(req, new[row], stops[row], max_seq_len)
+                if on_token is not None and reason is None and on_token(req.index, tok) is False:
                     reason = "stop"
                 if reason is None:
-                    feed[row] = [int(tok)]
+                    feed[row] = [tok]
                     still.append(row)
                 else:
                     results[row] = GenerationResult(list(req.prompt), new[row], reason)
