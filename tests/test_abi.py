@@ -72,3 +72,39 @@ def test_every_entry_point_that_python_calls_exists():
     assert len(used) >= 20
     missing = sorted(u for u in used if u not in defs)
     assert not missing, f"called from Python but defined in no source: {missing}"
+
+
+def header_declarations() -> dict:
+    """name -> (return type, [argument kinds]) of every prototype in the library's C header."""
+    text = (SRC / "vlrf_b200_kernels.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", re.sub(r"//[^\n]*", "", text), flags=re.S)
+    out = {}
+    for m in re.finditer(r"^([\w\s\*]+?)\s*\b(vlrf_\w+)\s*\(([^)]*)\)\s*;", text, flags=re.M):
+        ret, name, args = " ".join(m.group(1).split()), m.group(2), m.group(3).strip()
+        kinds = []
+        if args and args != "void":
+            for a in args.split(","):
+                a = " ".join(a.split())
+                if "*" in a or a.startswith("cudaStream_t"):
+                    kinds.append("pointer")
+                elif re.match(r"(const )?(unsigned )?int\b", a):
+                    kinds.append("int")
+                elif re.match(r"(const )?float\b", a):
+                    kinds.append("float")
+                else:
+                    kinds.append("int64")
+        out[name] = (ret, kinds)
+    return out
+
+
+def test_the_c_header_declares_exactly_what_the_sources_define():
+    """`vlrf_b200_kernels.h` is what a C or C++ caller includes: every exported function, with the arguments of
+    its definition, and nothing that does not exist."""
+    defs, decl = c_definitions(), header_declarations()
+    assert sorted(decl) == sorted(defs)
+    for name, (ret, kinds) in defs.items():
+        assert decl[name] == (ret, kinds), f"{name}: header {decl[name]} against source {(ret, kinds)}"
+    # every source sees the header (through common.cuh), so the compiler holds each definition against it too
+    assert '#include "vlrf_b200_kernels.h"' in (SRC / "common.cuh").read_text()
+    for path in SRC.glob("*.cu"):
+        assert '#include "common.cuh"' in path.read_text(), f"{path.name} does not include common.cuh"

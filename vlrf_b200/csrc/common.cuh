@@ -10,23 +10,10 @@
 #include <cstdio>
 #include <cstdarg>
 
-#define VLRF_OK 0
-#define VLRF_ERR_INVALID_ARG 1   // same numbering idea as the reference's status enum (include/api/vlrf.h:32-41)
-#define VLRF_ERR_UNSUPPORTED 2
-#define VLRF_ERR_CUDA 3
-
-#define VLRF_F32 0
-#define VLRF_BF16 1
-
-#define VLRF_ACT_NONE 0
-#define VLRF_ACT_GELU_TANH 1
-#define VLRF_ACT_GELU_ERF 2
-
-// Bits of the device-side error word that kernels set instead of faulting.
-#define VLRF_DEVERR_TOKEN_RANGE 1     // a token id outside the vocabulary was clamped
-#define VLRF_DEVERR_POSITION_RANGE 2  // a position outside the table was clamped
-#define VLRF_DEVERR_NO_BLOCK 4        // a token's cache block was not mapped; the token was skipped
-#define VLRF_DEVERR_WAIT_TIMEOUT 8    // a bounded wait on a barrier gave up
+// Status codes (same numbering idea as the reference's status enum, include/api/vlrf.h:32-41), element types,
+// activations, the bits of the device-side error word that kernels set instead of faulting, and the prototype of
+// every exported function: the definitions in the .cu files are checked against them by the compiler.
+#include "vlrf_b200_kernels.h"
 
 extern "C" const char* vlrf_last_error();
 int vlrf_fail(int code, const char* fmt, ...);
