@@ -130,3 +130,74 @@ def test_an_error_in_a_step_gives_the_slots_back():
     with pytest.raises(RuntimeError, match="boom"):
         generate(b, [[1], [2]], greedy(5))
     assert sorted(b.free) == [0, 1, 2, 3]
+
+
+class HashBackend(ScriptedBackend):
+    """The next token is a function of everything the sequence has been fed so far (as with a real model), so a
+    token fed twice, skipped or given to the wrong row changes all that follows."""
+
+    def open_batch(self, requests):
+        h = super().open_batch(requests)
+        h["seen"] = [[] for _ in requests]
+        h["used_tokens"] = 0
+        return h
+
+    def run(self, h, rows, tokens):
+        assert len(set(rows)) == len(rows)
+        out = []
+        for r, t in zip(rows, tokens):
+            assert r in h["open"] and len(t) >= 1
+            h["seen"][r].extend(t)
+            assert len(h["seen"][r]) <= self.lim[3], "a sequence was fed beyond the model's positions"
+            out.append(next_token_of(h["seen"][r]))
+        held = sum((len(h["seen"][r]) + 63) // 64 * 64 for r in h["open"])
+        assert held <= self.lim[0], "the live sequences hold more tokens than the cache has"
+        return out
+
+
+def next_token_of(history):
+    x = 17
+    for t in history:
+        x = (x * 31 + t + 7) % 1009
+    return x % 50
+
+
+def alone(prompt, params, bos, eos, max_seq_len):
+    """What one request generates by the rules, computed without the loop."""
+    ids = list(prompt) if prompt else [bos]
+    stop = params.stop_token_ids if params.stop_token_ids is not None else (eos,)
+    new = []
+    if params.max_new_tokens == 0:
+        return new, "length"
+    if len(ids) >= max_seq_len:
+        return new, "context"
+    while True:
+        new.append(next_token_of(ids + new))
+        if new[-1] in stop:
+            return new, "stop"
+        if len(new) >= params.max_new_tokens:
+            return new, "length"
+        if len(ids) + len(new) >= max_seq_len:
+            return new, "context"
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_any_batching_gives_each_request_what_it_gets_alone(seed):
+    import random
+    rnd = random.Random(seed)
+    max_seq_len = rnd.choice([16, 40, 64])
+    n_slots = rnd.choice([1, 2, 3, 5, 8])
+    max_tokens = 64 * rnd.choice([n_slots, max(1, n_slots // 2), 2 * n_slots])
+    b = HashBackend(max_tokens=max_tokens, n_slots=n_slots, max_seq_len=max_seq_len)
+    prompts, params = [], []
+    for _ in range(rnd.randint(1, 14)):
+        prompts.append([rnd.randrange(50) for _ in range(rnd.choice([0, 1, 2, 5, 9, max_seq_len - 1, max_seq_len]))])
+        stop = rnd.choice([None, (), (3,), (1, 2, 3, 4, 5, 6, 7, 8, 9)])
+        params.append(SamplingParams(max_new_tokens=rnd.choice([0, 1, 2, 7, 30, 100]), do_sample=False, stop_token_ids=stop))
+    res = generate(b, prompts, params, bos_token_id=11, eos_token_id=4)
+    assert len(res) == len(prompts)
+    for p, sp, r in zip(prompts, params, res):
+        want_new, want_reason = alone(p, sp, 11, 4, max_seq_len)
+        assert (r.new_tokens, r.finish_reason) == (want_new, want_reason)
+        assert r.token_ids == (list(p) if p else [11]) + want_new
+    assert sorted(b.free) == list(range(n_slots))                   # every slot came back, none twice
