@@ -40,6 +40,19 @@ def test_init_takes_a_preset_name(tmp_path, capsys):
     assert json.loads((tmp_path / "a" / "config.json").read_text())["n_embd"] == 64
 
 
+def test_what_the_library_refuses_is_a_message_and_status_1(tmp_path, capsys):
+    from vlrf_b200.cli import main
+    assert main(["info", "--model", str(tmp_path / "nowhere")]) == 1
+    assert "cannot read" in capsys.readouterr().err
+    assert main(["init", "--config", "no-such-preset", "--out", str(tmp_path / "x")]) == 1
+    err = capsys.readouterr().err
+    assert "neither a preset" in err and "tiny-a" in err
+    bad = tmp_path / "cfg.json"
+    bad.write_text(json.dumps(dict(TINY_B, n_head=7)))              # 96 is no multiple of 7
+    assert main(["init", "--config", str(bad), "--out", str(tmp_path / "y")]) == 1
+    assert "n_head" in capsys.readouterr().err
+
+
 def test_prompts_from_text_ids_and_file(tmp_path):
     import argparse
 

@@ -104,7 +104,15 @@ def cmd_init(args) -> int:
     import vlrf_b200.models  # noqa: F401
     from .config import load_preset, preset_names
     from .weights import write_random_model
-    cfg = load_preset(args.config) if args.config in preset_names() else json.loads(Path(args.config).read_text())
+    if args.config in preset_names():
+        cfg = load_preset(args.config)
+    else:
+        try:
+            cfg = json.loads(Path(args.config).read_text())
+        except (OSError, ValueError) as exc:
+            from .config.base import ConfigError
+            raise ConfigError(f"--config {args.config}: neither a preset ({', '.join(sorted(preset_names()))}) "
+                              f"nor a readable config.json ({exc})") from exc
     out = write_random_model(cfg, args.seed, args.out)
     print(f"wrote {out}/config.json and {out}/model.safetensors (seed {args.seed})")
     return 0
@@ -120,7 +128,19 @@ def main(argv=None) -> int:
     pi.add_argument("--out", required=True)
     pi.add_argument("--seed", type=int, default=1234)
     args = ap.parse_args(argv)
-    return {"run": cmd_run, "info": cmd_info, "init": cmd_init}[args.command](args)
+    from .cache import CacheError
+    from .config.base import ConfigError
+    from .csrc import KernelError
+    from .engine.generate import GenerationError
+    from .engine.step import StepError
+    from .weights.safetensors_io import WeightError
+    try:
+        return {"run": cmd_run, "info": cmd_info, "init": cmd_init}[args.command](args)
+    except (ConfigError, WeightError, GenerationError, StepError, CacheError, KernelError) as exc:
+        # what the library itself refuses is a message and a status, as with the reference's CLI; anything else is a fault
+        # of the program and keeps its traceback
+        print(f"vlrf_b200 {args.command}: {exc}", file=sys.stderr)
+        return 1
 
 
 if __name__ == "__main__":
