@@ -5,7 +5,8 @@
 
 A step is one decode step of the whole batch: every sequence goes on by one token.  The default run has
 the layer sizes of the GPT-2 small configuration with random weights (seeded, synthetic token ids), a
-batch of 8 and a context of 1,024: the sequences start from 512-token prompts and decode towards 1,024.
+batch of 8 and a context of 1,024: the sequences start from 512-token prompts and decode to 1,024 (16 warm-up
+steps, then the 496 timed ones).
 One JSON line is printed:
 
   value      decoded tokens a second, K steps timed on the device with CUDA events after W warm-up steps;
@@ -284,7 +285,7 @@ def prefill_device(model_dir, dtype="bfloat16", reps=5, replay=True):
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--steps", type=int, default=496, help="decode steps to time (496 after 16 warm-up steps ends at position 1,024)")
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--preset", default="gpt2")
