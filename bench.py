@@ -46,17 +46,31 @@ FALLBACK_BF16_TFLOPS = 1590.0
 PROMPT_LEN = 512
 
 
-def peaks():
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+def peaks(root: str = ROOT):
+    """(HBM copy GB/s, bf16 TFLOP/s of a burst, "measured" | "fallback").  The measured file gives `hbm_gbs` and
+    `bf16_tflops` as numbers (a figure wrapped as {"value": x} is read too); anything else in it, or a file that
+    does not parse, leaves the fallback figure for that peak."""
+    path = os.path.join(root, "MEASURED_PEAKS.json")
     hbm, tf, src = FALLBACK_HBM_GBS, FALLBACK_BF16_TFLOPS, "fallback"
+
+    def number(v):
+        if isinstance(v, dict):
+            v = v.get("value")
+        if isinstance(v, (int, float)) and not isinstance(v, bool) and v > 0:
+            return float(v)
+        return None
+
     try:
         with open(path) as f:
             p = json.load(f)
-        hbm = float(p.get("hbm_gbs", hbm))
-        tf = float(p.get("bf16_tflops", tf))
-        src = "measured"
     except (OSError, ValueError):
-        pass
+        return hbm, tf, src
+    if isinstance(p, dict):
+        got_hbm, got_tf = number(p.get("hbm_gbs")), number(p.get("bf16_tflops"))
+        if got_hbm is not None:
+            hbm, src = got_hbm, "measured"
+        if got_tf is not None:
+            tf, src = got_tf, "measured"
     return hbm, tf, src
 
 
