@@ -14,7 +14,7 @@ import dataclasses
 import numpy as np
 import torch
 
-from ..cache import CacheError, SequenceCache
+from ..cache import SequenceCache
 from ..csrc import KernelError, library
 from .capture import capture_into
 from ..parts.context import StepContext, Workspace

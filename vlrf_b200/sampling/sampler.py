@@ -1,11 +1,9 @@
 """Choosing the next token of every row of logits on the device."""
 from __future__ import annotations
 
-import numpy as np
 import torch
 
 from ..csrc import ops
-from .params import SamplingParams
 from .rng import as_signed64
 
 
