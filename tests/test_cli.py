@@ -53,6 +53,16 @@ def test_what_the_library_refuses_is_a_message_and_status_1(tmp_path, capsys):
     assert "n_head" in capsys.readouterr().err
 
 
+def test_without_a_gpu_run_says_so(tmp_path, capsys):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("this machine has a GPU")
+    from vlrf_b200.cli import main
+    run_cli(["init", "--config", "tiny-a", "--out", str(tmp_path / "a")], capsys)
+    assert main(["run", "--model", str(tmp_path / "a"), "--prompt-ids", "1,2", "--tokens", "2", "--greedy"]) == 1
+    assert "no other execution path" in capsys.readouterr().err
+
+
 def test_prompts_from_text_ids_and_file(tmp_path):
     import argparse
 

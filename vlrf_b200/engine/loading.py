@@ -26,4 +26,8 @@ def load_model(model_dir, dtype="bfloat16", device="cuda:0") -> DecoderModel:
     import vlrf_b200.models  # noqa: F401  (registers the architectures)
     arch, cfg, weights = open_model_dir(model_dir)
     options = BuildOptions(dtype=parse_dtype(dtype), device=torch.device(device))
+    if options.device.type != "cuda" or not torch.cuda.is_available():
+        from ..csrc import KernelError
+        raise KernelError(f"cannot put a model on '{device}': the engine's kernels are CUDA code for sm_100a and there "
+                          f"is no other execution path (CUDA available: {torch.cuda.is_available()})")
     return arch.build(cfg, weights, options)
