@@ -68,6 +68,18 @@ _SIGNATURES = {
     "vlrf_attn_decode": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
                          _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int,
                          _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+    "vlrf_decode_program_op_bytes": [],
+    "vlrf_decode_program_max_rows": [],
+    "vlrf_decode_program_gemv_takes": [_c_int, _c_int, _c_int, _c_int, _c_int],
+    "vlrf_decode_program_attention_takes": [_c_int, _c_int],
+    "vlrf_decode_op_embed": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int],
+    "vlrf_decode_op_gemv": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_float,
+                            _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p,
+                            _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int],
+    "vlrf_decode_op_attention": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
+                                 _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void_p,
+                                 _c_void_p],
+    "vlrf_decode_program_run": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "vlrf_sample": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                     _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "vlrf_apply_penalties": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
@@ -113,6 +125,14 @@ def launch_count() -> int:
     """How many kernel entry points have been called so far (each launches one kernel unless it says
     otherwise); replays of a captured graph are counted by whoever replays it."""
     return _launches
+
+
+def call_host(name: str, *args) -> None:
+    """An entry point that only works on the host (it launches nothing, so it is not counted as a launch)."""
+    lib = library()
+    status = getattr(lib, name)(*args)
+    if status != 0:
+        raise KernelError(f"{name}: {lib.vlrf_last_error().decode('utf-8', 'replace')} (status {status})")
 
 
 def call(name: str, *args) -> None:

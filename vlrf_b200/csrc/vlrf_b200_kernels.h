@@ -173,6 +173,34 @@ int vlrf_sample(const float* logits, int ld, int n_rows, int V, const float* tem
 int vlrf_apply_penalties(float* logits, int ld, int n_rows, int V, const int* gen, int gen_ld, const int* gen_len,
                          const float* rep, const float* freq, const float* pres, const int* ngram, cudaStream_t stream);
 
+// ---- a whole decode step as one persistent kernel (decode_program.cu) ----------------------------------------
+// The step is a list of operations (embedding; few-row product with an optional norm of its input, bias, activation,
+// residual and cache scatter; attention of one query per row and head over the paged cache), filled on the HOST one
+// record at a time by the vlrf_decode_op_* functions into an array of vlrf_decode_program_op_bytes() bytes a record,
+// copied to the device by the caller, and run by vlrf_decode_program_run: one cooperative launch of one CTA per SM
+// whose CTAs meet at a grid barrier after every operation.  At most vlrf_decode_program_max_rows() rows; bfloat16
+// weights and caches.  norm: 0 none, 1 LayerNorm (beta may be null), 2 RMS norm.  The *_takes functions say
+// whether an operation's sizes are taken.
+int vlrf_decode_program_op_bytes();
+int vlrf_decode_program_max_rows();
+int vlrf_decode_program_gemv_takes(int n_rows, int N, int K, int in_f32, int norm);
+int vlrf_decode_program_attention_takes(int head_dim, int block_tokens);
+int vlrf_decode_op_embed(void* ops_host, int index, const void* wte, const void* wpe, const int* tokens, float* x, int d,
+                         int V, int P);
+int vlrf_decode_op_gemv(void* ops_host, int index, int n_rows, const void* in, int in_f32, int ld_in, int norm,
+                        const float* gamma, const float* beta, float eps, const void* W, const float* bias, int N, int K,
+                        int act, void* out, int out_f32, int ld_out, const float* residual, void* kc, void* vc,
+                        const int* block_table, int max_blocks, int k_off, int v_off, int Hkv, int dh, int BT);
+int vlrf_decode_op_attention(void* ops_host, int index, const void* qkv, int ld_qkv, int q_off, const void* kc,
+                             const void* vc, const int* block_table, int max_blocks, void* out, int ld_out, int H, int Hkv,
+                             int dh, int BT, float scale, int window, int n_split, float* partials, int* counters);
+// sync_words: 4 uint32 on the device, zero before the first launch (the kernel leaves them zero); launches that share
+// them, or scratch that the operations name, must not overlap.  trace: null, or int64 [n_ops + 1][8] on the device:
+// times (ns) of the CTA that sync_words[3] names: [op][0] it begins the operation ([n_ops][0]: it has finished the
+// last), [op][1…5] rows staged, first weights landed, products done, results stored, arrived at the barrier.
+int vlrf_decode_program_run(const void* ops_dev, int n_ops, int n_rows, const int* tok_slot, const int* tok_pos,
+                            void* sync_words, int* dev_err, long long* trace, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -10,14 +10,22 @@ from __future__ import annotations
 
 import torch
 
+import os
+
 from ..csrc import launch_count
 from .capture import capture_into
 from ..parts.context import StepContext, Workspace
 from .step import Engine
 
 
+#: Whether a session states its step as a decode program (one persistent kernel a step) where the model's parts
+#: allow it; off, or for models whose parts cannot, every operation is a launch of its own.
+USE_DECODE_PROGRAM = os.environ.get("VLRF_B200_DECODE_PROGRAM", "0") != "0"
+
+
 class DecodeSession:
-    def __init__(self, engine: Engine, slots: list, *, use_graph: bool = True, pad_to: int | None = None):
+    def __init__(self, engine: Engine, slots: list, *, use_graph: bool = True, pad_to: int | None = None,
+                 use_program: bool | None = None):
         self.engine, self.model = engine, engine.model
         self.slots = list(slots)
         self.n = len(slots)
@@ -40,6 +48,31 @@ class DecodeSession:
         self.logits = None
         self.kernels_per_step = 0
         self._sync_tables()
+        self.program = None
+        self.program_refused = None      # why the step is not a decode program, if it is not
+        if USE_DECODE_PROGRAM if use_program is None else use_program:
+            self._build_program()
+
+    def _build_program(self) -> None:
+        from ..parts.program import DecodeProgram, NotFusable
+        try:
+            if not self.model.replayable:
+                raise NotFusable("a part of the model decides on the host what to launch")
+            program = DecodeProgram(n_rows=self.rows, tokens=self.tokens, tok_slot=self.tok_slot, tok_pos=self.tok_pos,
+                                    dev_err=self.engine.dev_err, ws=self.ws, act_dtype=self.model.act_dtype,
+                                    max_context=self.model.max_seq_len)
+            self._program_logits = self.model.emit_decode(program, self.engine.cache)
+            program.finalize()
+            self.program = program
+        except NotFusable as why:
+            self.program_refused = str(why)
+
+    def _run_model(self) -> torch.Tensor:
+        """The model on this step's rows: one launch of the decode program where there is one."""
+        if self.program is not None:
+            self.program.run()
+            return self._program_logits
+        return self.model.forward(self._context(), self.engine.cache)
 
     def _sync_tables(self) -> None:
         c = self.engine.cache
@@ -81,7 +114,7 @@ class DecodeSession:
         def run():
             if before is not None:
                 before()
-            logits = self.model.forward(self._context(), c)
+            logits = self._run_model()
             sample(logits)
             if after is not None:
                 after()
@@ -151,19 +184,19 @@ class DecodeSession:
         if self.use_graph and self.graph is None:
             # a warm-up run sizes the workspace; the capture then sees stable addresses
             before = launch_count()
-            self.logits = self.model.forward(self._context(), c)
+            self.logits = self._run_model()
             self.kernels_per_step = launch_count() - before
             torch.cuda.synchronize()
             self.ws.frozen = True
             g = torch.cuda.CUDAGraph()
             with capture_into(g):
-                self.logits = self.model.forward(self._context(), c)
+                self.logits = self._run_model()
             self.graph = g
         if self.use_graph:
             self.graph.replay()
         else:
             before = launch_count()
-            self.logits = self.model.forward(self._context(), c)
+            self.logits = self._run_model()
             self.kernels_per_step = launch_count() - before
         if advance_on_device:
             self.tok_pos.add_(self.one * (self.tok_slot >= 0))

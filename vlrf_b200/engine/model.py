@@ -87,6 +87,26 @@ class DecoderModel:
             visit(part)
         return total
 
+    def emit_decode(self, program, cache) -> torch.Tensor:
+        """The same forward pass for a decode step (one token a row, logits for every row), written down as the
+        operations of a decode program (`parts.program.DecodeProgram`) instead of being launched.  Returns the
+        float32 logits tensor [rows, vocab] that running the program fills.  Raises `NotFusable` if a part cannot
+        state its step that way; the step then runs through `forward` as always."""
+        from ..parts.program import NotFusable
+        rows = program.n_rows
+        for part in (self.embedding, self.head, *self.layers):
+            if not hasattr(part, "emit_decode"):
+                raise NotFusable(f"{type(part).__name__} has no emit_decode")
+        x = program.scratch("residual", rows, self.width, torch.float32)
+        self.embedding.emit_decode(program, x)
+        for i, call in enumerate(self.schedule):
+            owner = i if call.reads_cache_of is None else call.reads_cache_of
+            view = cache.view(owner) if cache.needs[owner] is not None else None
+            self.layers[call.layer].emit_decode(program, x, view, writes_cache=call.reads_cache_of is None)
+        logits = program.scratch("logits", rows, self.vocab_size, torch.float32)
+        self.head.emit_decode(program, x, self.final_norm, logits)
+        return logits
+
     def forward(self, ctx: StepContext, cache) -> torch.Tensor:
         """Run the tokens of `ctx` through all scheduled layers; returns float32 logits
         [ctx.n_logit_rows, vocab] for the rows in ctx.logit_rows

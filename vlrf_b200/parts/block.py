@@ -18,6 +18,16 @@ class PreNormBlock:
     def cache_need(self):
         return self.mixer.cache_need()
 
+    def emit_decode(self, program, x: torch.Tensor, view, writes_cache: bool = True) -> None:
+        """This block's decode step as operations of a decode program: possible when the mixer and the
+        feed-forward can state theirs (they get the norm to fuse, as in `forward`)."""
+        from .program import NotFusable
+        for part in (self.mixer, self.feed_forward):
+            if not hasattr(part, "emit_decode"):
+                raise NotFusable(f"{type(part).__name__} has no emit_decode")
+        self.mixer.emit_decode(program, x, self.norm1, view, writes_cache)
+        self.feed_forward.emit_decode(program, x, self.norm2)
+
     def forward(self, x: torch.Tensor, ctx: StepContext, view, writes_cache: bool = True) -> None:
         if getattr(self.mixer, "fuses_norm", False):
             self.mixer.forward(None, x, ctx, view, writes_cache, norm=self.norm1)

@@ -21,6 +21,9 @@ class TokenEmbedding:
         else:
             self.position = None
 
+    def emit_decode(self, program, x: torch.Tensor) -> None:
+        program.embed(self.weight, self.position.table if self.position is not None else None, x)
+
     def __call__(self, ctx: StepContext, x: torch.Tensor) -> torch.Tensor:
         table = self.position.table if self.position is not None else None
         ops.embed(self.weight, table, ctx.tokens, ctx.tok_pos if table is not None else None, x, ctx.dev_err)
@@ -34,6 +37,11 @@ class LMHead:
     def __init__(self, weight: torch.Tensor):
         self.weight = weight
         self.vocab_size, self.width = weight.shape
+
+    def emit_decode(self, program, x: torch.Tensor, norm, logits: torch.Tensor) -> None:
+        """logits = norm(x) · weightᵀ for every row of the program."""
+        from .program import norm_terms
+        program.product(x, self.weight, None, logits, norm=norm_terms(norm))
 
     def __call__(self, h: torch.Tensor, logits: torch.Tensor, n_rows: int) -> torch.Tensor:
         ops.linear(h, self.weight, None, logits, rows=n_rows)

@@ -33,10 +33,17 @@ class DenseMLP:
     #: the block may hand over its norm instead of normed rows: forward(None, x, ctx, norm=…)
     fuses_norm = True
 
+    def emit_decode(self, program, x: torch.Tensor, norm) -> None:
+        """The decode step of this part as two operations of a decode program."""
+        from .program import norm_terms
+        u = program.scratch("ffn_inner", program.n_rows, self.inner, program.act_dtype)
+        program.product(x, self.w_in, self.b_in, u, norm=norm_terms(norm), act=self.activation)
+        program.product(u, self.w_out, self.b_out, x, residual=x)
+
     def forward(self, h, x: torch.Tensor, ctx: StepContext, norm=None) -> None:
         T = ctx.n_tokens
         u = ctx.ws.get("ffn_inner", T, self.inner, ctx.act_dtype)
-        if h is None and ops.can_fuse_layernorm(T, x.shape[1], self.w_in.dtype) and hasattr(norm, "eps"):
+        if h is None and getattr(norm, "fusable_as", None) == "layernorm" and ops.can_fuse_layernorm(T, x.shape[1], self.w_in.dtype):
             ops.linear_layernorm(x, norm.weight, norm.bias, norm.eps, self.w_in, self.b_in, u, act=self.activation)
         else:
             if h is None:

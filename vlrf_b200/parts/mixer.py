@@ -66,7 +66,7 @@ class CausalSelfAttention:
         T = ctx.n_tokens
         qkv = ctx.ws.get("attn_qkv", T, self.qkv_width, ctx.act_dtype)
         appended = False
-        if h is None and ops.can_fuse_layernorm(T, x.shape[1], self.w_qkv.dtype) and hasattr(norm, "eps"):
+        if h is None and getattr(norm, "fusable_as", None) == "layernorm" and ops.can_fuse_layernorm(T, x.shape[1], self.w_qkv.dtype):
             # few rows: norm, projection and the cache write in one kernel
             scatter = None
             if writes_cache:
@@ -88,6 +88,20 @@ class CausalSelfAttention:
         merged = ctx.ws.get("attn_out", T, self.n_heads * self.head_dim, ctx.act_dtype)
         self._attend(qkv, view, merged, ctx)
         ops.linear(merged, self.w_out, self.b_out, x, residual=x)
+
+    def emit_decode(self, program, x: torch.Tensor, norm, view, writes_cache: bool = True) -> None:
+        """The decode step of this mixer as operations of a decode program: norm + q/k/v projection (+ cache
+        write), attention over the cache, output projection + residual."""
+        from .program import norm_terms
+        rows = program.n_rows
+        qkv = program.scratch("attn_qkv", rows, self.qkv_width, program.act_dtype)
+        merged = program.scratch("attn_out", rows, self.n_heads * self.head_dim, program.act_dtype)
+        scatter = (view.k, view.v, view.block_table, self.k_off, self.v_off, self.n_kv_heads, self.head_dim) \
+            if writes_cache else None
+        program.product(x, self.w_qkv, self.b_qkv, qkv, norm=norm_terms(norm), kv_scatter=scatter)
+        program.attention(qkv, self.q_off, view.k, view.v, view.block_table, merged, n_heads=self.n_heads,
+                          n_kv_heads=self.n_kv_heads, head_dim=self.head_dim, scale=self.scale, window=self.window)
+        program.product(merged, self.w_out, self.b_out, x, residual=x)
 
     def _attend(self, qkv, view, merged, ctx: StepContext) -> None:
         T = ctx.n_tokens

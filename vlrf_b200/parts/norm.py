@@ -12,6 +12,10 @@ class LayerNorm:
     """y = (x − mean)·(1/sqrt(var + eps))·weight + bias over the last axis, biased variance, statistics
     in float32 (reference: include/model/ops.hpp:443-476)."""
 
+    #: what a product kernel may compute in its own prologue instead of calling this norm: a mixer or feed-forward
+    #: that is handed the norm looks here (and at weight / bias / eps), never at the class
+    fusable_as = "layernorm"
+
     def __init__(self, weight: torch.Tensor, bias: torch.Tensor, eps: float):
         if weight.shape != bias.shape or weight.dim() != 1:
             raise ValueError("LayerNorm: weight and bias are vectors of one length")
