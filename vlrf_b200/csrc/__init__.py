@@ -70,15 +70,17 @@ _SIGNATURES = {
                          _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "vlrf_decode_program_op_bytes": [],
     "vlrf_decode_program_max_rows": [],
-    "vlrf_decode_program_gemv_takes": [_c_int, _c_int, _c_int, _c_int, _c_int],
+    "vlrf_decode_program_gemv_takes": [_c_int, _c_int, _c_int, _c_int, _c_int, _c_int],
     "vlrf_decode_program_attention_takes": [_c_int, _c_int],
-    "vlrf_decode_op_embed": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int],
-    "vlrf_decode_op_gemv": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_float,
-                            _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p,
-                            _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int],
-    "vlrf_decode_op_attention": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
-                                 _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void_p,
-                                 _c_void_p],
+    "vlrf_decode_op_embed": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
+                             _c_int],
+    "vlrf_decode_op_gemv": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
+                            _c_void_p, _c_float, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int,
+                            _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
+                            _c_int, _c_int, _c_int],
+    "vlrf_decode_op_attention": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                 _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                 _c_int, _c_float, _c_int, _c_int, _c_void_p, _c_void_p],
     "vlrf_decode_program_run": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "vlrf_sample": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                     _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],

@@ -177,27 +177,36 @@ int vlrf_apply_penalties(float* logits, int ld, int n_rows, int V, const int* ge
 // The step is a list of operations (embedding; few-row product with an optional norm of its input, bias, activation,
 // residual and cache scatter; attention of one query per row and head over the paged cache), filled on the HOST one
 // record at a time by the vlrf_decode_op_* functions into an array of vlrf_decode_program_op_bytes() bytes a record,
-// copied to the device by the caller, and run by vlrf_decode_program_run: one cooperative launch of one CTA per SM
-// whose CTAs meet at a grid barrier after every operation.  At most vlrf_decode_program_max_rows() rows; bfloat16
-// weights and caches.  norm: 0 none, 1 LayerNorm (beta may be null), 2 RMS norm.  The *_takes functions say
-// whether an operation's sizes are taken.
+// copied to the device by the caller, and run by vlrf_decode_program_run: one cooperative launch of one CTA per SM.
+// At most vlrf_decode_program_max_rows() rows; bfloat16 weights and caches.  norm: 0 none, 1 LayerNorm (beta may be
+// null), 2 RMS norm.  Buffers between operations have a format: 0 float32 rows, 1 bfloat16 rows (`ld` elements a
+// row), or flagged rows, 2: groups of 16 bytes holding 3 float32 and a flag, 3: 6 bfloat16 and a flag (`ld` groups a
+// row; `seg` > 0 cuts a row's columns into segments that each begin a new group; zero-filled before first use).
+// An operation that reads a flagged buffer waits, group by group, for the flag of the operation `dep` (its index in
+// the list) that writes it in the same launch; there is no other ordering between operations, so plain buffers must
+// be complete before the launch, and a flagged buffer may be rewritten only by an operation that cannot begin before
+// every reader of the old contents has finished.  The *_takes functions say whether an operation's sizes are taken.
 int vlrf_decode_program_op_bytes();
 int vlrf_decode_program_max_rows();
-int vlrf_decode_program_gemv_takes(int n_rows, int N, int K, int in_f32, int norm);
+int vlrf_decode_program_gemv_takes(int n_rows, int N, int K, int in_fmt, int out_fmt, int norm);
 int vlrf_decode_program_attention_takes(int head_dim, int block_tokens);
-int vlrf_decode_op_embed(void* ops_host, int index, const void* wte, const void* wpe, const int* tokens, float* x, int d,
-                         int V, int P);
-int vlrf_decode_op_gemv(void* ops_host, int index, int n_rows, const void* in, int in_f32, int ld_in, int norm,
-                        const float* gamma, const float* beta, float eps, const void* W, const float* bias, int N, int K,
-                        int act, void* out, int out_f32, int ld_out, const float* residual, void* kc, void* vc,
-                        const int* block_table, int max_blocks, int k_off, int v_off, int Hkv, int dh, int BT);
-int vlrf_decode_op_attention(void* ops_host, int index, const void* qkv, int ld_qkv, int q_off, const void* kc,
-                             const void* vc, const int* block_table, int max_blocks, void* out, int ld_out, int H, int Hkv,
-                             int dh, int BT, float scale, int window, int n_split, float* partials, int* counters);
-// sync_words: 4 uint32 on the device, zero before the first launch (the kernel leaves them zero); launches that share
-// them, or scratch that the operations name, must not overlap.  trace: null, or int64 [n_ops + 1][8] on the device:
-// times (ns) of the CTA that sync_words[3] names: [op][0] it begins the operation ([n_ops][0]: it has finished the
-// last), [op][1…5] rows staged, first weights landed, products done, results stored, arrived at the barrier.
+int vlrf_decode_op_embed(void* ops_host, int index, const void* wte, const void* wpe, const int* tokens, void* x, int x_fmt,
+                         int x_ld, int d, int V, int P);
+int vlrf_decode_op_gemv(void* ops_host, int index, int n_rows, const void* in, int in_fmt, int in_ld, int in_seg, int in_dep,
+                        int norm, const float* gamma, const float* beta, float eps, const void* W, const float* bias, int N,
+                        int K, int act, void* out, int out_fmt, int out_ld, const void* residual, int res_fmt, int res_ld,
+                        int res_dep, void* kc, void* vc, const int* block_table, int max_blocks, int k_off, int v_off, int Hkv,
+                        int dh, int BT);
+// With a flagged q/k/v buffer the newest key and value are read from it (columns k_off, v_off) and the cache up to the
+// position before; with a plain one the cache holds every key.  A flagged output has one segment a head.
+int vlrf_decode_op_attention(void* ops_host, int index, const void* qkv, int qkv_fmt, int qkv_ld, int qkv_dep, int qkv_cols,
+                             int q_off, int k_off, int v_off, const void* kc, const void* vc, const int* block_table,
+                             int max_blocks, void* out, int out_fmt, int out_ld, int H, int Hkv, int dh, int BT, float scale,
+                             int window, int n_split, float* partials, int* counters);
+// sync_words: 4 uint32 on the device, zero before the first launch; [0] counts the launches (flags are made from it, so
+// flagged buffers belong to one sync_words).  Launches that share them, or buffers that the operations name, must not
+// overlap.  trace: null, or int64 [SMs][n_ops + 1][8] on the device: times (ns), [cta][op][0] the CTA begins the
+// operation ([cta][n_ops][0]: it has finished the last), [cta][op][1…4] stages inside it (0: no share of it).
 int vlrf_decode_program_run(const void* ops_dev, int n_ops, int n_rows, const int* tok_slot, const int* tok_pos,
                             void* sync_words, int* dev_err, long long* trace, cudaStream_t stream);
 

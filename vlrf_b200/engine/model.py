@@ -103,7 +103,7 @@ class DecoderModel:
             owner = i if call.reads_cache_of is None else call.reads_cache_of
             view = cache.view(owner) if cache.needs[owner] is not None else None
             self.layers[call.layer].emit_decode(program, x, view, writes_cache=call.reads_cache_of is None)
-        logits = program.scratch("logits", rows, self.vocab_size, torch.float32)
+        logits = program.plain("logits", rows, self.vocab_size, torch.float32)
         self.head.emit_decode(program, x, self.final_norm, logits)
         return logits
 

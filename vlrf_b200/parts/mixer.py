@@ -95,11 +95,11 @@ class CausalSelfAttention:
         from .program import norm_terms
         rows = program.n_rows
         qkv = program.scratch("attn_qkv", rows, self.qkv_width, program.act_dtype)
-        merged = program.scratch("attn_out", rows, self.n_heads * self.head_dim, program.act_dtype)
+        merged = program.scratch("attn_out", rows, self.n_heads * self.head_dim, program.act_dtype, seg=self.head_dim)
         scatter = (view.k, view.v, view.block_table, self.k_off, self.v_off, self.n_kv_heads, self.head_dim) \
             if writes_cache else None
         program.product(x, self.w_qkv, self.b_qkv, qkv, norm=norm_terms(norm), kv_scatter=scatter)
-        program.attention(qkv, self.q_off, view.k, view.v, view.block_table, merged, n_heads=self.n_heads,
+        program.attention(qkv, self.q_off, self.k_off, self.v_off, view.k, view.v, view.block_table, merged, n_heads=self.n_heads,
                           n_kv_heads=self.n_kv_heads, head_dim=self.head_dim, scale=self.scale, window=self.window)
         program.product(merged, self.w_out, self.b_out, x, residual=x)
 
