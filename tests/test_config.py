@@ -53,6 +53,8 @@ def test_sizes_are_required_not_defaulted(key):
 
 @pytest.mark.parametrize("patch,match", [
     (dict(n_embd=65), "multiple of n_head"),
+    (dict(n_embd=120, n_head=12), "multiples of 16"),        # head size 10: refused here, not inside the first step
+    (dict(n_embd=544, n_head=2), "multiples of 16 up to 256"),
     (dict(n_layer=0), "positive"),
     (dict(vocab_size=-1), "positive"),
     (dict(activation_function="relu"), "activation_function"),

@@ -209,10 +209,11 @@ def test_split_k_layernorm_from_row_statistics(split_k_always, M, N, K, out_dtyp
     deviation from the mean."""
     ops = split_k_always
     eps = 1e-5
+    stats = ops.RowStats(DEV)
     w0, x0 = randn(K, 64, seed=41, dtype=torch.bfloat16), randn(M, 64, seed=42, dtype=torch.bfloat16)
     x = (randn(M, K, seed=43) * 0.5 + 300.0).to(DEV)             # mean 300, deviation about 8
-    ops.linear(x0.to(DEV), w0.to(DEV), None, x, residual=x)
-    assert ops._row_stats_of(x, M, K) is not None
+    ops.linear(x0.to(DEV), w0.to(DEV), None, x, residual=x, stats=stats)
+    assert stats.describing(x, M, K) is not None
     gamma, beta = randn(K, seed=44) * 0.3 + 1, randn(K, seed=45) * 0.2
     w, b = randn(N, K, seed=46, dtype=torch.bfloat16, scale=0.2), randn(N, seed=47)
 
@@ -223,26 +224,30 @@ def test_split_k_layernorm_from_row_statistics(split_k_always, M, N, K, out_dtyp
 
     tol = 6e-3 if out_dtype == torch.bfloat16 else 3e-3
     out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
-    ops.linear_layernorm(x, gamma.to(DEV), beta.to(DEV), eps, w.to(DEV), b.to(DEV), out, act=act)
+    ops.linear_layernorm(x, gamma.to(DEV), beta.to(DEV), eps, w.to(DEV), b.to(DEV), out, act=act, stats=stats)
     assert rel_err(out.float().cpu(), want_for(x)) < tol
     # rows changed behind the statistics' back: by torch in place, by a kernel of this library, by a caller's own
     x.mul_(0.5)
-    assert ops._row_stats_of(x, M, K) is None
+    assert stats.describing(x, M, K) is None
     if ops.can_fuse_layernorm(M, K, torch.bfloat16):             # (the kernel that reads whole rows takes this width)
-        ops.linear_layernorm(x, gamma.to(DEV), beta.to(DEV), eps, w.to(DEV), b.to(DEV), out, act=act)
+        ops.linear_layernorm(x, gamma.to(DEV), beta.to(DEV), eps, w.to(DEV), b.to(DEV), out, act=act, stats=stats)
         assert rel_err(out.float().cpu(), want_for(x)) < tol
-    ops.linear(x0.to(DEV), w0.to(DEV), None, x, residual=x)
-    assert ops._row_stats_of(x, M, K) is not None
+    ops.linear(x0.to(DEV), w0.to(DEV), None, x, residual=x, stats=stats)
+    assert stats.describing(x, M, K) is not None
     # the embedding leaves statistics of the rows it writes, too
     table = (randn(50, K, seed=48) * 3 + 20).to(DEV)
     ops.embed(table, None, torch.arange(M, dtype=torch.int32, device=DEV) * 3, None, x,
-              torch.zeros(1, dtype=torch.int32, device=DEV))
-    assert ops._row_stats_of(x, M, K) is not None
-    ops.linear_layernorm(x, gamma.to(DEV), beta.to(DEV), eps, w.to(DEV), b.to(DEV), out, act=act)
+              torch.zeros(1, dtype=torch.int32, device=DEV), stats=stats)
+    assert stats.describing(x, M, K) is not None
+    ops.linear_layernorm(x, gamma.to(DEV), beta.to(DEV), eps, w.to(DEV), b.to(DEV), out, act=act, stats=stats)
     assert rel_err(out.float().cpu(), want_for(x)) < tol
+    # a product that is handed no statistics keeps none, and one that rewrites the rows without them forgets them
+    ops.linear(x0.to(DEV), w0.to(DEV), None, x, residual=x, stats=stats)
+    stats.forget()
+    assert stats.describing(x, M, K) is None
+    other = ops.RowStats(DEV)
     ops.linear(x0.to(DEV), w0.to(DEV), None, x, residual=x)
-    ops.residual_written(x)
-    assert ops._row_stats_of(x, M, K) is None
+    assert other.describing(x, M, K) is None
     assert ops.device_errors() == 0
 
 
@@ -261,11 +266,12 @@ def test_split_k_projection_writes_keys_and_values_into_the_cache(split_k_always
         out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
         if fused_norm:
             x = torch.zeros(M, K, device=DEV)
+            stats = ops.RowStats(DEV)
             ops.linear(randn(M, 64, seed=54, dtype=torch.bfloat16).to(DEV), randn(K, 64, seed=55, dtype=torch.bfloat16).to(DEV),
-                       None, x)
-            assert ops._row_stats_of(x, M, K) is not None
+                       None, x, stats=stats)
+            assert stats.describing(x, M, K) is not None
             ops.linear_layernorm(x, torch.ones(K, device=DEV), torch.zeros(K, device=DEV), 1e-5, w.to(DEV), b.to(DEV), out,
-                                 kv_scatter=scatter)
+                                 kv_scatter=scatter, stats=stats)
         else:
             assert ops.linear(randn(M, K, seed=51, dtype=torch.bfloat16).to(DEV), w.to(DEV), b.to(DEV), out, kv_scatter=scatter)
         o = out.cpu()

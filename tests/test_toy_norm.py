@@ -1,0 +1,196 @@
+"""Two promises of the part interfaces, each held by toys defined here and never shipped.
+
+1. A norm says what it may be fused as (`fusable_as`); nothing guesses from its attributes.  A toy RMS norm that
+   has a weight and an eps but no bias comes out right whether it says nothing (the library's mixer and feed-forward
+   then call it) or says "rmsnorm" (a decode program then norms inside its products).
+2. What the step knows about the residual rows (their statistics, which a fused LayerNorm trusts) cannot be left
+   stale by a part that has never heard of it: a toy feed-forward rewrites the rows with a raw kernel call and
+   tells nobody, between two library layers whose fused norms would otherwise use the old statistics.
+"""
+import dataclasses
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+HEADS = 2
+
+
+def define_toys():
+    from vlrf_b200.config import ModelConfig, key
+    from vlrf_b200.csrc import ops
+    from vlrf_b200.engine.model import DecoderModel, LayerCall
+    from vlrf_b200.parts import LayerNorm, LMHead, PreNormBlock, TokenEmbedding, get_part, register_part
+    from vlrf_b200.registry import Architecture, register_architecture
+    from vlrf_b200.weights.spec import TensorSpec, place
+
+    @register_part("norm", "toy_rms", replace=True)
+    class ToyRMSNorm:
+        """y = x / sqrt(mean(x²) + eps) · weight, in torch.  No bias; no mean is subtracted."""
+
+        def __init__(self, weight, eps, fusable_as=None):
+            self.weight, self.eps = weight, float(eps)
+            if fusable_as is not None:
+                self.fusable_as = fusable_as
+
+        def __call__(self, x, out, rows=None):
+            src = x if rows is None else x[rows.long()]
+            y = src * torch.rsqrt((src * src).mean(-1, keepdim=True) + self.eps) * self.weight
+            out[:y.shape[0]].copy_(y)
+            return out
+
+    @register_part("feed_forward", "toy_silent", replace=True)
+    class ToySilentFeedForward:
+        """x += gelu(h·W_inᵀ)·W_outᵀ through the library's kernels, handed no row statistics and declaring nothing."""
+
+        def __init__(self, w_in, w_out):
+            self.w_in, self.w_out = w_in, w_out
+
+        def forward(self, h, x, ctx):
+            T = ctx.n_tokens
+            u = torch.empty(T, self.w_in.shape[0], dtype=h.dtype, device=h.device)
+            ops.linear(h, self.w_in, None, u, act="gelu_tanh")
+            ops.linear(u, self.w_out, None, x, residual=x)            # rewrites the residual rows; tells nobody
+
+    @dataclasses.dataclass
+    class ToyNormConfig(ModelConfig):
+        model_type = "toy_norm"
+        vocab_size: int = key()
+        width: int = key()
+        max_len: int = key()
+        eps: float = key()
+        norm: str = key()              # "rms" | "rms_fusable" | "layer"
+        silent_layers: str = key()     # indices of layers whose feed-forward is the silent toy, e.g. "0,2"
+        n_layers: int = key()
+
+    def spec(cfg):
+        d = cfg.width
+        s = [TensorSpec("emb", (cfg.vocab_size, d)), TensorSpec("nf", (d,), "vector")]
+        for i in range(cfg.n_layers):
+            s += [TensorSpec(f"l{i}.n1", (d,), "vector"), TensorSpec(f"l{i}.n2", (d,), "vector"),
+                  TensorSpec(f"l{i}.qkv", (3 * d, d)), TensorSpec(f"l{i}.out", (d, d)),
+                  TensorSpec(f"l{i}.ffn_in", (2 * d, d)), TensorSpec(f"l{i}.ffn_out", (d, 2 * d))]
+        return s
+
+    def rand(cfg, gen):
+        return {t.name: (1.0 if ".n" in t.name or t.name == "nf" else 0.0) + 0.25 * torch.randn(t.shape, generator=gen)
+                for t in spec(cfg)}
+
+    def build(cfg, weights, options):
+        dt, dev = options.dtype, options.device
+        m = lambda n: place(weights[n], "matrix", dt, dev)   # noqa: E731
+        v = lambda n: place(weights[n], "vector", dt, dev)   # noqa: E731
+        zeros = lambda n: torch.zeros(n, device=dev)         # noqa: E731
+        d = cfg.width
+
+        def norm(name):
+            if cfg.norm == "layer":
+                return LayerNorm(v(name), zeros(d), cfg.eps)
+            return get_part("norm", "toy_rms")(v(name), cfg.eps, "rmsnorm" if cfg.norm == "rms_fusable" else None)
+
+        silent = {int(i) for i in cfg.silent_layers.split(",") if i}
+        emb = m("emb")
+        layers = []
+        for i in range(cfg.n_layers):
+            mixer = get_part("mixer", "causal_self_attention")(m(f"l{i}.qkv"), zeros(3 * d), m(f"l{i}.out"), zeros(d),
+                                                               n_heads=HEADS, n_kv_heads=HEADS, head_dim=d // HEADS,
+                                                               scale=1.0 / math.sqrt(d // HEADS))
+            if i in silent:
+                feed = get_part("feed_forward", "toy_silent")(m(f"l{i}.ffn_in"), m(f"l{i}.ffn_out"))
+            else:
+                feed = get_part("feed_forward", "dense_mlp")(m(f"l{i}.ffn_in"), zeros(2 * d), m(f"l{i}.ffn_out"), zeros(d),
+                                                             activation="gelu_tanh")
+            layers.append(PreNormBlock(norm(f"l{i}.n1"), mixer, norm(f"l{i}.n2"), feed))
+        return DecoderModel(config=cfg, embedding=TokenEmbedding(emb), layers=layers,
+                            schedule=[LayerCall(i) for i in range(len(layers))], final_norm=norm("nf"),
+                            head=LMHead(emb), options=options, max_seq_len=cfg.max_len)
+
+    register_architecture(Architecture("toy_norm", ToyNormConfig, spec, rand, build), replace=True)
+
+
+def toy_truth(cfg, w, ids):
+    import plain_gpt2 as plain
+    W = {k: v.double() for k, v in w.items()}
+    d = cfg["width"]
+    zeros = torch.zeros(d, dtype=torch.float64)
+
+    def norm(x, g):
+        if cfg["norm"] == "layer":
+            return plain.layer_norm(x, g, zeros, cfg["eps"])
+        return x / torch.sqrt((x * x).mean(-1, keepdim=True) + cfg["eps"]) * g
+
+    x = W["emb"][torch.tensor(ids)]
+    for i in range(cfg["n_layers"]):
+        h = norm(x, W[f"l{i}.n1"])
+        q, k, v = (plain.split_heads(t, HEADS) for t in plain.split_qkv(h @ W[f"l{i}.qkv"].T, d))
+        x = x + plain.merge_heads(plain.causal_attention(q, k, v, 1.0 / math.sqrt(d // HEADS))) @ W[f"l{i}.out"].T
+        h = norm(x, W[f"l{i}.n2"])
+        x = x + plain.gelu_tanh(h @ W[f"l{i}.ffn_in"].T) @ W[f"l{i}.ffn_out"].T
+    return norm(x, W["nf"]) @ W["emb"].T
+
+
+def decode_and_compare(model, cfg, w, reqs, starts, tol, use_program):
+    """A prompt step, then a decode session of all requests to their ends; every step's logits against the toy's truth."""
+    from conftest import rel_err
+    from vlrf_b200.engine import Engine, StepEntry
+    from vlrf_b200.engine.decode import DecodeSession
+    truth = [toy_truth(cfg, w, ids) for ids in reqs]
+    eng = Engine(model, max_tokens=512)
+    slots = [eng.start_sequence() for _ in reqs]
+    got = eng.step([StepEntry(s, r[:n], [n - 1]) for s, r, n in zip(slots, reqs, starts)]).float().cpu()
+    for i, n in enumerate(starts):
+        assert rel_err(got[i], truth[i][n - 1]) < tol, ("prompt", i)
+    sess = DecodeSession(eng, slots, use_graph=False, use_program=use_program)
+    at = list(starts)
+    while any(p < len(r) for p, r in zip(at, reqs)):
+        sess.set_tokens([r[min(p, len(r) - 1)] for r, p in zip(reqs, at)])
+        lg = sess.step().float().cpu()
+        for i, r in enumerate(reqs):
+            if at[i] < len(r):
+                assert rel_err(lg[i], truth[i][at[i]]) < tol, (i, at[i])
+                at[i] += 1
+                if at[i] == len(r):
+                    sess.end_row(i)
+    eng.check_device_errors()
+    return sess
+
+
+@pytest.mark.parametrize("norm,dtype,tol", [("rms", "float32", 1e-4), ("rms", "bfloat16", 3e-2), ("rms_fusable", "bfloat16", 3e-2)])
+def test_a_norm_that_is_no_layernorm_is_never_computed_as_one(tmp_path, norm, dtype, tol):
+    import plain_gpt2 as plain
+    from conftest import random_ids
+    from vlrf_b200.engine import load_model
+    from vlrf_b200.weights import write_random_model
+    define_toys()
+    cfg = dict(model_type="toy_norm", vocab_size=90, width=64, max_len=96, eps=1e-5, norm=norm, silent_layers="", n_layers=2)
+    d = write_random_model(cfg, 8, tmp_path / "toy_norm", dtype=torch.float32)
+    _, w = plain.read_model_dir(d)
+    model = load_model(d, dtype)
+    reqs = [random_ids(90, n, 70 + n) for n in (40, 12, 25)]
+    # rows with a large common offset would show a mean that was subtracted by mistake: the embedding has one
+    sess = decode_and_compare(model, cfg, w, reqs, [20, 3, 9], tol, use_program=False)
+    assert sess.program is None
+    if norm == "rms_fusable":
+        sess = decode_and_compare(model, cfg, w, reqs, [20, 3, 9], tol, use_program=True)
+        assert sess.program is not None, sess.program_refused       # the RMS norm ran inside the program's products
+
+
+def test_a_part_that_rewrites_the_residual_silently_leaves_no_stale_statistics(tmp_path):
+    import plain_gpt2 as plain
+    from conftest import random_ids
+    from vlrf_b200.engine import load_model
+    from vlrf_b200.weights import write_random_model
+    define_toys()
+    cfg = dict(model_type="toy_norm", vocab_size=90, width=64, max_len=96, eps=1e-5, norm="layer", silent_layers="0,2", n_layers=4)
+    d = write_random_model(cfg, 9, tmp_path / "toy_silent", dtype=torch.float32)
+    _, w = plain.read_model_dir(d)
+    model = load_model(d, "bfloat16")
+    assert [type(layer.feed_forward).__name__ for layer in model.layers] == \
+        ["ToySilentFeedForward", "DenseMLP", "ToySilentFeedForward", "DenseMLP"]
+    reqs = [random_ids(90, n, 80 + n) for n in (30, 11, 22, 17)]
+    sess = decode_and_compare(model, cfg, w, reqs, [10, 2, 8, 5], 3e-2, use_program=False)
+    assert sess.program is None
+    # the library's own layers do leave statistics, and the fused norm after them uses them
+    assert model.layers[1].leaves_row_stats and not model.layers[0].leaves_row_stats

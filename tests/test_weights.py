@@ -133,3 +133,35 @@ def test_check_tensors_types():
         check_tensors({"t": torch.zeros(2), "w": torch.zeros(2, 2)}, specs)
     with pytest.raises(WeightError, match="floating point"):
         check_tensors({"t": torch.zeros(2, dtype=torch.int32), "w": torch.zeros(2, 2, dtype=torch.int32)}, specs)
+
+
+def test_prefixes_and_ignorable_tensors_are_the_architectures_to_say(tmp_path):
+    """Another architecture with a prefix of its own and a real tensor called like GPT-2's mask buffer: the loader
+    takes both from its registry entry; nothing of GPT-2's conventions applies to it."""
+    import dataclasses
+    from vlrf_b200.config import ModelConfig, key
+    from vlrf_b200.registry import Architecture, register_architecture, unregister_architecture
+
+    @dataclasses.dataclass
+    class OtherConfig(ModelConfig):
+        model_type = "other_arch"
+        width: int = key()
+
+    def spec(cfg):
+        return [TensorSpec("emb", (4, cfg.width)), TensorSpec("l0.attn.bias", (cfg.width,), "vector")]
+
+    register_architecture(Architecture("other_arch", OtherConfig, spec, lambda cfg, gen: {}, lambda *a: None,
+                                       prefixes=("", "model."), ignored_tensors=lambda cfg: ("*.rotary.inv_freq",)), replace=True)
+    try:
+        (tmp_path / "config.json").write_text(json.dumps({"model_type": "other_arch", "width": 6}))
+        good = {"model.emb": torch.zeros(4, 6), "model.l0.attn.bias": torch.ones(6), "model.l0.rotary.inv_freq": torch.zeros(3)}
+        write_safetensors(tmp_path / "model.safetensors", good)
+        _, _, checked = open_model_dir(tmp_path)
+        assert torch.equal(checked["l0.attn.bias"], torch.ones(6))          # a real tensor here, not a mask to skip
+        # GPT-2's prefix is not this architecture's, and its own "*.attn.bias" is required, not ignorable
+        write_safetensors(tmp_path / "model.safetensors", {"transformer.emb": torch.zeros(4, 6), "model.l0.rotary.inv_freq": torch.zeros(3)})
+        with pytest.raises(WeightError) as e:
+            open_model_dir(tmp_path)
+        assert "emb" in str(e.value) and "l0.attn.bias" in str(e.value) and "transformer.emb" in str(e.value)
+    finally:
+        unregister_architecture("other_arch")

@@ -46,6 +46,10 @@ class GPT2Config(ModelConfig):
         if self.n_embd % self.n_head != 0:
             raise ConfigError(
                 f"n_embd ({self.n_embd}) must be a multiple of n_head ({self.n_head})")
+        if self.head_dim % 16 != 0 or self.head_dim > 256:
+            raise ConfigError(
+                f"n_embd / n_head = {self.head_dim}: this library's attention kernels take head sizes that are "
+                f"multiples of 16 up to 256")
         if not self.layer_norm_epsilon > 0.0:
             raise ConfigError(f"layer_norm_epsilon must be positive, got {self.layer_norm_epsilon}")
         if self.activation_function not in GPT2_ACTIVATIONS:

@@ -10,6 +10,7 @@ from __future__ import annotations
 import ctypes
 import threading
 
+from ..log import timers as _timers
 from .build import ensure_built
 
 
@@ -141,6 +142,9 @@ def call(name: str, *args) -> None:
     global _launches
     lib = library()
     _launches += 1
-    status = getattr(lib, name)(*args)
+    if _timers.on:
+        status = _timers.timed(name, getattr(lib, name), *args)
+    else:
+        status = getattr(lib, name)(*args)
     if status != 0:
         raise KernelError(f"{name}: {lib.vlrf_last_error().decode('utf-8', 'replace')} (status {status})")

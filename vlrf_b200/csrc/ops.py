@@ -46,8 +46,9 @@ def _dev(t: torch.Tensor, name: str, dtype=None) -> None:
         raise KernelError(f"{name} must be {dtype}, not {t.dtype}")
 
 
-def embed(wte, wpe, tokens, positions, out, dev_err) -> None:
-    """out[t] = wte[tokens[t]] (+ wpe[positions[t]]), float32."""
+def embed(wte, wpe, tokens, positions, out, dev_err, stats: "RowStats | None" = None) -> None:
+    """out[t] = wte[tokens[t]] (+ wpe[positions[t]]), float32.  With `stats` and few rows (a decode step) the rows'
+    statistics are left there for the next product's LayerNorm."""
     _dev(wte, "wte"); _dev(tokens, "tokens", torch.int32); _dev(out, "out", torch.float32)
     _dev(dev_err, "dev_err", torch.int32)
     T = tokens.shape[0]
@@ -60,12 +61,13 @@ def embed(wte, wpe, tokens, positions, out, dev_err) -> None:
             raise KernelError("embed: position table or positions do not match")
     if out.shape[0] < T or out.shape[1] != d:
         raise KernelError("embed: output does not match")
-    _written(out)
-    keep = 0 < T <= ROW_STATS_MAX_ROWS and d <= ROW_STATS_MAX_WIDTH     # few rows: a decode step; leave their statistics
+    keep = stats is not None and stats.takes(T, d)     # few rows: a decode step; leave their statistics
+    if stats is not None:
+        stats.written(out)
     call("vlrf_embed", _ptr(wte), _ptr(wpe), dtype_code(wte.dtype), _ptr(tokens), _ptr(positions), _ptr(out),
-         T, d, V, P, _ptr(_row_stats_buffer()) if keep else 0, _ptr(dev_err), _stream())
+         T, d, V, P, _ptr(stats.buffer()) if keep else 0, _ptr(dev_err), _stream())
     if keep:
-        _keep_row_stats(out, T, d)
+        stats.keep(out, T, d)
 
 
 def layernorm(x, gamma, beta, eps: float, out, rows=None) -> None:
@@ -79,16 +81,17 @@ def layernorm(x, gamma, beta, eps: float, out, rows=None) -> None:
         n = rows.shape[0]
     if gamma.shape[0] != d or beta.shape[0] != d or out.shape[1] != d or out.shape[0] < n:
         raise KernelError("layernorm: sizes do not match")
-    _written(out)
     call("vlrf_layernorm", _ptr(x), _ptr(rows), _ptr(gamma), _ptr(beta), _ptr(out), dtype_code(out.dtype), n, d,
          float(eps), _stream())
 
 
-def linear(x, w, bias, out, *, act=None, residual=None, rows: int | None = None, kv_scatter=None) -> bool:
+def linear(x, w, bias, out, *, act=None, residual=None, rows: int | None = None, kv_scatter=None,
+           stats: "RowStats | None" = None) -> bool:
     """out = act(x · wᵀ + bias) (+ residual).  x [M,K], w [N,K] (same dtype), bias/residual float32,
     out [M,N] float32 or bfloat16.  `rows` limits M to the first rows of x/out/residual.  `kv_scatter`
     (see linear_layernorm) asks the kernel to write K/V columns into a cache as well; the return value
-    says whether it did (only the tensor-core kernels can)."""
+    says whether it did (only the tensor-core kernels can).  `stats`: where the statistics of float32 result rows
+    are left when the kernel that takes the shape computes them (and where stale ones of `out` are forgotten)."""
     _dev(x, "x"); _dev(w, "w", x.dtype); _dev(out, "out")
     M = x.shape[0] if rows is None else rows
     K = x.shape[1]
@@ -105,10 +108,13 @@ def linear(x, w, bias, out, *, act=None, residual=None, rows: int | None = None,
             raise KernelError("linear: residual does not match")
     if x.dtype == torch.float32 and out.dtype != torch.float32:
         raise KernelError("linear: float32 input gives float32 output")
-    _written(out)
-    return _linear_dispatch(x, w, bias, out, ACT[act], residual, M, N, K, kv_scatter)
+    if stats is not None:
+        stats.written(out)
+    return _linear_dispatch(x, w, bias, out, ACT[act], residual, M, N, K, kv_scatter, stats)
 
 
+#: head sizes that the attention kernels take (each checks it again; parts refuse others when they are built)
+HEAD_DIM_STEP, HEAD_DIM_MAX = 16, 256
 _SM_COUNT = None
 USE_TCGEN05 = True
 PREFILL_ATTENTION_TCGEN05 = True     # head size 64; off: the mma.sync kernel takes those too
@@ -126,21 +132,56 @@ SPLITK_NORM_MIN_WEIGHT_BYTES = 0
 _DEV_ERR = None
 
 
-#: Row statistics of the float32 residual rows that a product has just written (per row and 32-column
-#: segment: sum and squared deviation from the segment's mean), kept so that the next product can apply a
-#: LayerNorm to those rows without reading them whole.  One buffer of fixed address (graphs capture it);
-#: `_ROW_STATS_OF` says whose rows it describes: (the tensor, its torch version counter then, rows, width) or
-#: None.  The tensor is held, so its memory cannot be given to another tensor meanwhile.
 ROW_STATS_MAX_ROWS, ROW_STATS_MAX_WIDTH = 64, 8192
-_ROW_STATS = None
-_ROW_STATS_OF = None
 
 
-def _row_stats_buffer() -> torch.Tensor:
-    global _ROW_STATS
-    if _ROW_STATS is None:
-        _ROW_STATS = torch.zeros(ROW_STATS_MAX_ROWS * (ROW_STATS_MAX_WIDTH // 32) * 2, dtype=torch.float32, device="cuda")
-    return _ROW_STATS
+class RowStats:
+    """Statistics of the float32 residual rows that a product has just written (per row and 32-column segment: sum
+    and squared deviation from the segment's mean), kept so that the next product can apply a LayerNorm to those
+    rows without reading them whole.  One buffer of fixed address (graphs capture it) on the device of the
+    workspace that owns it; `of` says whose rows it describes: (the tensor, its torch version counter then, rows,
+    width) or None.  The tensor is held, so its memory cannot be given to another tensor meanwhile.
+
+    Who may trust them: a product of this module that is handed the same object and the same rows.  Who keeps them
+    honest: every function of this module that writes a tensor and is handed the object forgets stale statistics;
+    torch's in-place operations are seen by the version counter; and the block forgets them after any part that does
+    not declare `leaves_row_stats` (parts/block.py), so a part that writes the residual with kernels of its own
+    cannot leave them stale by omission."""
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self._buffer = None
+        self.of = None
+
+    def buffer(self) -> torch.Tensor:
+        if self._buffer is None:
+            self._buffer = torch.zeros(ROW_STATS_MAX_ROWS * (ROW_STATS_MAX_WIDTH // 32) * 2, dtype=torch.float32,
+                                       device=self.device)
+        return self._buffer
+
+    def takes(self, rows: int, width: int) -> bool:
+        return 0 < rows <= ROW_STATS_MAX_ROWS and width <= ROW_STATS_MAX_WIDTH
+
+    def keep(self, t, rows: int, width: int) -> None:
+        v = _version_of(t)
+        self.of = (t, v, rows, width) if v >= 0 else None
+
+    def forget(self) -> None:
+        self.of = None
+
+    def written(self, t) -> None:
+        """`t` is being rewritten: statistics kept of it are stale."""
+        if self.of is not None and t is not None and self.of[0].data_ptr() == t.data_ptr():
+            self.of = None
+
+    def describing(self, x, rows: int, width: int):
+        """The statistics buffer if it describes exactly these rows as they are now, else None."""
+        if self.of is None:
+            return None
+        held, version, n_rows, n_cols = self.of
+        if held.data_ptr() == x.data_ptr() and _version_of(x) == version and (n_rows, n_cols) == (rows, width):
+            return self._buffer
+        return None
 
 
 def _version_of(t) -> int:
@@ -150,35 +191,6 @@ def _version_of(t) -> int:
         return t._version
     except RuntimeError:
         return -1
-
-
-def _keep_row_stats(t, rows: int, width: int) -> None:
-    global _ROW_STATS_OF
-    v = _version_of(t)
-    _ROW_STATS_OF = (t, v, rows, width) if v >= 0 else None
-
-
-def _written(t) -> None:
-    """Every function here that writes a tensor says so: statistics kept of it are stale then."""
-    global _ROW_STATS_OF
-    if _ROW_STATS_OF is not None and t is not None and _ROW_STATS_OF[0].data_ptr() == t.data_ptr():
-        _ROW_STATS_OF = None
-
-
-def residual_written(t) -> None:
-    """For code that changes residual rows with kernels of its own (torch's in-place operations are seen
-    without this): forget what is known about those rows."""
-    _written(t)
-
-
-def _row_stats_of(x, rows: int, width: int):
-    """The statistics buffer if it describes exactly these rows as they are now, else None."""
-    if _ROW_STATS_OF is None:
-        return None
-    held, version, n_rows, n_cols = _ROW_STATS_OF
-    if held.data_ptr() == x.data_ptr() and _version_of(x) == version and (n_rows, n_cols) == (rows, width):
-        return _ROW_STATS
-    return None
 
 
 def _splitk_takes(M: int, N: int, K: int, ldx: int, fused_norm: bool) -> bool:
@@ -239,7 +251,7 @@ def _kv_args(kv_scatter, N: int) -> list:
             kc.shape[2]]
 
 
-def _linear_dispatch(x, w, bias, out, act, residual, M, N, K, kv_scatter=None) -> bool:
+def _linear_dispatch(x, w, bias, out, act, residual, M, N, K, kv_scatter=None, stats=None) -> bool:
     bf16_out = out.dtype == torch.bfloat16
     if (x.dtype == torch.bfloat16 and M <= SKINNY_MAX_ROWS and K % 8 == 0 and USE_TCGEN05 and kv_scatter is None
             and N >= SWAPPED_MIN_COLUMNS):
@@ -251,12 +263,12 @@ def _linear_dispatch(x, w, bias, out, act, residual, M, N, K, kv_scatter=None) -
     if x.dtype == torch.bfloat16 and M <= SKINNY_MAX_ROWS and _splitk_takes(M, N, K, K, False):
         # few rows, a large matrix: tiles of w on the tensor cores, the sum over k cut into parts
         scatter = kv_scatter is not None and bf16_out
-        keep = not bf16_out and M <= ROW_STATS_MAX_ROWS and N <= ROW_STATS_MAX_WIDTH
+        keep = stats is not None and not bf16_out and stats.takes(M, N)
         call("vlrf_gemm_splitk", _ptr(x), 0, _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), dtype_code(out.dtype),
              M, N, K, K, N, act, 0, 0, 0.0, *_kv_args(kv_scatter if scatter else None, N), 0,
-             _ptr(_row_stats_buffer()) if keep else 0, _ptr(_dev_err()), _stream())
+             _ptr(stats.buffer()) if keep else 0, _ptr(_dev_err()), _stream())
         if keep:
-            _keep_row_stats(out, M, N)
+            stats.keep(out, M, N)
         return scatter
     if x.dtype == torch.bfloat16 and M <= SKINNY_MAX_ROWS and K % 32 == 0:
         # few rows: the product is bound by streaming w once
@@ -286,7 +298,7 @@ def can_fuse_layernorm(n_rows: int, width: int, w_dtype: torch.dtype) -> bool:
 
 
 def linear_layernorm(x, gamma, beta, eps: float, w, bias, out, *, act=None, rows: int | None = None,
-                     kv_scatter=None) -> None:
+                     kv_scatter=None, stats: "RowStats | None" = None) -> None:
     """out = act(LayerNorm(x) · wᵀ + bias) for few rows, the norm fused into the product's prologue.
     x float32 [M,K]; w bfloat16 [N,K]; out bfloat16 or float32.  `kv_scatter` = (k_cache, v_cache,
     block_table, tok_slot, tok_pos, k_off, v_off, n_kv_heads, head_dim) also writes those columns of the
@@ -300,12 +312,13 @@ def linear_layernorm(x, gamma, beta, eps: float, w, bias, out, *, act=None, rows
     if bias is not None:
         _dev(bias, "bias", torch.float32)
     kv = _kv_args(kv_scatter, N)
-    stats = _row_stats_of(x, M, K)
-    _written(out)
-    if stats is not None and _splitk_takes(M, N, K, K, True):
+    known = stats.describing(x, M, K) if stats is not None else None
+    if stats is not None:
+        stats.written(out)
+    if known is not None and _splitk_takes(M, N, K, K, True):
         # the rows' statistics are at hand: each CTA normalises only the columns it multiplies
         call("vlrf_gemm_splitk", _ptr(x), 1, _ptr(w), _ptr(bias), 0, _ptr(out), dtype_code(out.dtype), M, N, K, K, N,
-             ACT[act], _ptr(gamma), _ptr(beta), float(eps), *kv, _ptr(stats), 0, _ptr(_dev_err()), _stream())
+             ACT[act], _ptr(gamma), _ptr(beta), float(eps), *kv, _ptr(known), 0, _ptr(_dev_err()), _stream())
         return
     call("vlrf_gemm_skinny", _ptr(x), 1, _ptr(w), _ptr(bias), 0, _ptr(out), dtype_code(out.dtype), M, N, K, K, N,
          ACT[act], _ptr(gamma), _ptr(beta), float(eps), *kv, sm_count(), _ptr(_dev_err()), _stream())
@@ -346,7 +359,6 @@ def attention_decode(qkv, q_off: int, k_cache, v_cache, block_table, tok_slot, t
         _dev(partials, "partials", torch.float32); _dev(counters, "counters", torch.int32)
         if partials.numel() < n_rows * n_heads * n_split * (head_dim + 2) or counters.numel() < n_rows * n_heads:
             raise KernelError("attention_decode: scratch is too small")
-    _written(out)
     call("vlrf_attn_decode", _ptr(qkv), dtype_code(qkv.dtype), qkv.shape[1], q_off, _ptr(k_cache), _ptr(v_cache), nb,
          _ptr(block_table), block_table.shape[1], _ptr(tok_slot), _ptr(tok_pos), _ptr(out), out.shape[1], n_rows,
          n_heads, n_kv_heads, head_dim, bt, float(scale), int(window), int(n_split), _ptr(partials), _ptr(counters),
@@ -387,7 +399,6 @@ def attention_generic(qkv, q_off: int, k_cache, v_cache, block_table, tok_slot, 
         raise KernelError("attention: output does not match")
     if q_off + n_heads * head_dim > qkv.shape[1]:
         raise KernelError("attention: Q columns lie outside the row")
-    _written(out)
     call("vlrf_attn_generic", _ptr(qkv), dtype_code(qkv.dtype), qkv.shape[1], q_off, _ptr(k_cache), _ptr(v_cache),
          _ptr(block_table), block_table.shape[1], _ptr(tok_slot), _ptr(tok_pos), _ptr(out), out.shape[1],
          n_tokens, n_heads, n_kv_heads, head_dim, bt, float(scale), int(window), _ptr(dev_err), _stream())
@@ -441,6 +452,23 @@ def attention_prefill_takes(dtype: torch.dtype, head_dim: int, block_tokens: int
     return bool(library().vlrf_attn_prefill_takes(head_dim, block_tokens, row_width, q_off))
 
 
+def attention_prefill_kind(dtype: torch.dtype, head_dim: int, block_tokens: int, row_width: int, q_off: int, out_width: int) -> str:
+    """Which kernel prompt attention of these sizes runs on: "tcgen05" (bfloat16, head size 64), "mma.sync"
+    (bfloat16, head sizes 64 and 128) or "CUDA cores" (everything else, and the 32-bit path)."""
+    from . import library
+    lib = library()
+    if dtype == torch.bfloat16 and PREFILL_ATTENTION_TCGEN05 and lib.vlrf_attn_prefill_tc_takes(head_dim, block_tokens, row_width, q_off, out_width):
+        return "tcgen05"
+    if dtype == torch.bfloat16 and lib.vlrf_attn_prefill_takes(head_dim, block_tokens, row_width, q_off):
+        return "mma.sync"
+    return "CUDA cores"
+
+
+def attention_decode_kind(dtype: torch.dtype, head_dim: int) -> str:
+    """Which kernel decode attention runs on: "mma.sync" (bfloat16, head size 64) or "CUDA cores"."""
+    return "mma.sync" if dtype == torch.bfloat16 and head_dim == 64 else "CUDA cores"
+
+
 def attention_prefill_parts(dtype: torch.dtype, n_seqs: int, max_new: int, n_heads: int, head_dim: int, block_tokens: int,
                             row_width: int, q_off: int) -> int:
     """Into how many parts `attention_prefill` best deals the keys of a long tile of queries (1: not at all;
@@ -489,7 +517,6 @@ def attention_prefill(qkv, q_off: int, k_cache, v_cache, block_table, seq_slot, 
         raise KernelError("attention_prefill: output does not match")
     if seq_slot.shape[0] < n_seqs or seq_start.shape[0] < n_seqs + 1 or seq_pos0.shape[0] < n_seqs:
         raise KernelError("attention_prefill: sequence tables are too short")
-    _written(out)
     from . import library
     if PREFILL_ATTENTION_TCGEN05 and library().vlrf_attn_prefill_tc_takes(head_dim, bt, qkv.shape[1], q_off, out.shape[1]):
         # head size 64: S and O on the tcgen05 tensor cores, accumulators in tensor memory

@@ -1,8 +1,11 @@
 """From a model folder to a model on the device."""
 from __future__ import annotations
 
+import time
+
 import torch
 
+from .. import log
 from ..weights.model_dir import open_model_dir
 from .model import BuildOptions, DecoderModel
 
@@ -30,4 +33,16 @@ def load_model(model_dir, dtype="bfloat16", device="cuda:0") -> DecoderModel:
         from ..csrc import KernelError
         raise KernelError(f"cannot put a model on '{device}': the engine's kernels are CUDA code for sm_100a and there "
                           f"is no other execution path (CUDA available: {torch.cuda.is_available()})")
-    return arch.build(cfg, weights, options)
+    started = time.perf_counter()
+    model = arch.build(cfg, weights, options)
+    log.info(f"{model_dir}: {arch.name}, {len(model.layers)} layers, width {model.width}, vocabulary {model.vocab_size}, "
+             f"{model.weight_bytes() / 2**20:.1f} MiB of weights as {options.dtype} on {options.device} "
+             f"in {time.perf_counter() - started:.2f} s")
+    kinds = {}
+    for i, name, k in model.describe_kernels():
+        kinds.setdefault((name, k["prompt"], k["decode"]), []).append(i)
+    for (name, prompt, decode), layers in kinds.items():
+        say = log.warn if options.dtype == torch.bfloat16 and "CUDA cores" in (prompt, decode) else log.info
+        say(f"layers {layers[0]}…{layers[-1]} ({name}): prompt attention on {prompt}, decode attention on {decode}"
+            + (" (no tensor-core kernel takes this head size)" if say is log.warn else ""))
+    return model

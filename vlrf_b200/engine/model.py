@@ -62,6 +62,15 @@ class DecoderModel:
             parts.extend(v for v in vars(layer).values() if not isinstance(v, (int, float, str, torch.Tensor)))
         return all(ok(p) for p in parts)
 
+    def describe_kernels(self, block_tokens: int = 64) -> list:
+        """For every layer whose mixer can say, which attention kernels its sizes get (see the mixers' `kernels`)."""
+        out = []
+        for i, layer in enumerate(self.layers):
+            mixer = getattr(layer, "mixer", None)
+            if mixer is not None and hasattr(mixer, "kernels"):
+                out.append((i, type(mixer).__name__, mixer.kernels(self.act_dtype, block_tokens)))
+        return out
+
     def cache_needs(self) -> list:
         """For every schedule entry what it keeps per sequence (None for entries that read another's)."""
         return [None if c.reads_cache_of is not None else self.layers[c.layer].cache_need()
@@ -112,11 +121,16 @@ class DecoderModel:
         [ctx.n_logit_rows, vocab] for the rows in ctx.logit_rows
         (reference: include/model/transformer.hpp:335-424, which keeps the last row only)."""
         x = ctx.ws.get("residual", ctx.n_tokens, self.width, torch.float32)
+        ctx.ws.row_stats.forget()                      # nothing is known about the rows of the step before
         self.embedding(ctx, x)
+        if not getattr(self.embedding, "leaves_row_stats", False):
+            ctx.ws.row_stats.forget()
         for i, call in enumerate(self.schedule):
             owner = i if call.reads_cache_of is None else call.reads_cache_of
             view = cache.view(owner) if cache.needs[owner] is not None else None
             self.layers[call.layer].forward(x, ctx, view, writes_cache=call.reads_cache_of is None)
+            if not getattr(self.layers[call.layer], "leaves_row_stats", False):
+                ctx.ws.row_stats.forget()              # a block of another kind that does not vouch for them
         n = ctx.n_logit_rows
         logits = ctx.ws.get("logits", max(n, 1), self.vocab_size, torch.float32)
         if n == 0:

@@ -113,5 +113,14 @@ def build(cfg: GPT2Config, weights: CheckedWeights, options: BuildOptions) -> De
                         options=options, max_seq_len=cfg.n_positions)
 
 
+def ignored_tensors(cfg: GPT2Config) -> tuple:
+    """What Hugging Face GPT-2 checkpoints carry but no computation reads: the causal-mask buffers
+    (tools/converter/test_converters.py:113-114 has them skipped) and, with a tied head, the head's copy of the
+    embedding (tools/converter/convert_gpt2.py:141-142)."""
+    return ("*.attn.bias", "*.attn.masked_bias") + (("lm_head.weight",) if cfg.tie_word_embeddings else ())
+
+
 GPT2 = register_architecture(Architecture(
-    name="gpt2", config_cls=GPT2Config, weight_spec=weight_spec, random_weights=random_weights, build=build))
+    name="gpt2", config_cls=GPT2Config, weight_spec=weight_spec, random_weights=random_weights, build=build,
+    prefixes=("", "transformer."),          # tools/converter/convert_gpt2.py:83-95 accepts both
+    ignored_tensors=ignored_tensors))

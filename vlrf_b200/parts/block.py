@@ -18,6 +18,11 @@ class PreNormBlock:
     def cache_need(self):
         return self.mixer.cache_need()
 
+    @property
+    def leaves_row_stats(self) -> bool:
+        """Whether the step's row statistics are true after this block: its last part says (see forward)."""
+        return bool(getattr(self.feed_forward, "leaves_row_stats", False))
+
     def emit_decode(self, program, x: torch.Tensor, view, writes_cache: bool = True) -> None:
         """This block's decode step as operations of a decode program: possible when the mixer and the
         feed-forward can state theirs (they get the norm to fuse, as in `forward`)."""
@@ -34,8 +39,14 @@ class PreNormBlock:
         else:
             h = ctx.ws.get("block_normed", ctx.n_tokens, x.shape[1], ctx.act_dtype)
             self.mixer.forward(self.norm1(x, h), x, ctx, view, writes_cache)
+        # What is known about the residual rows (their statistics, for a fused LayerNorm) is true only if the part
+        # that just rewrote them says so; a part with kernels of its own need not know that such a thing exists.
+        if not getattr(self.mixer, "leaves_row_stats", False):
+            ctx.ws.row_stats.forget()
         if getattr(self.feed_forward, "fuses_norm", False):
             self.feed_forward.forward(None, x, ctx, norm=self.norm2)
         else:
             h = ctx.ws.get("block_normed", ctx.n_tokens, x.shape[1], ctx.act_dtype)
             self.feed_forward.forward(self.norm2(x, h), x, ctx)
+        if not getattr(self.feed_forward, "leaves_row_stats", False):
+            ctx.ws.row_stats.forget()

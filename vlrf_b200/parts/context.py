@@ -23,6 +23,10 @@ class Workspace:
         self._views: dict = {}   # (name, rows, cols, dtype) -> the view handed out last time (making one costs 2 to 3 us)
         self.frozen = False  # set while a captured graph depends on the addresses
         self.generation = 0  # counts (re)allocations: captured steps are valid for one generation only
+        from ..csrc.ops import RowStats
+        #: statistics of the residual rows that the step's last product wrote (see csrc.ops.RowStats); parts hand
+        #: this to the products that may leave or use them, the block forgets them after parts it cannot vouch for
+        self.row_stats = RowStats(self.device)
 
     def get(self, name: str, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
         key = (name, rows, cols, dtype)

@@ -21,12 +21,16 @@ class TokenEmbedding:
         else:
             self.position = None
 
+    #: the rows are written by a kernel that is handed the step's row statistics (see parts/block.py)
+    leaves_row_stats = True
+
     def emit_decode(self, program, x: torch.Tensor) -> None:
         program.embed(self.weight, self.position.table if self.position is not None else None, x)
 
     def __call__(self, ctx: StepContext, x: torch.Tensor) -> torch.Tensor:
         table = self.position.table if self.position is not None else None
-        ops.embed(self.weight, table, ctx.tokens, ctx.tok_pos if table is not None else None, x, ctx.dev_err)
+        ops.embed(self.weight, table, ctx.tokens, ctx.tok_pos if table is not None else None, x, ctx.dev_err,
+                  stats=ctx.ws.row_stats)
         return x
 
 

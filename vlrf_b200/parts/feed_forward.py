@@ -32,6 +32,8 @@ class DenseMLP:
 
     #: the block may hand over its norm instead of normed rows: forward(None, x, ctx, norm=…)
     fuses_norm = True
+    #: the residual rows are written last by a product that is handed the step's row statistics (see the mixer)
+    leaves_row_stats = True
 
     def emit_decode(self, program, x: torch.Tensor, norm) -> None:
         """The decode step of this part as two operations of a decode program."""
@@ -44,9 +46,10 @@ class DenseMLP:
         T = ctx.n_tokens
         u = ctx.ws.get("ffn_inner", T, self.inner, ctx.act_dtype)
         if h is None and getattr(norm, "fusable_as", None) == "layernorm" and ops.can_fuse_layernorm(T, x.shape[1], self.w_in.dtype):
-            ops.linear_layernorm(x, norm.weight, norm.bias, norm.eps, self.w_in, self.b_in, u, act=self.activation)
+            ops.linear_layernorm(x, norm.weight, norm.bias, norm.eps, self.w_in, self.b_in, u, act=self.activation,
+                                 stats=ctx.ws.row_stats)
         else:
             if h is None:
                 h = norm(x, ctx.ws.get("block_normed", T, x.shape[1], ctx.act_dtype))
             ops.linear(h, self.w_in, self.b_in, u, act=self.activation)
-        ops.linear(u, self.w_out, self.b_out, x, residual=x)
+        ops.linear(u, self.w_out, self.b_out, x, residual=x, stats=ctx.ws.row_stats)

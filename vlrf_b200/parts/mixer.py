@@ -46,6 +46,9 @@ class CausalSelfAttention:
             raise ValueError("attention: output projection does not take the merged heads")
         if n_heads % n_kv_heads != 0:
             raise ValueError(f"attention: {n_heads} heads cannot share {n_kv_heads} key/value heads")
+        if head_dim % ops.HEAD_DIM_STEP != 0 or not (0 < head_dim <= ops.HEAD_DIM_MAX):
+            raise ValueError(f"attention: a head size of {head_dim} is not taken: the attention kernels take head sizes "
+                             f"that are multiples of {ops.HEAD_DIM_STEP} up to {ops.HEAD_DIM_MAX}")
         if position is not None and getattr(position, "where", None) == "qk":
             raise NotImplementedError("attention: no position encoding acting on q/k is built into this mixer")
         self.w_qkv, self.b_qkv, self.w_out, self.b_out = w_qkv, b_qkv, w_out, b_out
@@ -61,6 +64,9 @@ class CausalSelfAttention:
 
     #: the block may hand over its norm instead of normed rows: forward(None, x, …, norm=…)
     fuses_norm = True
+    #: the residual rows are written last by a product of csrc.ops that is handed the step's row statistics, so
+    #: what those say afterwards is true (the block forgets them after parts that do not declare this)
+    leaves_row_stats = True
 
     def forward(self, h, x: torch.Tensor, ctx: StepContext, view, writes_cache: bool = True, norm=None) -> None:
         T = ctx.n_tokens
@@ -73,7 +79,8 @@ class CausalSelfAttention:
                 scatter = (view.k, view.v, view.block_table, ctx.tok_slot, ctx.tok_pos, self.k_off, self.v_off,
                            self.n_kv_heads, self.head_dim)
                 appended = True
-            ops.linear_layernorm(x, norm.weight, norm.bias, norm.eps, self.w_qkv, self.b_qkv, qkv, kv_scatter=scatter)
+            ops.linear_layernorm(x, norm.weight, norm.bias, norm.eps, self.w_qkv, self.b_qkv, qkv, kv_scatter=scatter,
+                                 stats=ctx.ws.row_stats)
         else:
             if h is None:
                 h = norm(x, ctx.ws.get("block_normed", T, x.shape[1], ctx.act_dtype))
@@ -87,7 +94,7 @@ class CausalSelfAttention:
                           ctx.tok_pos, T, self.n_kv_heads, self.head_dim, ctx.dev_err)
         merged = ctx.ws.get("attn_out", T, self.n_heads * self.head_dim, ctx.act_dtype)
         self._attend(qkv, view, merged, ctx)
-        ops.linear(merged, self.w_out, self.b_out, x, residual=x)
+        ops.linear(merged, self.w_out, self.b_out, x, residual=x, stats=ctx.ws.row_stats)
 
     def emit_decode(self, program, x: torch.Tensor, norm, view, writes_cache: bool = True) -> None:
         """The decode step of this mixer as operations of a decode program: norm + q/k/v projection (+ cache
@@ -102,6 +109,14 @@ class CausalSelfAttention:
         program.attention(qkv, self.q_off, self.k_off, self.v_off, view.k, view.v, view.block_table, merged, n_heads=self.n_heads,
                           n_kv_heads=self.n_kv_heads, head_dim=self.head_dim, scale=self.scale, window=self.window)
         program.product(merged, self.w_out, self.b_out, x, residual=x)
+
+    def kernels(self, act_dtype: torch.dtype, block_tokens: int) -> dict:
+        """Which attention kernels these sizes get: {"prompt": …, "decode": …}, each "tcgen05", "mma.sync" or
+        "CUDA cores".  Said once when a model is built, so that a head size that leaves the tensor cores is a
+        visible fact."""
+        return {"prompt": ops.attention_prefill_kind(act_dtype, self.head_dim, block_tokens, self.qkv_width, self.q_off,
+                                                     self.n_heads * self.head_dim),
+                "decode": ops.attention_decode_kind(act_dtype, self.head_dim)}
 
     def _attend(self, qkv, view, merged, ctx: StepContext) -> None:
         T = ctx.n_tokens

@@ -28,6 +28,11 @@ class Architecture:
     random_weights: Callable
     #: (config, CheckedWeights, BuildOptions) -> engine.model.DecoderModel
     build: Callable
+    #: spellings that a checkpoint may put in front of every tensor name of `weight_spec` ("" = none)
+    prefixes: tuple = ("",)
+    #: config -> fnmatch patterns of tensors that a checkpoint may carry but no computation reads (buffers of
+    #: the training code, a head that is tied to the embedding): present or absent, they are no error
+    ignored_tensors: Callable = lambda cfg: ()
 
 
 _ARCHITECTURES: dict[str, Architecture] = {}

@@ -16,10 +16,6 @@ from ..registry import Architecture, parse_config
 from .safetensors_io import WeightError, read_safetensors, write_safetensors
 from .spec import CheckedWeights, check_tensors
 
-#: tensors that Hugging Face GPT-2 checkpoints carry but no computation reads: the causal-mask
-#: buffers (tools/converter/test_converters.py:113-114 has them skipped)
-_IGNORED = ("*.attn.bias", "*.attn.masked_bias")
-
 
 def open_model_dir(model_dir) -> tuple[Architecture, ModelConfig, CheckedWeights]:
     model_dir = Path(model_dir)
@@ -29,9 +25,9 @@ def open_model_dir(model_dir) -> tuple[Architecture, ModelConfig, CheckedWeights
         raise WeightError(f"{model_dir} has no model.safetensors")
     found = read_safetensors(st)
     specs = arch.weight_spec(cfg)
-    tied = getattr(cfg, "tie_word_embeddings", False)
-    ignore = _IGNORED + (("lm_head.weight",) if tied else ())
-    checked = check_tensors(found, specs, prefixes=("", "transformer."), ignore=ignore, source=str(st))
+    # which prefixes a checkpoint may carry and which of its tensors nothing reads is the architecture's to say
+    checked = check_tensors(found, specs, prefixes=tuple(arch.prefixes), ignore=tuple(arch.ignored_tensors(cfg)),
+                            source=str(st))
     return arch, cfg, checked
 
 
