@@ -118,3 +118,73 @@ def test_generation_inside_inference_mode(model_dirs):
         model = Model.load(model_dirs["tiny_b"], dtype="bfloat16", max_tokens=256)
         got = model.generate_ids(prompts, params)
     assert [r.new_tokens for r in got] == [r.new_tokens for r in want]
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", TOL_F32), ("bfloat16", TOL_BF16)])
+def test_waiting_requests_take_freed_rows_at_the_next_step_boundary(model_dirs, plain_models, dtype, tol):
+    """Ten requests on four rows with unequal ends: a waiting request's prompt runs in the step in which the others go
+    on by one token, then it decodes with them in the replayed session.  Every request gets what it gets alone."""
+    from vlrf_b200 import Model, SamplingParams
+    cfg, w = plain_models["tiny_b"]
+    model = Model.load(model_dirs["tiny_b"], dtype=dtype, max_tokens=64 * 12, n_slots=4)
+    lens = [7, 30, 2, 65, 1, 12, 64, 3, 40, 9]
+    news = [12, 2, 9, 1, 14, 3, 2, 11, 1, 6]
+    prompts = [random_ids(cfg["vocab_size"], n, 300 + i) for i, n in enumerate(lens)]
+    params = [SamplingParams(max_new_tokens=m, do_sample=False, stop_token_ids=()) for m in news]
+    res = model.generate_ids(prompts, params)
+    for p, m, r in zip(prompts, news, res):
+        assert r.prompt == p and r.tokens_generated == m and r.finish_reason == "length"
+        check_greedy(cfg, w, p, r.new_tokens, tol)
+        if dtype == "float32":
+            assert r.new_tokens == plain.greedy_generate(cfg, w, p, m)
+    b = model.backend
+    static_steps = sum(max(news[i:i + 4]) for i in range(0, 10, 4))
+    assert b.prompt_steps + b.decode_steps < static_steps          # fewer steps than whole batches would take
+    assert b.prompt_steps >= 3 and b.decode_steps > 0              # prompts joined running steps; decoding was replayed
+    assert model.engine.cache.slots.n_held == 0
+    model.engine.cache.check()
+    model.engine.check_device_errors()
+
+
+def test_a_request_that_ends_at_its_first_token_does_not_keep_the_rest_from_the_replayed_session(model_dirs, plain_models):
+    from vlrf_b200 import Model, SamplingParams
+    cfg, w = plain_models["tiny_a"]
+    model = Model.load(model_dirs["tiny_a"], dtype="float32", max_tokens=512)
+    prompts = [random_ids(512, n, 400 + n) for n in (9, 4, 20)]
+    params = [SamplingParams(max_new_tokens=m, do_sample=False, stop_token_ids=()) for m in (10, 1, 10)]
+    res = model.generate_ids(prompts, params)
+    assert [r.new_tokens for r in res] == [plain.greedy_generate(cfg, w, p, m) for p, m in zip(prompts, (10, 1, 10))]
+    assert model.backend.prompt_steps == 1 and model.backend.decode_steps == 9
+    # the same when it ends by a stop token that its prompt's logits choose
+    stop = res[0].new_tokens[0]
+    again = model.generate_ids(prompts, [SamplingParams(max_new_tokens=10, do_sample=False, stop_token_ids=(stop,)),
+                                         SamplingParams(max_new_tokens=10, do_sample=False, stop_token_ids=()),
+                                         SamplingParams(max_new_tokens=10, do_sample=False, stop_token_ids=())])
+    assert again[0].new_tokens == [stop] and again[0].finish_reason == "stop"
+    assert again[2].new_tokens == res[2].new_tokens
+    assert model.engine.cache.slots.n_held == 0
+
+
+def test_penalties_and_blocked_ngrams_follow_the_plain_rules_token_by_token(model_dirs, plain_models):
+    """Greedy generation under repetition / frequency / presence penalties and a blocked n-gram size: every token is the
+    first maximum of the plain implementation's logits edited by the plain rules from the tokens generated so far."""
+    import numpy as np
+    from vlrf_b200 import Model, SamplingParams
+    cfg, w = plain_models["tiny_a"]
+    model = Model.load(model_dirs["tiny_a"], dtype="float32", max_tokens=512)
+    prompts = [random_ids(512, n, 500 + n) for n in (6, 15)]
+    p = SamplingParams(max_new_tokens=30, do_sample=False, stop_token_ids=(), repetition_penalty=1.3, frequency_penalty=0.2,
+                       presence_penalty=0.1, no_repeat_ngram_size=3)
+    res = model.generate_ids(prompts, p)
+    for prompt, r in zip(prompts, res):
+        ids, new = list(prompt), []
+        for t in r.new_tokens:
+            lg = plain.logits_all_positions(cfg, w, ids)[-1].numpy()
+            counts = {}
+            for g in new:
+                counts[g] = counts.get(g, 0) + 1
+            edited = plain.block_repeated_ngrams(plain.apply_penalties(lg, counts, 1.3, 0.2, 0.1), new, 3)
+            best = float(edited.max())
+            assert np.isfinite(edited[t]) and best - float(edited[t]) <= 2 * TOL_F32 * float(np.abs(lg).max()), (len(ids), t)
+            ids.append(t)
+            new.append(t)

@@ -12,21 +12,32 @@ class ScriptedBackend:
         self.lim = (max_tokens, n_slots, 64, max_seq_len)
         self.free = list(range(n_slots))
         self.log = []
-        self.batches = 0
+        self.tables = 0
+        self.steps = 0
 
     def limits(self):
         return self.lim
 
-    def open_batch(self, requests):
-        self.batches += 1
-        slots = [self.free.pop(0) for _ in requests]
-        return {"slots": slots, "next": [r.prompt[0] for r in requests], "fed": [0] * len(requests), "open": set(range(len(requests)))}
+    def open_table(self, n_rows, requests):
+        self.tables += 1
+        assert 1 <= n_rows <= self.lim[1]
+        return {"slots": [None] * n_rows, "next": [None] * n_rows, "fed": [0] * n_rows, "open": set(), "closed": False}
+
+    def admit(self, h, row, request):
+        assert row not in h["open"] and not h["closed"], "a row is given to two requests"
+        h["open"].add(row)
+        h["slots"][row] = self.free.pop(0)
+        h["next"][row] = request.prompt[0]
+        h["fed"][row] = 0
+        self.log.append(("admit", h["slots"][row], request.index))
 
     def run(self, h, rows, tokens):
+        self.steps += 1
+        assert rows == sorted(set(rows)) and set(rows) == h["open"], "a step runs every live row once"
         self.log.append(("run", [h["slots"][r] for r in rows], [len(t) for t in tokens]))
         out = []
         for r, t in zip(rows, tokens):
-            assert r in h["open"]
+            assert len(t) == 1 or h["fed"][r] == 0, "only a row just admitted brings more than one token"
             h["fed"][r] += len(t)
             h["next"][r] += 1
             out.append(h["next"][r])
@@ -37,6 +48,11 @@ class ScriptedBackend:
         h["open"].remove(row)
         self.free.append(h["slots"][row])
         self.log.append(("close", h["slots"][row]))
+        h["slots"][row] = None
+
+    def close_table(self, h):
+        assert not h["open"] and not h["closed"]
+        h["closed"] = True
 
 
 def greedy(n, **kw):
@@ -94,11 +110,25 @@ def test_zero_new_tokens_runs_nothing():
     assert r.new_tokens == [] and r.finish_reason == "length" and b.log == []
 
 
-def test_requests_are_cut_into_batches_that_fit_and_slots_are_reused():
+def test_waiting_requests_take_the_rows_of_those_that_ended():
     b = ScriptedBackend(max_tokens=256, n_slots=2)
     res = generate(b, [[i] for i in range(5)], greedy(3))
     assert [r.new_tokens for r in res] == [[i + 1, i + 2, i + 3] for i in range(5)]
-    assert b.batches == 3 and sorted(b.free) == [0, 1]
+    assert b.tables == 1 and sorted(b.free) == [0, 1]
+    # 5 requests of 3 tokens on 2 rows: 3 + 3 + 3 steps, as with whole batches here (they all end together) …
+    assert b.steps == 9
+    # … but with unequal ends a waiting request joins at the next step boundary instead of waiting for the batch:
+    # 10 requests, 4 rows; static batches of 4, 4, 2 would take 12 + 12 + 12 = 36 steps
+    b = ScriptedBackend(max_tokens=4096, n_slots=4)
+    lens = [12, 2, 3, 2, 12, 1, 1, 2, 12, 3]
+    res = generate(b, [[10 * i] for i in range(10)], [greedy(n) for n in lens])
+    assert [r.new_tokens for r in res] == [[10 * i + k + 1 for k in range(n)] for i, n in enumerate(lens)]
+    assert b.steps == 16 and sorted(b.free) == [0, 1, 2, 3]          # 16 steps, not 36
+    # a step that admits a request runs its prompt beside the others' single tokens
+    runs = [e for e in b.log if e[0] == "run"]
+    assert any(len(set(widths)) > 1 or len(widths) > 1 for _, _, widths in runs)
+    admitted = [e[2] for e in b.log if e[0] == "admit"]
+    assert admitted == list(range(10))                      # in their order
     # tokens, not only slots, bound a batch: 100-token prompts + 100 new → 256 tokens each
     reqs = [Request([0] * 100, greedy(100), i) for i in range(3)]
     assert tokens_needed(reqs[0], 64, 1024) == 256
@@ -122,7 +152,7 @@ def test_callback_can_stop_a_sequence():
 def test_an_error_in_a_step_gives_the_slots_back():
     class Failing(ScriptedBackend):
         def run(self, h, rows, tokens):
-            if len(self.log) >= 2:
+            if self.steps >= 2:
                 raise RuntimeError("boom")
             return super().run(h, rows, tokens)
 
@@ -136,14 +166,18 @@ class HashBackend(ScriptedBackend):
     """The next token is a function of everything the sequence has been fed so far (as with a real model), so a
     token fed twice, skipped or given to the wrong row changes all that follows."""
 
-    def open_batch(self, requests):
-        h = super().open_batch(requests)
-        h["seen"] = [[] for _ in requests]
-        h["used_tokens"] = 0
+    def open_table(self, n_rows, requests):
+        h = super().open_table(n_rows, requests)
+        h["seen"] = [[] for _ in range(n_rows)]
         return h
+
+    def admit(self, h, row, request):
+        super().admit(h, row, request)
+        h["seen"][row] = []
 
     def run(self, h, rows, tokens):
         assert len(set(rows)) == len(rows)
+        self.steps += 1
         out = []
         for r, t in zip(rows, tokens):
             assert r in h["open"] and len(t) >= 1

@@ -109,7 +109,7 @@ def test_dense_mlp(dtype, tol, act):
 
 
 def test_layernorm_part_and_embedding_and_head():
-    from vlrf_b200.parts import LayerNorm, LearnedAbsolutePositions, LMHead, TokenEmbedding
+    from vlrf_b200.parts import LayerNorm, LearnedAbsolutePositions, LMHead, TokenEmbedding, Workspace
     d, V, P, T = 48, 130, 40, 11
     gamma, beta = randn(d, seed=1) + 1, randn(d, seed=2)
     x = randn(T, d, seed=3) * 2
@@ -123,7 +123,7 @@ def test_layernorm_part_and_embedding_and_head():
     pos = torch.tensor([0, 1, 2, 3, 4, 5, 6, 0, 1, 38, 39], dtype=torch.int32)
 
     class Ctx:
-        tokens, tok_pos, dev_err = tok.to(DEV), pos.to(DEV), torch.zeros(1, dtype=torch.int32, device=DEV)
+        tokens, tok_pos, dev_err, ws = tok.to(DEV), pos.to(DEV), torch.zeros(1, dtype=torch.int32, device=DEV), Workspace(DEV)
 
     xe = torch.empty(T, d, device=DEV)
     emb(Ctx, xe)

@@ -75,7 +75,7 @@ def define_toys():
         return s
 
     def rand(cfg, gen):
-        return {t.name: (1.0 if ".n" in t.name or t.name == "nf" else 0.0) + 0.25 * torch.randn(t.shape, generator=gen)
+        return {t.name: (1.0 if ".n" in t.name or t.name == "nf" else 0.0) + 0.15 * torch.randn(t.shape, generator=gen)
                 for t in spec(cfg)}
 
     def build(cfg, weights, options):
@@ -131,8 +131,9 @@ def toy_truth(cfg, w, ids):
     return norm(x, W["nf"]) @ W["emb"].T
 
 
-def decode_and_compare(model, cfg, w, reqs, starts, tol, use_program):
-    """A prompt step, then a decode session of all requests to their ends; every step's logits against the toy's truth."""
+def decode_and_compare(model, cfg, w, reqs, starts, tol, use_program, worst=None):
+    """A prompt step, then a decode session of all requests to their ends; every step's logits against the toy's truth
+    (with `worst`, a list, the largest error is put there instead of being held against `tol`)."""
     from conftest import rel_err
     from vlrf_b200.engine import Engine, StepEntry
     from vlrf_b200.engine.decode import DecodeSession
@@ -149,7 +150,11 @@ def decode_and_compare(model, cfg, w, reqs, starts, tol, use_program):
         lg = sess.step().float().cpu()
         for i, r in enumerate(reqs):
             if at[i] < len(r):
-                assert rel_err(lg[i], truth[i][at[i]]) < tol, (i, at[i])
+                err = rel_err(lg[i], truth[i][at[i]])
+                if worst is not None:
+                    worst.append(err)
+                else:
+                    assert err < tol, (i, at[i], err)
                 at[i] += 1
                 if at[i] == len(r):
                     sess.end_row(i)
@@ -177,7 +182,7 @@ def test_a_norm_that_is_no_layernorm_is_never_computed_as_one(tmp_path, norm, dt
         assert sess.program is not None, sess.program_refused       # the RMS norm ran inside the program's products
 
 
-def test_a_part_that_rewrites_the_residual_silently_leaves_no_stale_statistics(tmp_path):
+def test_a_part_that_rewrites_the_residual_silently_leaves_no_stale_statistics(tmp_path, monkeypatch):
     import plain_gpt2 as plain
     from conftest import random_ids
     from vlrf_b200.engine import load_model
@@ -194,3 +199,9 @@ def test_a_part_that_rewrites_the_residual_silently_leaves_no_stale_statistics(t
     assert sess.program is None
     # the library's own layers do leave statistics, and the fused norm after them uses them
     assert model.layers[1].leaves_row_stats and not model.layers[0].leaves_row_stats
+    # and this test can fail: were the statistics kept across the silent part, the norm after it would be wrong
+    from vlrf_b200.csrc import ops
+    monkeypatch.setattr(ops.RowStats, "forget", lambda self: None)
+    worst = []
+    decode_and_compare(model, cfg, w, reqs, [10, 2, 8, 5], 3e-2, use_program=False, worst=worst)
+    assert max(worst) > 0.1

@@ -558,7 +558,7 @@ __global__ void penalties_kernel(float* __restrict__ logits, int ld, int V, cons
                                  const float* __restrict__ rep, const float* __restrict__ freq,
                                  const float* __restrict__ pres, const int* __restrict__ ngram) {
     const int row = blockIdx.x;
-    const int n = gen_len[row];
+    const int n = min(gen_len[row], gen_ld);       // a count beyond the row's width reads nothing beyond it
     if (n <= 0) return;
     const int* g = gen + (size_t)row * gen_ld;
     float* lg = logits + (size_t)row * ld;
@@ -632,7 +632,7 @@ extern "C" int vlrf_sample(const float* logits, int ld, int n_rows, int V, const
 extern "C" int vlrf_apply_penalties(float* logits, int ld, int n_rows, int V, const int* gen, int gen_ld,
                                     const int* gen_len, const float* rep, const float* freq,
                                     const float* pres, const int* ngram, cudaStream_t stream) {
-    VLRF_REQUIRE(n_rows >= 0 && V > 0 && ld >= V && gen_ld >= 0, "penalties: bad sizes");
+    VLRF_REQUIRE(n_rows >= 0 && V > 0 && ld >= V && gen_ld > 0, "penalties: bad sizes (the history needs a width)");
     if (n_rows == 0) return VLRF_OK;
     penalties_kernel<<<n_rows, 256, 0, stream>>>(logits, ld, V, gen, gen_ld, gen_len, rep, freq, pres, ngram);
     return vlrf_check_launch("penalties");

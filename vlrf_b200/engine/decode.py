@@ -27,13 +27,13 @@ class DecodeSession:
     def __init__(self, engine: Engine, slots: list, *, use_graph: bool = True, pad_to: int | None = None,
                  use_program: bool | None = None):
         self.engine, self.model = engine, engine.model
-        self.slots = list(slots)
+        self.slots = list(slots)         # a row's cache slot, or None for a row that holds no sequence (yet)
         self.n = len(slots)
         self.rows = pad_to if pad_to is not None else self.n
         if self.rows < self.n:
             raise ValueError("pad_to is smaller than the number of sequences")
         dev = engine.device
-        self.live = [True] * self.n
+        self.live = [s is not None for s in self.slots]
         self.tokens = torch.zeros(self.rows, dtype=torch.int32, device=dev)
         self.tok_slot = torch.full((self.rows,), -1, dtype=torch.int32, device=dev)
         self.tok_pos = torch.zeros(self.rows, dtype=torch.int32, device=dev)
@@ -78,8 +78,8 @@ class DecodeSession:
         c = self.engine.cache
         slot = [s if live else -1 for s, live in zip(self.slots, self.live)] + [-1] * (self.rows - self.n)
         pos = [c.lengths[s] if live else 0 for s, live in zip(self.slots, self.live)] + [0] * (self.rows - self.n)
-        self.tok_slot.copy_(torch.tensor(slot, dtype=torch.int32))
-        self.tok_pos.copy_(torch.tensor(pos, dtype=torch.int32))
+        self.tok_slot.copy_(torch.tensor(slot, dtype=torch.int32), non_blocking=False)
+        self.tok_pos.copy_(torch.tensor(pos, dtype=torch.int32), non_blocking=False)
 
     def set_tokens(self, tokens) -> None:
         """The tokens to feed at the next step: a device int32 tensor [n] or a host list."""
@@ -145,6 +145,18 @@ class DecodeSession:
         self.engine.steps_run += 1
         return self.logits
 
+    def take_row(self, row: int, slot: int) -> None:
+        """A free row takes the sequence in `slot` (which already holds its prompt); `sync_tables()` must follow
+        before the next step."""
+        if self.live[row]:
+            raise ValueError(f"row {row} still holds a sequence")
+        self.slots[row], self.live[row] = slot, True
+
+    def sync_tables(self) -> None:
+        """Bring the device's row tables (slot and position of every row) up to the cache's books: after rows were
+        taken, or after steps that ran outside the session."""
+        self._sync_tables()
+
     def end_row(self, row: int) -> None:
         """The sequence of this row has ended; its row becomes padding.  (The slot is the caller's to free.)"""
         self.live[row] = False
@@ -169,7 +181,8 @@ class DecodeSession:
             seq_slot=self.tok_slot, seq_start=self.seq_start, seq_pos0=self.tok_pos, max_new=1,
             max_context=self.model.max_seq_len if self.use_graph else most, logit_rows=self.logit_rows,
             n_logit_rows=self.rows, act_dtype=self.model.act_dtype, dev_err=self.engine.dev_err, ws=self.ws,
-            host_seq_slots=list(self.slots), host_seq_lens=[1] * self.rows, host_seq_pos0=[])
+            host_seq_slots=[s if live else -1 for s, live in zip(self.slots, self.live)], host_seq_lens=[1] * self.rows,
+            host_seq_pos0=[])
 
     def step(self, advance_on_device: bool = True) -> torch.Tensor:
         """One decode step of all rows from `self.tokens`; returns float32 logits [rows, vocab] (static

@@ -15,12 +15,15 @@ class RowSampler:
     row of `logits`, appends it to the row's history, and returns the tokens as a device tensor.
     """
 
-    def __init__(self, params: list, keys: list, device, max_history: int):
+    def __init__(self, params: list, keys: list, device, max_history: int, *, any_sampling: bool | None = None,
+                 any_penalties: bool | None = None):
+        """`any_sampling` / `any_penalties`: what the rows must be able to do even if none of `params` asks for it
+        now (rows are given to other requests later, see `set_row`); by default what `params` ask for."""
         n = len(params)
         self.n, self.device = n, torch.device(device)
         self.params = list(params)
-        self.any_sampling = any(not p.greedy for p in params)
-        self.any_penalties = any(p.has_penalties for p in params)
+        self.any_sampling = any(not p.greedy for p in params) if any_sampling is None else bool(any_sampling)
+        self.any_penalties = any(p.has_penalties for p in params) if any_penalties is None else bool(any_penalties)
         f32 = lambda vals: torch.tensor(vals, dtype=torch.float32, device=self.device)  # noqa: E731
         i32 = lambda vals: torch.tensor(vals, dtype=torch.int32, device=self.device)    # noqa: E731
         self.temperature = f32([0.0 if p.greedy else p.temperature for p in params])
@@ -36,6 +39,24 @@ class RowSampler:
             self.history = torch.zeros((n, max(1, max_history)), dtype=torch.int32, device=self.device)
             self.history_len = torch.zeros(n, dtype=torch.int32, device=self.device)
         self.out = torch.zeros(n, dtype=torch.int32, device=self.device)
+
+    def set_row(self, row: int, params, key: int) -> None:
+        """The row goes to another request: its options, a fresh random stream and an empty history.  The tensors stay
+        where they are (a captured step reads them), only the row's entries change."""
+        if (not params.greedy and not self.any_sampling) or (params.has_penalties and not self.any_penalties):
+            raise ValueError("the sampler was set up without what this request's options need")
+        self.params[row] = params
+        self.temperature[row] = 0.0 if params.greedy else params.temperature
+        self.top_k[row] = params.top_k
+        self.top_p[row] = params.top_p
+        self.rng_key[row] = as_signed64(key)
+        self.rng_ctr[row] = 0
+        if self.any_penalties:
+            self.rep[row] = params.repetition_penalty
+            self.freq[row] = params.frequency_penalty
+            self.pres[row] = params.presence_penalty
+            self.ngram[row] = params.no_repeat_ngram_size
+            self.history_len[row] = 0
 
     def sample(self, logits: torch.Tensor, rows: list, *, next_pos=None, row_slot=None) -> torch.Tensor:
         """logits [len(rows), vocab] float32; rows: which requests these logits belong to, in order.
@@ -62,7 +83,10 @@ class RowSampler:
             ops.sample(logits, m, out, next_pos=next_pos, row_slot=row_slot)
         if self.any_penalties:
             r = torch.arange(self.n, device=self.device) if all_rows else idx
+            # a row whose history is full overwrites its last entry and counts no further (rows that hold no request are
+            # sampled along in a decode session and would count without end)
             at = self.history_len.index_select(0, r).long().clamp_(max=self.history.shape[1] - 1)
             self.history[r, at] = out.to(torch.int32)
             self.history_len.index_add_(0, r, torch.ones(m, dtype=torch.int32, device=self.device))
+            self.history_len.clamp_(max=self.history.shape[1])
         return out
