@@ -68,14 +68,14 @@ def test_prompts_from_text_ids_and_file(tmp_path):
 
     from vlrf_b200.cli import _prompts
     ns = argparse.Namespace(prompts_file=None, prompt_ids=None, prompt="Hi!")
-    assert _prompts(ns, 512) == [[ord("H") + 4, ord("i") + 4, ord("!") + 4]]         # byte + 4, as the reference without a tokenizer
-    assert _prompts(argparse.Namespace(prompts_file=None, prompt_ids=None, prompt="\xff"), 100) == [[99, 99]]   # capped at the vocabulary
-    assert _prompts(argparse.Namespace(prompts_file=None, prompt_ids="5, 17,3", prompt=None), 512) == [[5, 17, 3]]
+    # byte + 4, as the reference without a tokenizer; the cap at the vocabulary follows once the model is loaded
+    assert _prompts(ns) == ([[ord("H") + 4, ord("i") + 4, ord("!") + 4]], True)
+    assert _prompts(argparse.Namespace(prompts_file=None, prompt_ids="5, 17,3", prompt=None)) == ([[5, 17, 3]], False)
     f = tmp_path / "p.txt"
     f.write_text("1 2 3\n\n4,5\n")
-    assert _prompts(argparse.Namespace(prompts_file=str(f), prompt_ids=None, prompt=None), 512) == [[1, 2, 3], [4, 5]]
+    assert _prompts(argparse.Namespace(prompts_file=str(f), prompt_ids=None, prompt=None)) == ([[1, 2, 3], [4, 5]], False)
     with pytest.raises(SystemExit):
-        _prompts(argparse.Namespace(prompts_file=None, prompt_ids=None, prompt=None), 512)
+        _prompts(argparse.Namespace(prompts_file=None, prompt_ids=None, prompt=None))
 
 
 @pytest.mark.gpu

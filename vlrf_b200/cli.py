@@ -46,30 +46,31 @@ def _add_run_options(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
 
 
-def _prompts(args, vocab_size: int) -> list:
+def _prompts(args) -> tuple[list, bool]:
+    """(prompts, whether they are bytes of --prompt text that still want the cap at the vocabulary)."""
     if args.prompts_file:
         out = []
         for line in Path(args.prompts_file).read_text().splitlines():
             line = line.strip()
             if line:
                 out.append([int(t) for t in line.replace(",", " ").split()])
-        return out
+        return out, False
     if args.prompt_ids is not None:
-        return [[int(t) for t in args.prompt_ids.replace(",", " ").split()]]
+        return [[int(t) for t in args.prompt_ids.replace(",", " ").split()]], False
     if args.prompt is not None:
-        return [[min(b + 4, vocab_size - 1) for b in args.prompt.encode("utf-8")]]
+        return [[b + 4 for b in args.prompt.encode("utf-8")]], True
     raise SystemExit("run: give --prompt, --prompt-ids or --prompts-file")
 
 
 def cmd_run(args) -> int:
     from . import Model, SamplingParams
-    from .config.base import read_config_json
-    vocab = int(read_config_json(args.model).get("vocab_size", 0))
-    prompts = _prompts(args, vocab)
+    prompts, from_text = _prompts(args)
     need = sum((len(p) + args.tokens + 63) // 64 * 64 for p in prompts)
     print(f"Loading model from {args.model} ...")
     model = Model.load(args.model, dtype=args.dtype, max_tokens=args.ctx if args.ctx > 0 else need)
     print(model.model_summary())
+    if from_text:       # bytes beyond the vocabulary become its last id (src/api/vlrf_api.cpp:373-381)
+        prompts = [[min(t, model.decoder.vocab_size - 1) for t in p] for p in prompts]
     params = SamplingParams(
         max_new_tokens=args.tokens, temperature=args.temp, top_k=args.top_k, top_p=args.top_p,
         do_sample=not args.greedy, repetition_penalty=args.repeat_penalty, frequency_penalty=args.freq_penalty,
