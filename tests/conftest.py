@@ -26,12 +26,50 @@ TINY_C = dict(model_type="gpt2", n_layer=2, n_embd=192, n_head=3, n_inner=None, 
 TINY_D = dict(model_type="gpt2", n_layer=2, n_embd=80, n_head=5, n_inner=136, vocab_size=333, n_positions=160,
               layer_norm_epsilon=1e-5, activation_function="gelu_new", scale_attn_by_inverse_layer_idx=True,
               tie_word_embeddings=True, bos_token_id=3, eos_token_id=4)
-TINY = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C, "tiny_d": TINY_D}
+#: a fifth one whose attention is sharp: the q/k/v projection is drawn six times larger (standard deviation 0.12
+#: instead of 0.02), so that the scaled scores have a standard deviation of about 2 instead of 0.04 and a wrong scale,
+#: mask edge or far key moves the logits by far more than rounding does (fifteen times larger, scores of deviation
+#: 11, made bfloat16's own rounding of q and k worth 8 % of the logit scale: that tests nothing); head size 64 as the
+#: serving kernels want it, three layers with the per-layer scale
+TINY_SHARP = dict(model_type="gpt2", n_layer=3, n_embd=128, n_head=2, n_inner=352, vocab_size=611, n_positions=384,
+                  layer_norm_epsilon=1e-5, activation_function="gelu_new", scale_attn_by_inverse_layer_idx=True,
+                  tie_word_embeddings=True, bos_token_id=7, eos_token_id=8)
+SHARP_FACTOR = 6.0
+TINY = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C, "tiny_d": TINY_D, "tiny_sharp": TINY_SHARP}
 
-#: tolerances, fixed before the first measurement: the largest absolute logit error over the logit scale
-#: (largest absolute logit of the plain implementation)
+#: Tolerances: the largest absolute logit error over the logit scale (largest absolute logit of the plain
+#: implementation).  The 32-bit bound was fixed before the first measurement (measured since: 4e-6 at worst).  The
+#: bfloat16 bound is twice the worst error that the engine tests measured over all their drives and GPT-2 models
+#: (7.5e-3, at the model with sharp attention; 5.0e-3 for GPT-2 small at its full depth of 12 layers; the tests write
+#: what they measure to gpurun_out/logit_errors.json, see `record_error`); it was 3e-2 before anything had been measured.
 TOL_F32 = 1e-4
-TOL_BF16 = 3e-2
+TOL_BF16 = 1.5e-2
+
+_ERRORS: dict = {}
+
+
+def record_error(drive: str, model: str, dtype: str, worst: float) -> None:
+    """Remember the worst error of a comparison; the session writes them all to a file when it ends."""
+    key = f"{drive} | {model} | {dtype}"
+    _ERRORS[key] = max(_ERRORS.get(key, 0.0), float(worst))
+
+
+def pytest_sessionfinish(session, exitstatus):
+    if not _ERRORS:
+        return
+    import json
+    import os
+    out_dir = ROOT / "gpurun_out"
+    try:
+        out_dir.mkdir(exist_ok=True)
+        by_dtype = {}
+        for k, v in _ERRORS.items():
+            dt = k.rsplit(" | ", 1)[1]
+            by_dtype[dt] = max(by_dtype.get(dt, 0.0), v)
+        (out_dir / "logit_errors.json").write_text(json.dumps({"worst_by_dtype": by_dtype, "by_drive": dict(sorted(_ERRORS.items()))},
+                                                              indent=1) + "\n")
+    except OSError:
+        pass
 
 
 def pytest_configure(config):
@@ -55,9 +93,28 @@ def model_dirs(tmp_path_factory):
     out = {}
     for i, (name, cfg) in enumerate(TINY.items()):
         d = tmp_path_factory.mktemp(name)
-        write_random_model(cfg, 100 + i, d)
+        if name == "tiny_sharp":
+            write_sharp_model(cfg, 100 + i, d)
+        else:
+            write_random_model(cfg, 100 + i, d)
         out[name] = d
     return out
+
+
+def write_sharp_model(cfg: dict, seed: int, out_dir) -> None:
+    """The random-weights draw with every q/k/v projection matrix made SHARP_FACTOR times larger."""
+    import json
+    from vlrf_b200.registry import parse_config
+    from vlrf_b200.weights import write_safetensors
+    arch, parsed = parse_config(cfg)
+    gen = torch.Generator().manual_seed(seed)
+    tensors = arch.random_weights(parsed, gen)
+    for name in tensors:
+        if name.endswith("attn.c_attn.weight"):
+            tensors[name] = tensors[name] * SHARP_FACTOR
+    Path(out_dir).mkdir(parents=True, exist_ok=True)
+    (Path(out_dir) / "config.json").write_text(json.dumps(cfg, indent=2))
+    write_safetensors(Path(out_dir) / "model.safetensors", {k: v.to(torch.bfloat16) for k, v in tensors.items()})
 
 
 @pytest.fixture(scope="session")

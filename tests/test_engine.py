@@ -4,7 +4,7 @@ import pytest
 import torch
 
 import plain_gpt2 as plain
-from conftest import TOL_BF16, TOL_F32, random_ids, rel_err
+from conftest import TOL_BF16, TOL_F32, random_ids, record_error, rel_err
 from engine_drives import drive_batches, drive_tail_one_by_one, drive_whole, poison
 
 pytestmark = pytest.mark.gpu
@@ -12,7 +12,9 @@ pytestmark = pytest.mark.gpu
 DTYPES = [("float32", TOL_F32), ("bfloat16", TOL_BF16)]
 #: request lengths per model: prompts of 5/17/31 and 1/9/40/100 tokens with their decode steps added, and longer ones
 LENGTHS = {"tiny_a": [5 + 16, 17 + 16, 31 + 16, 70, 128], "tiny_b": [1 + 24, 9 + 24, 40 + 24, 100 + 24, 200, 256],
-           "tiny_c": [3 + 20, 64 + 20, 65 + 20, 127 + 20, 250, 320], "tiny_d": [2 + 12, 33 + 12, 64 + 12, 100, 160]}
+           "tiny_c": [3 + 20, 64 + 20, 65 + 20, 127 + 20, 250, 320], "tiny_d": [2 + 12, 33 + 12, 64 + 12, 100, 160],
+           "tiny_sharp": [4 + 20, 63 + 20, 130 + 20, 257, 384]}
+MODELS = ["tiny_a", "tiny_b", "tiny_c", "tiny_d", "tiny_sharp"]
 
 
 @pytest.fixture(scope="module")
@@ -32,7 +34,8 @@ def make_engine(model_dirs, name, dtype, max_tokens):
     return eng
 
 
-def compare(got, truth, tol, what):
+def compare(got, truth, tol, what, model="", dtype=""):
+    """Every position of every request within `tol`; the worst error is recorded under (what, model, dtype)."""
     worst = 0.0
     for i, (g, t) in enumerate(zip(got, truth)):
         assert g.shape == t.shape, f"{what}: request {i} has shape {tuple(g.shape)}, expected {tuple(t.shape)}"
@@ -43,32 +46,33 @@ def compare(got, truth, tol, what):
         assert bad.numel() == 0, (f"{what}: request {i} (length {len(t)}) first differs at position {int(bad[0])} "
                                   f"with error {float(err[bad[0]]):.3e} of the logit scale (tolerance {tol:.0e})")
         worst = max(worst, float(err.max()))
+    record_error(what, model, dtype or ("float32" if tol <= TOL_F32 else "bfloat16"), worst)
     return worst
 
 
 @pytest.mark.parametrize("dtype,tol", DTYPES)
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d"])
+@pytest.mark.parametrize("name", MODELS)
 def test_each_request_alone_and_whole(model_dirs, requests_and_truth, name, dtype, tol):
     reqs, truth = requests_and_truth[name]
-    eng = make_engine(model_dirs, name, dtype, 320)
-    compare(drive_whole(eng, reqs), truth, tol, "whole")
+    eng = make_engine(model_dirs, name, dtype, 384)
+    compare(drive_whole(eng, reqs), truth, tol, "whole", name)
     eng.cache.check()
     assert eng.cache.slots.n_held == 0
 
 
 @pytest.mark.parametrize("dtype,tol", DTYPES)
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d"])
+@pytest.mark.parametrize("name", MODELS)
 def test_last_32_tokens_one_by_one(model_dirs, requests_and_truth, name, dtype, tol):
     reqs, truth = requests_and_truth[name]
-    eng = make_engine(model_dirs, name, dtype, 320)
-    compare(drive_tail_one_by_one(eng, reqs, 32), truth, tol, "prefix + 32 single tokens")
+    eng = make_engine(model_dirs, name, dtype, 384)
+    compare(drive_tail_one_by_one(eng, reqs, 32), truth, tol, "prefix + 32 single tokens", name)
 
 
 @pytest.mark.parametrize("dtype,tol", DTYPES)
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d"])
+@pytest.mark.parametrize("name", MODELS)
 def test_unequal_batches_one_after_another(model_dirs, requests_and_truth, name, dtype, tol):
     reqs, truth = requests_and_truth[name]
-    decode = {"tiny_a": 16, "tiny_b": 24, "tiny_c": 20, "tiny_d": 12}[name]
+    decode = {"tiny_a": 16, "tiny_b": 24, "tiny_c": 20, "tiny_d": 12, "tiny_sharp": 20}[name]
     prompt_lens = [max(1, len(r) - decode) for r in reqs]
     # a cache just large enough for one batch: the second batch must reuse slots and blocks of the first
     batch = 3 if name == "tiny_a" else 4
@@ -80,11 +84,11 @@ def test_unequal_batches_one_after_another(model_dirs, requests_and_truth, name,
     need = max(need_of(reqs), need_of([reqs[i] for i in order]))
     eng = make_engine(model_dirs, name, dtype, need)
     got = drive_batches(eng, reqs, batch, prompt_lens)
-    compare(got, truth, tol, "unequal batches")
+    compare(got, truth, tol, "unequal batches", name)
     assert eng.cache.slots.n_held == 0
     # the same again in another order: every slot and block has been used before
     got2 = drive_batches(eng, [reqs[i] for i in order], batch, [prompt_lens[i] for i in order])
-    compare(got2, [truth[i] for i in order], tol, "unequal batches, reused cache")
+    compare(got2, [truth[i] for i in order], tol, "unequal batches, reused cache", name)
 
 
 @pytest.mark.parametrize("dtype,tol", DTYPES)
@@ -98,14 +102,14 @@ def test_long_decoding_from_one_token(model_dirs, plain_models, dtype, tol):
 
 
 @pytest.mark.parametrize("dtype,tol", DTYPES)
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d"])
+@pytest.mark.parametrize("name", MODELS)
 def test_first_tokens(model_dirs, plain_models, name, dtype, tol):
     cfg, w = plain_models[name]
     reqs = [random_ids(cfg["vocab_size"], n, 50 + n) for n in (1, 2, 3, 1)]
     truth = [plain.logits_all_positions(cfg, w, ids) for ids in reqs]
     eng = make_engine(model_dirs, name, dtype, 256)
-    compare(drive_whole(eng, reqs), truth, tol, "first tokens, whole")
-    compare(drive_batches(eng, reqs, 4, [1, 1, 1, 1]), truth, tol, "first tokens, batch")
+    compare(drive_whole(eng, reqs), truth, tol, "first tokens, whole", name)
+    compare(drive_batches(eng, reqs, 4, [1, 1, 1, 1]), truth, tol, "first tokens, batch", name)
 
 
 @pytest.mark.parametrize("dtype,tol", DTYPES)
@@ -118,7 +122,7 @@ def test_a_batch_of_a_hundred_sequences(model_dirs, plain_models, name, dtype, t
     truth = [plain.logits_all_positions(cfg, w, ids) for ids in reqs]
     eng = make_engine(model_dirs, name, dtype, 64 * len(reqs))
     got = drive_batches(eng, reqs, len(reqs), [max(1, len(r) - 10) for r in reqs])
-    compare(got, truth, tol, "a batch of 100")
+    compare(got, truth, tol, "a batch of 100", name)
     assert eng.cache.slots.n_held == 0
 
 

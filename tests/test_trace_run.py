@@ -89,3 +89,32 @@ def test_replay_whole_tail_and_batches(model_dirs, plain_models, tmp_path, dtype
                 fed[k] += 1
             live = [k for k in live if k not in ending]
     rp.close()
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", TOL_F32), ("bfloat16", TOL_BF16)])
+def test_replay_of_prompts_that_arrive_in_portions(model_dirs, plain_models, tmp_path, dtype, tol):
+    """40 tokens of a request, then 30 more in a step that also starts another request, then single tokens: the
+    replay program takes such a schedule, and the logits are those of the whole sequences."""
+    cfg, w = plain_models["tiny_c"]
+    V = cfg["vocab_size"]
+    a, b = random_ids(V, 75, 31), random_ids(V, 20, 32)
+    ta, tb = plain.logits_all_positions(cfg, w, a), plain.logits_all_positions(cfg, w, b)
+
+    def close_enough(got, want, what):
+        err = float((got.double() - want).abs().max() / want.abs().max())
+        assert got.shape == want.shape and err < tol, (what, err)
+
+    rp = Replay(model_dirs["tiny_c"], dtype, tmp_path / "out", 64 * 3)
+    f = rp.send([{"id": "a", "tokens": a[:40], "want": [0, 39]}])
+    close_enough(read(f, V), ta[[0, 39]], "first portion")
+    f = rp.send([{"id": "a", "tokens": a[40:70], "want": [0, 29]}, {"id": "b", "tokens": b[:15], "want": [14]}])
+    got = read(f, V)
+    close_enough(got[:2], ta[[40, 69]], "second portion")
+    close_enough(got[2:], tb[[14]], "a new request beside it")
+    for j in range(5):
+        f = rp.send([{"id": "a", "tokens": [a[70 + j]], "want": [0]}, {"id": "b", "tokens": [b[15 + j]], "want": [0]}],
+                    end=["a", "b"] if j == 4 else [])
+        got = read(f, V)
+        close_enough(got[:1], ta[[70 + j]], f"a at {70 + j}")
+        close_enough(got[1:], tb[[15 + j]], f"b at {15 + j}")
+    rp.close()

@@ -1,12 +1,14 @@
 """The decode-attention entry point that allocates nothing (vlrf_attn_decode_noalloc).
 
-Some users of the kernel library cannot call cudaMalloc where they call attention: they are inside a
-stream capture, in a loop that must never touch the allocator, or they are handed only inputs and
-outputs.  For them the library carries the scratch memory of the split-context attention inside itself.
+Some users of the kernel library cannot call cudaMalloc where they call attention: they are in a loop
+that must never touch the allocator, their memory plan is fixed up front, or they are handed only inputs
+and outputs.  For them the library carries the scratch memory of the split-context attention inside itself.
 This test calls that entry point the way such a user would — through its exported C symbol, with raw
 pointers — twice in a row, and checks each result against the ordinary entry point (which takes the
-scratch from the caller) within the tolerance the other kernel tests use.  It is collected last, so a run
-that stops at the first failure has already run everything else; it also passes when run alone.
+scratch from the caller) and against the plain attention, within the tolerance the other kernel tests use;
+then a third call of a smaller shape with another split count, which finds the scratch as the larger calls
+left it.  It is collected last, so a run that stops at the first failure has already run everything else;
+it also passes when run alone.
 """
 import ctypes
 import math
@@ -49,7 +51,8 @@ def test_no_alloc_entry_point_matches_the_ordinary_one(dtype, tol, rows, H, Hkv,
     scale = 1.0 / math.sqrt(dh)
     err = torch.zeros(1, dtype=torch.int32, device=DEV)
     stream = torch.cuda.current_stream().cuda_stream
-    for call in range(2):                                  # two calls in a row share the built-in scratch
+    shapes = [(rows, H, Hkv, dh, ctx, n_split)] * 2 + [(max(1, rows // 2), H, Hkv, dh, max(65, ctx // 3), max(1, n_split - 1))]
+    for call, (rows, H, Hkv, dh, ctx, n_split) in enumerate(shapes):   # calls in a row share the built-in scratch
         kc, vc, table, slot, pos, qkv = _case(dtype, rows, H, Hkv, dh, ctx, 100 + call)
         want = torch.full((rows, H * dh), float("nan"), dtype=dtype, device=DEV)
         partials = torch.empty(rows * H * n_split * (dh + 2), device=DEV)
@@ -65,6 +68,19 @@ def test_no_alloc_entry_point_matches_the_ordinary_one(dtype, tol, rows, H, Hkv,
         assert torch.isfinite(got.float()).all()
         diff = (got.float() - want.float()).abs().max() / want.float().abs().max()
         assert float(diff) < tol, (call, float(diff))
+        # and against the plain attention on the same keys and values (not only against the other entry point)
+        import plain_gpt2 as plain
+        for r in range(rows):
+            n = int(pos[r]) + 1
+            blocks = table[r].cpu().tolist()
+            k = torch.cat([kc[b].cpu().double() for b in blocks], dim=1)[:, :n]
+            v = torch.cat([vc[b].cpu().double() for b in blocks], dim=1)[:, :n]
+            rep = H // Hkv
+            q = torch.zeros(H, n, dh, dtype=torch.float64)
+            q[:, n - 1] = qkv[r, :H * dh].cpu().double().view(H, dh)
+            ref = plain.causal_attention(q, k.repeat_interleave(rep, 0), v.repeat_interleave(rep, 0), scale)[:, n - 1]
+            err_plain = (got[r].cpu().double().view(H, dh) - ref).abs().max() / ref.abs().max()
+            assert float(err_plain) < tol, (call, r, float(err_plain))
     assert int(err.item()) == 0
 
 

@@ -2,7 +2,7 @@
 //
 // A decode step has few queries (rows × heads), far fewer than the GPU has SMs, and each has a long
 // stream of keys and values to read; so the keys 0…position of a (row, head) are cut into `n_split`
-// contiguous parts, one CTA each.  Inside a CTA four warps take the 32-key chunks of the part in turn
+// contiguous parts, one CTA each.  Inside a CTA eight warps take the 32-key chunks of the part in turn
 // and each keeps a running (max, sum, weighted V sum) in float32 (reference:
 // include/model/attention.hpp:265-307); the warps' results are merged in shared memory, and the CTA
 // writes its partial (max, sum, sum·V) to scratch memory.  For head sizes 64 and 128 the keys and values

@@ -3,9 +3,9 @@
 // This entry point has no counterpart in the reference (VLRF-org/VLRF has no GPU allocator to avoid and no
 // split-context attention); it exists for users of this library.
 //
-// Who needs it: code that runs where cudaMalloc is off limits — inside a stream capture, inside a
-// real-time or latency-critical loop that must not take the allocator's locks, in a host process whose
-// memory plan is fixed up front, or a plugin that is handed inputs and outputs but no allocator.  The
+// Who needs it: code that runs where cudaMalloc is off limits — inside a real-time or latency-critical
+// loop that must not take the allocator's locks, in a host process whose memory plan is fixed up front, or
+// a plugin that is handed inputs and outputs but no allocator.  The
 // ordinary entry point, vlrf_attn_decode, needs scratch memory from its caller when a context is cut into
 // several parts (partial results of the parts, and a counter per (row, head)); such callers have nowhere
 // to get it from.  Here the scratch is a fixed array inside the library itself, so the caller passes only
@@ -25,8 +25,11 @@
 //     streams, no ordering between them) race on the scratch and give wrong results: order them.
 //   * Nothing is allocated or freed: no cudaMalloc, no cudaFree, no library routine that allocates.
 //
-// Arguments are those of vlrf_attn_decode without `partials` and `counters`; returns 0 or a status whose
-// text vlrf_last_error() gives.
+// Arguments are those of vlrf_attn_decode without `n_blocks`, `partials` and `counters`; returns 0 or a
+// status whose text vlrf_last_error() gives.  Without the pool's block count no tensor map of the cache can
+// be made, so bfloat16 with head size 64 runs here on the kernel that copies keys and values in bulk and
+// multiplies on the CUDA cores, not on the `mma.sync` kernel that vlrf_attn_decode picks for those sizes:
+// the same sums in another order, equal within rounding, and slower.
 #pragma once
 #include <cuda_runtime.h>
 
