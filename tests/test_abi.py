@@ -70,7 +70,9 @@ def test_every_entry_point_that_python_calls_exists():
         if path.name != Path(__file__).name:
             used |= set(pattern.findall(path.read_text()))
     assert len(used) >= 20
-    missing = sorted(u for u in used if u not in defs)
+    # (names of the model-level C interface are held against its header; its definitions are C++, not in the table)
+    capi = (SRC.parent / "capi" / "vlrf_b200_api.cpp").read_text()
+    missing = sorted(u for u in used if u not in defs and not (u.startswith("vlrf_b200_") and re.search(rf"\b{u}\(", capi)))
     assert not missing, f"called from Python but defined in no source: {missing}"
 
 

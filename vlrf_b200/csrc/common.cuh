@@ -45,11 +45,16 @@ cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    // every kernel of a step asks for the same split of an SM's memory between shared memory and L1 (all of
+    // it shared): an SM changes the split only when it is empty, which would keep kernels that want different
+    // splits from running side by side
+    attr[0].id = cudaLaunchAttributePreferredSharedMemoryCarveout;
+    attr[0].val.sharedMemCarveout = cudaSharedmemCarveoutMaxShared;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = vlrf_chained_launch_enabled() ? 1 : 0;
+    cfg.numAttrs = vlrf_chained_launch_enabled() ? 2 : 1;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
@@ -63,15 +68,17 @@ cudaError_t launch_chained_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 blo
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
+    cudaLaunchAttribute attr[3];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = cluster.x;
     attr[0].val.clusterDim.y = cluster.y;
     attr[0].val.clusterDim.z = cluster.z;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributePreferredSharedMemoryCarveout;
+    attr[1].val.sharedMemCarveout = cudaSharedmemCarveoutMaxShared;
+    attr[2].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[2].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = vlrf_chained_launch_enabled() ? 2 : 1;
+    cfg.numAttrs = vlrf_chained_launch_enabled() ? 3 : 2;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
