@@ -7,14 +7,15 @@
 // layer's matrices have only N/128 such tiles, too few to keep HBM busy, so the grid is tiles × splits and
 // the `splits` CTAs of a tile form a thread-block cluster: CTA (tile, s) streams the 64-wide k blocks of
 // part s through a ring of shared-memory stages (TMA, 128-byte swizzle), one elected thread issues
-// `tcgen05.mma` per block, and the partial tile is put into the CTA's own shared memory.  After a cluster
-// barrier the warps of all CTAs of the cluster share the tile's (row, 32-column) pieces among them; a warp
-// reads its piece from every CTA's shared memory (distributed shared memory) and adds the parts in the
-// order of s, so the result does not depend on timing; it then applies bias, GELU and the residual sum
-// (reference include/model/feedforward.hpp:54-76, include/model/transformer_block.hpp:153,158), stores
-// the piece and, for a fused q/k/v projection, scatters K and V columns into the paged cache (reference
-// include/model/kv_cache.hpp:215-251).  A second cluster barrier keeps every CTA's shared memory alive
-// until its neighbours have read it.
+// `tcgen05.mma` per block.  The finished tile is dealt to the warps of all CTAs of the cluster in pieces (a row,
+// 32 columns); every CTA sends each piece of its partial tile into the shared memory of the CTA whose warp
+// finishes that piece, as stores that count down a barrier there (`st.async`), so a piece crosses the cluster
+// once and nobody waits at a cluster barrier or reads another CTA's memory on the way.  The receiving warp
+// adds the parts in the order of their CTAs, so the result does not depend on timing; it then applies bias, GELU
+// and the residual sum (reference include/model/feedforward.hpp:54-76,
+// include/model/transformer_block.hpp:153,158), stores the piece and, for a fused q/k/v projection, scatters K
+// and V columns into the paged cache (reference include/model/kv_cache.hpp:215-251).  A CTA leaves when it has
+// received all it is due, which is after everyone has stopped writing to it.
 //
 // A tile may also have 64 rows of W only (twice as many tiles for narrow matrices): the MMA still works on
 // 128 rows, the upper 64 being whatever follows in shared memory, and the upper 64 lanes of the accumulator
@@ -26,8 +27,8 @@
 // have produced, while the weight copies are already in flight.
 //
 // Launched "chained": weights are requested before the kernel ahead has finished, activations only after.
-// Every wait on an mbarrier is bounded; a CTA that gives up sets the device error word, still meets its
-// cluster at both barriers and frees its tensor memory.
+// Every wait on an mbarrier is bounded; a CTA that gives up sets the device error word, sends nothing (its
+// receivers then give up too, after their own bounded wait) and frees its tensor memory.
 #include "common.cuh"
 #include "tma.cuh"
 #include "tcgen05.cuh"
@@ -48,6 +49,83 @@ struct SpKvScatter {
     const int* block_table; const int* tok_slot; const int* tok_pos;
     int max_blocks, k_off, v_off, width, dh, Hkv, BT;
 };
+
+// One warp norms its CTA's k range [k_lo, k_hi) of one float32 row and writes it as bfloat16 into shared memory in
+// the layout TMA would have produced (128-byte swizzle, a tile of 64 columns after the other).  JV: float4 a lane
+// of the range (32 lanes × 4 columns each); JG: 32-column segments a lane of the row's statistics.  Both are
+// template arguments so that a warp executes no instruction for pieces it does not have: the norm lies on the
+// product's critical path and is executed by single warps, at the latency of every instruction.
+// The row's mean and variance come from the per-segment sums that the kernel which wrote the row left: sum and
+// squared deviation from the segment's own mean; segments combine exactly (M2 = Σ M2_g + n_g·(mean_g − mean)²),
+// in a fixed order (reference include/model/ops.hpp:443-476 for the norm itself).
+template <int JV, int JG>
+__device__ __forceinline__ void sp_norm_row(const float* __restrict__ row, const float* __restrict__ st, int lane, int m,
+                                            int k_lo, int k_hi, int K, int G, float inv_K, float eps,
+                                            const float* s_gamma, const float* s_beta, unsigned char* b_tiles, int b_bytes) {
+    // this CTA's k range of the row: requested first, used after the statistics
+    float4 v[JV];
+#pragma unroll
+    for (int j = 0; j < JV; ++j) {
+        const int i = k_lo + (j * 32 + lane) * 4;
+        v[j] = (i < k_hi && i < K) ? *reinterpret_cast<const float4*>(row + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float sg[JG], qg[JG];
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < JG; ++j) {
+        const int g = j * 32 + lane;
+        sg[j] = 0.f; qg[j] = 0.f;
+        if (g < G) { const float2 t2 = *reinterpret_cast<const float2*>(st + 2 * g); sg[j] = t2.x; qg[j] = t2.y; }
+        s += sg[j];
+    }
+    const float mean = warp_sum(s) * inv_K;
+    float q = 0.f;
+#pragma unroll
+    for (int j = 0; j < JG; ++j) {
+        const int g = j * 32 + lane;
+        if (g < G) {
+            const float n_g = (float)min(32, K - g * 32);
+            const float dm = __fdividef(sg[j], n_g) - mean;
+            q += qg[j] + n_g * dm * dm;
+        }
+    }
+    const float inv = rsqrtf(warp_sum(q) * inv_K + eps);
+    // normalised; columns beyond K are zeros (W reads as zeros there too)
+#pragma unroll
+    for (int j = 0; j < JV; ++j) {
+        const int kl = (j * 32 + lane) * 4;
+        const int i = k_lo + kl;
+        if (i < k_hi) {
+            uint2 pk = make_uint2(0u, 0u);
+            if (i < K) {
+                const float4 gm = *reinterpret_cast<const float4*>(s_gamma + kl);
+                const float4 bt = *reinterpret_cast<const float4*>(s_beta + kl);
+                pk.x = pack2((v[j].x - mean) * inv * gm.x + bt.x, (v[j].y - mean) * inv * gm.y + bt.y);
+                pk.y = pack2((v[j].z - mean) * inv * gm.z + bt.z, (v[j].w - mean) * inv * gm.w + bt.w);
+            }
+            unsigned char* dst = b_tiles + (size_t)(kl >> 6) * b_bytes + m * 128 + ((((kl & 63) >> 3) ^ (m & 7)) << 4) + (kl & 7) * 2;
+            *reinterpret_cast<uint2*>(dst) = pk;
+        }
+    }
+}
+
+// Whether the finished tile is dealt out in pieces of 32 lanes × 4 columns (many rows) or 32 lanes × 1 column.
+__host__ __device__ inline bool sp_is_wide(int M, int bm, int splits, bool ln) { return !ln && M * (bm / 32) > 4 * 4 * splits; }
+// Floats of the buffer in which a CTA receives its warps' pieces from every part.
+__host__ __device__ inline int sp_recv_floats(int M, int bm, int splits, bool wide) {
+    const int rpp = 32 / (bm >> 2);
+    const int units = wide ? (M + rpp - 1) / rpp : M * (bm >> 5);
+    const int n_j = (units + 4 * splits - 1) / (4 * splits);
+    return splits * n_j * 4 * 32 * (wide ? 4 : 1);
+}
+// a float into the shared memory of CTA `rank` of the cluster (at the place `own_addr` has in this CTA), counted
+// down on the barrier at `own_bar`'s place there
+__device__ __forceinline__ void sp_send_f32(uint32_t own_addr, uint32_t own_bar, uint32_t rank, float v) {
+    uint32_t addr, bar;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(own_addr), "r"(rank));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(bar) : "r"(own_bar), "r"(rank));
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(addr), "r"(__float_as_uint(v)), "r"(bar) : "memory");
+}
 
 // bm: rows of W per tile (64 or 128); stages: depth of the ring; kb_cap: most k blocks of one part
 // WIDE: the pieces of the finished tile are 32 lanes × 4 columns (many rows) instead of 32 lanes × 1 column
@@ -72,8 +150,8 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     unsigned char* after_b = b_tiles + (size_t)(LN ? kb_cap : stages) * B_BYTES;
     float* s_gamma = reinterpret_cast<float*>(after_b);              // LN: [kb_cap·64] this part's norm weights
     float* s_beta = s_gamma + (LN ? kb_cap * SP_BK : 0);
-    // this CTA's part of the tile, written at the end: [m][bm] float32
-    float* part = s_beta + (LN ? kb_cap * SP_BK : 0);
+    // what this CTA receives of the tile: the pieces its warps finish, from every part of the sum (below)
+    float* recv = s_beta + (LN ? kb_cap * SP_BK : 0);
     // The finished tile is dealt to the 4·splits epilogue warps of the cluster in pieces of 32 lanes × 4
     // columns: one row of a 128-row tile, two rows of a 64-row tile.
     const int lpr = bm >> 2, rpp = 32 / lpr;                         // lanes a row, rows a piece
@@ -81,11 +159,19 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     // … unless that leaves most warps without a piece (few rows): then pieces of 32 lanes × 1 column
     const int segs = bm >> 5, units_n = M * segs;
     constexpr bool wide = WIDE;
-    uint64_t* full = reinterpret_cast<uint64_t*>(part + (size_t)M * bm);
+    // Every CTA of the cluster sends each piece of its partial tile to the CTA whose warp finishes that piece, as
+    // stores into that CTA's shared memory that count down a barrier there (`st.async`): recv[source part][piece of
+    // the warp j][warp][32 lanes × PW floats].  The receiver waits on its own barrier for all the bytes it is due
+    // and adds the parts in the order of their CTAs: one crossing of the cluster instead of a cluster barrier and a
+    // read of the others' memory, and nobody's shared memory is read by another CTA.
+    constexpr int PW = WIDE ? 4 : 1;
+    const int n_j = ((wide ? units : units_n) + ustride - 1) / ustride;   // pieces a warp
+    uint64_t* full = reinterpret_cast<uint64_t*>(recv + (size_t)sp_recv_floats(M, bm, (int)gridDim.y, WIDE));
     uint64_t* empty = full + SP_MAX_STAGES;
     uint64_t* acc_full = empty + SP_MAX_STAGES;
     uint64_t* x_ready = acc_full + 1;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(x_ready + 1);
+    uint64_t* recv_bar = x_ready + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(recv_bar + 1);
     int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
     int* s_kv_blk = s_abort + 1;                                     // [64]
     int* s_kv_row = s_kv_blk + 64;                                   // [64]
@@ -101,8 +187,15 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         for (int s = 0; s < stages; ++s) { tbar_init(&full[s], 1); tbar_init(&empty[s], 1); }
         tbar_init(acc_full, 1);
         tbar_init(x_ready, 8);
+        tbar_init(recv_bar, 1);
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // the bytes this CTA is due: its warps' pieces, once from every part
+        int floats = 0;
+        for (int w = 0; w < 4; ++w)
+            for (int u = split * 4 + w; u < (wide ? units : units_n); u += ustride)
+                floats += wide ? min(rpp, M - u * rpp) * bm : 32;
+        tbar_expect_tx(recv_bar, (uint32_t)(floats * splits * 4));
     }
     if (warp == 4) {
         if (lane == 0) { tma_prefetch_descriptor(&tmap_w); if (!LN) tma_prefetch_descriptor(&tmap_x); }
@@ -114,6 +207,8 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    // every CTA of the cluster has set up its receiving barrier before anyone sends (waited for further down)
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 
     // The weights do not depend on the kernel ahead: the first stages' tiles of W are requested at once, and
     // the norm's weights for this part's columns are copied to shared memory.
@@ -144,6 +239,8 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             s_beta[i] = k < K ? beta[k] : 0.f;
         }
     }
+    const float inv_K = 1.f / (float)K;
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     pdl_launch_dependents();
     pdl_wait();                                    // the rows of X, the residual and the positions are ready
 
@@ -188,58 +285,14 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             asm volatile("bar.sync 2, 256;" ::: "memory");     // the norm's weights are in shared memory
             const int k_lo = kb0 * SP_BK, k_hi = kb1 * SP_BK;
             const int G = (K + 31) >> 5;                       // 32-column segments of a row
+            const int jv = (n_kb * SP_BK + 127) >> 7, jg = (G + 31) >> 5;        // uniform over the CTA
             for (int m = lw; m < M; m += 8) {
                 const float* row = Xf + (size_t)m * ldx;
-                // this CTA's k range of the row: requested first, used after the statistics
-                float4 v[SP_LN_MAX_KB / 2];
-#pragma unroll
-                for (int j = 0; j < SP_LN_MAX_KB / 2; ++j) {
-                    const int i = k_lo + (j * 32 + lane) * 4;
-                    v[j] = (i < k_hi && i < K) ? *reinterpret_cast<const float4*>(row + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-                }
-                // The row's mean and variance from the per-segment sums that the kernel which wrote the row
-                // left: sum and squared deviation from the segment's own mean; segments combine exactly
-                // (M2 = Σ M2_g + n_g·(mean_g − mean)²), in a fixed order.
                 const float* st = stats_in + (size_t)m * G * 2;
-                float sg[SP_STAT_SEGS / 32], qg[SP_STAT_SEGS / 32];
-                float s = 0.f;
-#pragma unroll
-                for (int j = 0; j < SP_STAT_SEGS / 32; ++j) {
-                    const int g = j * 32 + lane;
-                    sg[j] = 0.f; qg[j] = 0.f;
-                    if (g < G) { const float2 t2 = *reinterpret_cast<const float2*>(st + 2 * g); sg[j] = t2.x; qg[j] = t2.y; }
-                    s += sg[j];
-                }
-                const float mean = warp_sum(s) / (float)K;
-                float q = 0.f;
-#pragma unroll
-                for (int j = 0; j < SP_STAT_SEGS / 32; ++j) {
-                    const int g = j * 32 + lane;
-                    if (g < G) {
-                        const float n_g = (float)min(32, K - g * 32);
-                        const float dm = sg[j] / n_g - mean;
-                        q += qg[j] + n_g * dm * dm;
-                    }
-                }
-                const float inv = 1.f / sqrtf(warp_sum(q) / (float)K + eps);
-                // normalised, in the swizzled layout of a TMA tile; columns beyond K are zeros (W reads as
-                // zeros there too)
-#pragma unroll
-                for (int j = 0; j < SP_LN_MAX_KB / 2; ++j) {
-                    const int kl = (j * 32 + lane) * 4;
-                    const int i = k_lo + kl;
-                    if (i < k_hi) {
-                        uint2 pk = make_uint2(0u, 0u);
-                        if (i < K) {
-                            const float4 gm = *reinterpret_cast<const float4*>(s_gamma + kl);
-                            const float4 bt = *reinterpret_cast<const float4*>(s_beta + kl);
-                            pk.x = pack2((v[j].x - mean) * inv * gm.x + bt.x, (v[j].y - mean) * inv * gm.y + bt.y);
-                            pk.y = pack2((v[j].z - mean) * inv * gm.z + bt.z, (v[j].w - mean) * inv * gm.w + bt.w);
-                        }
-                        unsigned char* dst = b_tiles + (size_t)(kl >> 6) * B_BYTES + m * 128 + ((((kl & 63) >> 3) ^ (m & 7)) << 4) + (kl & 7) * 2;
-                        *reinterpret_cast<uint2*>(dst) = pk;
-                    }
-                }
+                if (jv <= 1 && jg <= 1) sp_norm_row<1, 1>(row, st, lane, m, k_lo, k_hi, K, G, inv_K, eps, s_gamma, s_beta, b_tiles, B_BYTES);
+                else if (jv <= 2 && jg <= 2) sp_norm_row<2, 2>(row, st, lane, m, k_lo, k_hi, K, G, inv_K, eps, s_gamma, s_beta, b_tiles, B_BYTES);
+                else if (jv <= 4 && jg <= 4) sp_norm_row<4, 4>(row, st, lane, m, k_lo, k_hi, K, G, inv_K, eps, s_gamma, s_beta, b_tiles, B_BYTES);
+                else sp_norm_row<SP_LN_MAX_KB / 2, SP_STAT_SEGS / 32>(row, st, lane, m, k_lo, k_hi, K, G, inv_K, eps, s_gamma, s_beta, b_tiles, B_BYTES);
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the MMA reads these through the async proxy
             __syncwarp();
@@ -306,15 +359,27 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                 }
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             }
-            if (warp * 32 < bm) {
+            if (have && warp * 32 < bm) {
+                // this thread's column c of the partial tile, row after row, to whoever finishes the piece it is in
+                const uint32_t recv0 = tsm(recv), bar0 = tsm(recv_bar);
+                const int c = warp * 32 + lane;
+                // the piece of row 0: its owner (a warp of the cluster, g) and which of that warp's pieces it is (j)
+                int g = wide ? 0 : warp, j = 0;            // (segs ≤ 4 ≤ ustride: one subtraction wraps)
 #pragma unroll
-                for (int m = 0; m < BN; ++m)
-                    if (m < M) part[m * bm + warp * 32 + lane] = r[m];
+                for (int m = 0; m < BN; ++m) {
+                    if (m < M) {
+                        const int slot = ((split * n_j + j) * 4 + (g & 3)) * 32;
+                        const int off = wide ? (slot + (rpp == 2 ? (m & 1) * lpr : 0) + (c >> 2)) * 4 + (c & 3) : slot + lane;
+                        sp_send_f32(recv0 + (uint32_t)off * 4u, bar0, (uint32_t)(g >> 2), r[m]);
+                        if (wide) { if (rpp == 1 || (m & 1)) { if (++g == ustride) { g = 0; ++j; } } }
+                        else { g += segs; if (g >= ustride) { g -= ustride; ++j; } }
+                    }
+                }
             }
         }
     }
     __syncwarp();
-    cluster_sync_all();                                        // every part of the tile is in shared memory
+    if (warp < 4 && !*(volatile int*)s_abort && !tbar_wait_or_abort(recv_bar, 0, s_abort)) atomicExch(s_abort, 1);
     if (warp < 4 && wide && !*(volatile int*)s_abort) {
         int j = 0;
         for (int u = gw; u < units; u += ustride, ++j) {
@@ -323,11 +388,11 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             const bool row_ok = m < M;
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
             if (row_ok) {
-                const uint32_t own = tsm(part + m * bm + colw);
+                const float* mine = recv + ((size_t)(j * 4 + warp) * 32 + lane) * 4;
                 float4 v[SP_MAX_SPLITS];
 #pragma unroll
                 for (int s = 0; s < SP_MAX_SPLITS; ++s)
-                    v[s] = s < splits ? ld_cluster_f32x4(own, (uint32_t)s) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    v[s] = s < splits ? *reinterpret_cast<const float4*>(mine + (size_t)s * n_j * 512) : make_float4(0.f, 0.f, 0.f, 0.f);
                 acc[0] = v[0].x; acc[1] = v[0].y; acc[2] = v[0].z; acc[3] = v[0].w;
 #pragma unroll
                 for (int s = 1; s < SP_MAX_SPLITS; ++s) {               // always in the order of the parts
@@ -403,10 +468,10 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         for (int u = gw; u < units_n; u += ustride, ++j) {
             const int m = u / segs, colw = (u % segs) * 32 + lane;
             const int n = n0 + colw;
-            const uint32_t own = tsm(part + m * bm + colw);
+            const float* mine = recv + (size_t)(j * 4 + warp) * 32 + lane;
             float v[SP_MAX_SPLITS];
 #pragma unroll
-            for (int s = 0; s < SP_MAX_SPLITS; ++s) v[s] = s < splits ? ld_cluster_f32(own, (uint32_t)s) : 0.f;
+            for (int s = 0; s < SP_MAX_SPLITS; ++s) v[s] = s < splits ? mine[(size_t)s * n_j * 128] : 0.f;
             float acc = v[0];
 #pragma unroll
             for (int s = 1; s < SP_MAX_SPLITS; ++s) acc += v[s];    // always in the order of the parts
@@ -446,7 +511,6 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         }
     }
     __syncwarp();
-    cluster_sync_relaxed();                                    // nobody leaves while its shared memory is being read
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -471,10 +535,9 @@ struct SpPlan { int bm, tiles, splits, kb_cap, stages; size_t smem; };
 
 size_t sp_smem(int bm, int bn, bool ln, int stages, int kb_cap, int M, int splits) {
     const size_t ring = (size_t)stages * bm * 128;
-    (void)splits;
-    const size_t part = (size_t)M * bm * sizeof(float);
+    const size_t part = (size_t)sp_recv_floats(M, bm, splits, sp_is_wide(M, bm, splits, ln)) * sizeof(float);
     return 1024 + ring + part + (bm == 64 ? 8192 : 0) + (size_t)(ln ? kb_cap : stages) * bn * 128 +
-           (ln ? (size_t)kb_cap * SP_BK * 8 : 0) + (2 * SP_MAX_STAGES + 2) * 8 + 16 + 128 * sizeof(int);
+           (ln ? (size_t)kb_cap * SP_BK * 8 : 0) + (2 * SP_MAX_STAGES + 3) * 8 + 16 + 128 * sizeof(int);
 }
 
 // Tile height, number of parts and ring depth: about one CTA per SM (so that the next product's CTAs find
@@ -549,7 +612,7 @@ int launch_sp(const void* X, const void* W, const float* gamma, const float* bet
               const float* residual, void* Y, int M, int N, int K, int ldx, int ldy, int act, const SpKvScatter& kv,
               const float* stats_in, float* stats_out, const void* ahead, long long ahead_bytes, int* dev_err, cudaStream_t stream) {
     const SpPlan plan = sp_plan(M, N, K, BN, LN);
-    if (!LN && M * (plan.bm / 32) > 4 * 4 * plan.splits)
+    if (sp_is_wide(M, plan.bm, plan.splits, LN))
         return launch_sp_as<BN, OT, LN, !LN>(X, W, gamma, beta, eps, bias, residual, Y, M, N, K, ldx, ldy, act, kv, stats_in,
                                              stats_out, ahead, ahead_bytes, dev_err, stream);
     return launch_sp_as<BN, OT, LN, false>(X, W, gamma, beta, eps, bias, residual, Y, M, N, K, ldx, ldy, act, kv, stats_in,

@@ -6,6 +6,8 @@ no function has a CPU or library fallback.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import KernelError, call
@@ -130,7 +132,7 @@ SWAPPED_MIN_COLUMNS = 16384
 #: passes on the row statistics that the next LayerNorm needs.  The `mma.sync` kernel remains for the shapes
 #: the split-k kernel refuses and for a LayerNorm of rows whose statistics nobody left.
 #: Whether few-row products ask for the weights that follow theirs to be brought to L2 (`ahead=`).
-FETCH_WEIGHTS_AHEAD = True
+FETCH_WEIGHTS_AHEAD = os.environ.get("VLRF_B200_FETCH_AHEAD", "1") != "0"
 SPLITK_MIN_WEIGHT_BYTES = 0
 SPLITK_NORM_MIN_WEIGHT_BYTES = 0
 _DEV_ERR = None
