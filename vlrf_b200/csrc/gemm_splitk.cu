@@ -110,13 +110,11 @@ __device__ __forceinline__ void sp_norm_row(const float* __restrict__ row, const
 }
 
 // Whether the finished tile is dealt out in pieces of 32 lanes × 4 columns (many rows) or 32 lanes × 1 column.
-__host__ __device__ inline bool sp_is_wide(int M, int bm, int splits, bool ln) { return !ln && M * (bm / 32) > 4 * 4 * splits; }
-// Floats of the buffer in which a CTA receives its warps' pieces from every part.
-__host__ __device__ inline int sp_recv_floats(int M, int bm, int splits, bool wide) {
-    const int rpp = 32 / (bm >> 2);
-    const int units = wide ? (M + rpp - 1) / rpp : M * (bm >> 5);
-    const int n_j = (units + 4 * splits - 1) / (4 * splits);
-    return splits * n_j * 4 * 32 * (wide ? 4 : 1);
+__host__ __device__ inline bool sp_is_wide(int M, int bm, int splits, bool ln) { return !ln && M > 16 && M * (bm / 32) > 4 * 4 * splits; }
+// Floats of the buffer in which a CTA receives its warps' pieces (a row, 32 columns) from every part.
+__host__ __device__ inline int sp_recv_floats(int M, int bm, int splits) {
+    const int n_j = (M * (bm >> 5) + 4 * splits - 1) / (4 * splits);
+    return splits * n_j * 4 * 32;
 }
 // a float into the shared memory of CTA `rank` of the cluster (at the place `own_addr` has in this CTA), counted
 // down on the barrier at `own_bar`'s place there
@@ -150,8 +148,10 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     unsigned char* after_b = b_tiles + (size_t)(LN ? kb_cap : stages) * B_BYTES;
     float* s_gamma = reinterpret_cast<float*>(after_b);              // LN: [kb_cap·64] this part's norm weights
     float* s_beta = s_gamma + (LN ? kb_cap * SP_BK : 0);
-    // what this CTA receives of the tile: the pieces its warps finish, from every part of the sum (below)
+    // up to 16 rows: what this CTA receives of the tile, the pieces its warps finish from every part of the sum
+    // (below); more rows: this CTA's part of the tile, [m][bm] float32, which the others read
     float* recv = s_beta + (LN ? kb_cap * SP_BK : 0);
+    float* part = recv;
     // The finished tile is dealt to the 4·splits epilogue warps of the cluster in pieces of 32 lanes × 4
     // columns: one row of a 128-row tile, two rows of a 64-row tile.
     const int lpr = bm >> 2, rpp = 32 / lpr;                         // lanes a row, rows a piece
@@ -159,14 +159,17 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     // … unless that leaves most warps without a piece (few rows): then pieces of 32 lanes × 1 column
     const int segs = bm >> 5, units_n = M * segs;
     constexpr bool wide = WIDE;
-    // Every CTA of the cluster sends each piece of its partial tile to the CTA whose warp finishes that piece, as
-    // stores into that CTA's shared memory that count down a barrier there (`st.async`): recv[source part][piece of
-    // the warp j][warp][32 lanes × PW floats].  The receiver waits on its own barrier for all the bytes it is due
-    // and adds the parts in the order of their CTAs: one crossing of the cluster instead of a cluster barrier and a
-    // read of the others' memory, and nobody's shared memory is read by another CTA.
-    constexpr int PW = WIDE ? 4 : 1;
-    const int n_j = ((wide ? units : units_n) + ustride - 1) / ustride;   // pieces a warp
-    uint64_t* full = reinterpret_cast<uint64_t*>(recv + (size_t)sp_recv_floats(M, bm, (int)gridDim.y, WIDE));
+    // Up to 16 rows (PUSH): every CTA of the cluster sends each piece of its partial tile to the CTA whose warp
+    // finishes that piece, as stores into that CTA's shared memory that count down a barrier there (`st.async`):
+    // recv[source part][piece of the warp j][warp][32 lanes].  The receiver waits on its own barrier for all the
+    // bytes it is due and adds the parts in the order of their CTAs: one crossing of the cluster instead of a
+    // cluster barrier and a read of the others' memory, and nobody's shared memory is read by another CTA.
+    // More rows: a store per value would cost more than it saves; every CTA keeps its part, a cluster barrier
+    // says that all are complete, and the finishing warps read them through distributed shared memory.
+    constexpr bool PUSH = BN == 16;
+    static_assert(!(PUSH && WIDE), "pieces of up to 16 rows are 32 lanes × 1 column");
+    const int n_j = (units_n + ustride - 1) / ustride;                   // (PUSH) pieces a warp
+    uint64_t* full = reinterpret_cast<uint64_t*>(recv + (PUSH ? (size_t)sp_recv_floats(M, bm, (int)gridDim.y) : (size_t)M * bm));
     uint64_t* empty = full + SP_MAX_STAGES;
     uint64_t* acc_full = empty + SP_MAX_STAGES;
     uint64_t* x_ready = acc_full + 1;
@@ -190,12 +193,13 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         tbar_init(recv_bar, 1);
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        // the bytes this CTA is due: its warps' pieces, once from every part
-        int floats = 0;
-        for (int w = 0; w < 4; ++w)
-            for (int u = split * 4 + w; u < (wide ? units : units_n); u += ustride)
-                floats += wide ? min(rpp, M - u * rpp) * bm : 32;
-        tbar_expect_tx(recv_bar, (uint32_t)(floats * splits * 4));
+        if (PUSH) {
+            // the bytes this CTA is due: its warps' pieces, once from every part
+            int pieces = 0;
+            for (int w = 0; w < 4; ++w)
+                for (int u = split * 4 + w; u < units_n; u += ustride) ++pieces;
+            tbar_expect_tx(recv_bar, (uint32_t)(pieces * 32 * splits * 4));
+        }
     }
     if (warp == 4) {
         if (lane == 0) { tma_prefetch_descriptor(&tmap_w); if (!LN) tma_prefetch_descriptor(&tmap_x); }
@@ -208,7 +212,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
     // every CTA of the cluster has set up its receiving barrier before anyone sends (waited for further down)
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    if (PUSH) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 
     // The weights do not depend on the kernel ahead: the first stages' tiles of W are requested at once, and
     // the norm's weights for this part's columns are copied to shared memory.
@@ -240,7 +244,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         }
     }
     const float inv_K = 1.f / (float)K;
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (PUSH) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     pdl_launch_dependents();
     pdl_wait();                                    // the rows of X, the residual and the positions are ready
 
@@ -359,27 +363,34 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                 }
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             }
-            if (have && warp * 32 < bm) {
-                // this thread's column c of the partial tile, row after row, to whoever finishes the piece it is in
+            if (PUSH && have && warp * 32 < bm) {
+                // this thread's column of the partial tile, row after row, to whoever finishes the piece it is in
                 const uint32_t recv0 = tsm(recv), bar0 = tsm(recv_bar);
-                const int c = warp * 32 + lane;
                 // the piece of row 0: its owner (a warp of the cluster, g) and which of that warp's pieces it is (j)
-                int g = wide ? 0 : warp, j = 0;            // (segs ≤ 4 ≤ ustride: one subtraction wraps)
+                int g = warp, j = 0;                       // (segs ≤ 4 ≤ ustride: one subtraction wraps)
 #pragma unroll
                 for (int m = 0; m < BN; ++m) {
                     if (m < M) {
-                        const int slot = ((split * n_j + j) * 4 + (g & 3)) * 32;
-                        const int off = wide ? (slot + (rpp == 2 ? (m & 1) * lpr : 0) + (c >> 2)) * 4 + (c & 3) : slot + lane;
+                        const int off = ((split * n_j + j) * 4 + (g & 3)) * 32 + lane;
                         sp_send_f32(recv0 + (uint32_t)off * 4u, bar0, (uint32_t)(g >> 2), r[m]);
-                        if (wide) { if (rpp == 1 || (m & 1)) { if (++g == ustride) { g = 0; ++j; } } }
-                        else { g += segs; if (g >= ustride) { g -= ustride; ++j; } }
+                        g += segs;
+                        if (g >= ustride) { g -= ustride; ++j; }
                     }
                 }
+            }
+            if (!PUSH && warp * 32 < bm) {
+#pragma unroll
+                for (int m = 0; m < BN; ++m)
+                    if (m < M) part[m * bm + warp * 32 + lane] = r[m];
             }
         }
     }
     __syncwarp();
-    if (warp < 4 && !*(volatile int*)s_abort && !tbar_wait_or_abort(recv_bar, 0, s_abort)) atomicExch(s_abort, 1);
+    if (PUSH) {
+        if (warp < 4 && !*(volatile int*)s_abort && !tbar_wait_or_abort(recv_bar, 0, s_abort)) atomicExch(s_abort, 1);
+    } else {
+        cluster_sync_all();                                    // every part of the tile is in shared memory
+    }
     if (warp < 4 && wide && !*(volatile int*)s_abort) {
         int j = 0;
         for (int u = gw; u < units; u += ustride, ++j) {
@@ -388,11 +399,11 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             const bool row_ok = m < M;
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
             if (row_ok) {
-                const float* mine = recv + ((size_t)(j * 4 + warp) * 32 + lane) * 4;
+                const uint32_t own = tsm(part + m * bm + colw);
                 float4 v[SP_MAX_SPLITS];
 #pragma unroll
                 for (int s = 0; s < SP_MAX_SPLITS; ++s)
-                    v[s] = s < splits ? *reinterpret_cast<const float4*>(mine + (size_t)s * n_j * 512) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    v[s] = s < splits ? ld_cluster_f32x4(own, (uint32_t)s) : make_float4(0.f, 0.f, 0.f, 0.f);
                 acc[0] = v[0].x; acc[1] = v[0].y; acc[2] = v[0].z; acc[3] = v[0].w;
 #pragma unroll
                 for (int s = 1; s < SP_MAX_SPLITS; ++s) {               // always in the order of the parts
@@ -469,9 +480,11 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             const int m = u / segs, colw = (u % segs) * 32 + lane;
             const int n = n0 + colw;
             const float* mine = recv + (size_t)(j * 4 + warp) * 32 + lane;
+            const uint32_t own = tsm(part + m * bm + colw);
             float v[SP_MAX_SPLITS];
 #pragma unroll
-            for (int s = 0; s < SP_MAX_SPLITS; ++s) v[s] = s < splits ? mine[(size_t)s * n_j * 128] : 0.f;
+            for (int s = 0; s < SP_MAX_SPLITS; ++s)
+                v[s] = s >= splits ? 0.f : PUSH ? mine[(size_t)s * n_j * 128] : ld_cluster_f32(own, (uint32_t)s);
             float acc = v[0];
 #pragma unroll
             for (int s = 1; s < SP_MAX_SPLITS; ++s) acc += v[s];    // always in the order of the parts
@@ -511,6 +524,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         }
     }
     __syncwarp();
+    if (!PUSH) cluster_sync_relaxed();                         // nobody leaves while its shared memory is being read
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -535,7 +549,7 @@ struct SpPlan { int bm, tiles, splits, kb_cap, stages; size_t smem; };
 
 size_t sp_smem(int bm, int bn, bool ln, int stages, int kb_cap, int M, int splits) {
     const size_t ring = (size_t)stages * bm * 128;
-    const size_t part = (size_t)sp_recv_floats(M, bm, splits, sp_is_wide(M, bm, splits, ln)) * sizeof(float);
+    const size_t part = (bn == 16 ? (size_t)sp_recv_floats(M, bm, splits) : (size_t)M * bm) * sizeof(float);
     return 1024 + ring + part + (bm == 64 ? 8192 : 0) + (size_t)(ln ? kb_cap : stages) * bn * 128 +
            (ln ? (size_t)kb_cap * SP_BK * 8 : 0) + (2 * SP_MAX_STAGES + 3) * 8 + 16 + 128 * sizeof(int);
 }
@@ -612,8 +626,8 @@ int launch_sp(const void* X, const void* W, const float* gamma, const float* bet
               const float* residual, void* Y, int M, int N, int K, int ldx, int ldy, int act, const SpKvScatter& kv,
               const float* stats_in, float* stats_out, const void* ahead, long long ahead_bytes, int* dev_err, cudaStream_t stream) {
     const SpPlan plan = sp_plan(M, N, K, BN, LN);
-    if (sp_is_wide(M, plan.bm, plan.splits, LN))
-        return launch_sp_as<BN, OT, LN, !LN>(X, W, gamma, beta, eps, bias, residual, Y, M, N, K, ldx, ldy, act, kv, stats_in,
+    if (BN > 16 && sp_is_wide(M, plan.bm, plan.splits, LN))
+        return launch_sp_as<BN, OT, LN, (BN > 16 && !LN)>(X, W, gamma, beta, eps, bias, residual, Y, M, N, K, ldx, ldy, act, kv, stats_in,
                                              stats_out, ahead, ahead_bytes, dev_err, stream);
     return launch_sp_as<BN, OT, LN, false>(X, W, gamma, beta, eps, bias, residual, Y, M, N, K, ldx, ldy, act, kv, stats_in,
                                            stats_out, ahead, ahead_bytes, dev_err, stream);
