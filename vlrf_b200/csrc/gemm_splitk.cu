@@ -30,6 +30,8 @@
 // Every wait on an mbarrier is bounded; a CTA that gives up sets the device error word, sends nothing (its
 // receivers then give up too, after their own bounded wait) and frees its tensor memory.
 #include "common.cuh"
+#include <cstdlib>
+#include <cstring>
 #include "tma.cuh"
 #include "tcgen05.cuh"
 
@@ -125,9 +127,94 @@ __device__ __forceinline__ void sp_send_f32(uint32_t own_addr, uint32_t own_bar,
     asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(addr), "r"(__float_as_uint(v)), "r"(bar) : "memory");
 }
 
+__device__ __forceinline__ void sp_ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void sp_ldsm_x2(uint32_t addr, uint32_t& r0, uint32_t& r1) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+__device__ __forceinline__ void sp_mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// SYNC: one finishing warp's product.  Its 32 rows of the W tile (two 16-row MMA tiles) times all rows of X (NT
+// 8-column tiles), k block after k block from the ring; then every value is sent to whoever finishes the piece
+// (row m of X, this warp's 32 columns) it is in.  An `mma.sync` has a long latency here, and the MMAs of a k block
+// that add to one accumulator would wait for one another: the four 16-wide steps of a k block have accumulators of
+// their own, which are added at the end (in a fixed order).
+template <int NT, bool LN>
+__device__ __forceinline__ bool sp_sync_product(int warp, int lane, int M, int n_kb, int stages, unsigned char* a_tiles, int a_bytes,
+                                                unsigned char* b_tiles, int b_bytes, uint64_t* full, uint64_t* empty, int* s_abort,
+                                                float* recv, uint64_t* recv_bar, const int* s_piece, int segs, int split, int n_j) {
+    float acc[SP_BK / 16][2][NT][4];
+#pragma unroll
+    for (int ks = 0; ks < SP_BK / 16; ++ks)
+#pragma unroll
+        for (int a = 0; a < 2; ++a)
+#pragma unroll
+            for (int b = 0; b < NT; ++b)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[ks][a][b][e] = 0.f;
+    const int a_row = warp * 32 + (lane & 15);                     // + 16 for the second tile
+    const int b_row = (lane & 7) + ((lane >> 4) << 3);
+    for (int i = 0; i < n_kb; ++i) {
+        const int s = i % stages;
+        if (!tbar_wait_or_abort(&full[s], (uint32_t)((i / stages) & 1), s_abort)) return false;
+        const uint32_t a_base = tsm(a_tiles + (size_t)s * a_bytes), b_base = tsm(b_tiles + (size_t)(LN ? i : s) * b_bytes);
+        uint32_t a[SP_BK / 16][2][4], b[SP_BK / 16][4];
+#pragma unroll
+        for (int ks = 0; ks < SP_BK / 16; ++ks) {
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+                const int row = a_row + mt * 16, ch = ks * 2 + (lane >> 4);
+                sp_ldsm_x4(a_base + row * 128 + ((ch ^ (row & 7)) << 4), a[ks][mt][0], a[ks][mt][1], a[ks][mt][2], a[ks][mt][3]);
+            }
+            const int ch = ks * 2 + ((lane >> 3) & 1);
+            if (NT == 2) sp_ldsm_x4(b_base + b_row * 128 + ((ch ^ (b_row & 7)) << 4), b[ks][0], b[ks][1], b[ks][2], b[ks][3]);
+            else sp_ldsm_x2(b_base + (lane & 7) * 128 + ((ch ^ (lane & 7)) << 4), b[ks][0], b[ks][1]);
+        }
+#pragma unroll
+        for (int ks = 0; ks < SP_BK / 16; ++ks)
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+                sp_mma16816(acc[ks][mt][0], a[ks][mt][0], a[ks][mt][1], a[ks][mt][2], a[ks][mt][3], b[ks][0], b[ks][1]);
+                if (NT == 2) sp_mma16816(acc[ks][mt][1], a[ks][mt][0], a[ks][mt][1], a[ks][mt][2], a[ks][mt][3], b[ks][2], b[ks][3]);
+            }
+        if (n_kb > stages) {                       // the stage is needed again
+            __syncwarp();
+            if (lane == 0) tbar_arrive(&empty[s]);
+        }
+    }
+    const uint32_t recv0 = tsm(recv), bar0 = tsm(recv_bar);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int e1 = 0; e1 < 2; ++e1) {
+            const int m = nt * 8 + (lane & 3) * 2 + e1;
+            if (m < M) {
+                const int who = s_piece[m * segs + warp], g = who & 255, j = who >> 8;
+                const uint32_t base = recv0 + (uint32_t)(((split * n_j + j) * 4 + (g & 3)) * 32 + (lane >> 2)) * 4u;
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                    for (int e2 = 0; e2 < 2; ++e2) {
+                        const int e = e2 * 2 + e1;
+                        const float v = (acc[0][mt][nt][e] + acc[1][mt][nt][e]) + (acc[2][mt][nt][e] + acc[3][mt][nt][e]);
+                        sp_send_f32(base + (uint32_t)(mt * 16 + e2 * 8) * 4u, bar0, (uint32_t)(g >> 2), v);
+                    }
+            }
+        }
+    return true;
+}
+
 // bm: rows of W per tile (64 or 128); stages: depth of the ring; kb_cap: most k blocks of one part
+// SYNC (up to 16 rows only): the product on `mma.sync` by the four finishing warps, each on its 32 rows of the W
+// tile, straight from the ring (ldmatrix reads the 128-byte swizzle), the accumulators in registers: with so few
+// rows an MMA is a few cycles of work, and the one thread that issues `tcgen05.mma`, its commit, the barrier and
+// the read-back from tensor memory are a longer chain than eight warp-level MMAs a k block.
 // WIDE: the pieces of the finished tile are 32 lanes × 4 columns (many rows) instead of 32 lanes × 1 column
-template <int BN, typename OT, bool LN, bool WIDE>
+template <int BN, typename OT, bool LN, bool WIDE, bool SYNC>
 __global__ void __launch_bounds__(LN ? SP_THREADS_LN : SP_THREADS, 2)
 gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                    const float* __restrict__ Xf, int ldx, const float* __restrict__ gamma,
@@ -168,6 +255,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     // says that all are complete, and the finishing warps read them through distributed shared memory.
     constexpr bool PUSH = BN == 16;
     static_assert(!(PUSH && WIDE), "pieces of up to 16 rows are 32 lanes × 1 column");
+    static_assert(!SYNC || BN == 16, "the mma.sync variant is for up to 16 rows");
     const int n_j = (units_n + ustride - 1) / ustride;                   // (PUSH) pieces a warp
     uint64_t* full = reinterpret_cast<uint64_t*>(recv + (PUSH ? (size_t)sp_recv_floats(M, bm, (int)gridDim.y) : (size_t)M * bm));
     uint64_t* empty = full + SP_MAX_STAGES;
@@ -178,6 +266,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
     int* s_kv_blk = s_abort + 1;                                     // [64]
     int* s_kv_row = s_kv_blk + 64;                                   // [64]
+    int* s_piece = s_kv_row + 64;                                    // [64] (SYNC) who finishes piece u: warp of the cluster | its piece << 8
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.x, split = blockIdx.y, splits = gridDim.y;
@@ -187,7 +276,8 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     const int n0 = tile * bm;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < stages; ++s) { tbar_init(&full[s], 1); tbar_init(&empty[s], 1); }
+        // (a stage is given back by the commit of its MMAs, or by every warp that read it)
+        for (int s = 0; s < stages; ++s) { tbar_init(&full[s], 1); tbar_init(&empty[s], SYNC ? (uint32_t)min(4, bm >> 5) : 1u); }
         tbar_init(acc_full, 1);
         tbar_init(x_ready, 8);
         tbar_init(recv_bar, 1);
@@ -201,11 +291,16 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             tbar_expect_tx(recv_bar, (uint32_t)(pieces * 32 * splits * 4));
         }
     }
+    if (SYNC && (int)threadIdx.x < units_n && threadIdx.x < 64) s_piece[threadIdx.x] = ((int)threadIdx.x % ustride) | (((int)threadIdx.x / ustride) << 8);
     if (warp == 4) {
         if (lane == 0) { tma_prefetch_descriptor(&tmap_w); if (!LN) tma_prefetch_descriptor(&tmap_x); }
         __syncwarp();
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tsm(tmem_slot)), "r"((uint32_t)TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (!SYNC) {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tsm(tmem_slot)), "r"((uint32_t)TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        } else if (lane == 0) {
+            *tmem_slot = 0;
+        }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -267,7 +362,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             }
         }
     } else if (warp == 5) {
-        if (lane == 0) {
+        if (!SYNC && lane == 0) {
             constexpr uint32_t idesc = umma_idesc_bf16(128, BN);
             bool ok = true;
             if (LN && !tbar_wait_or_abort(x_ready, 0, s_abort)) { atomicExch(s_abort, 1); ok = false; }
@@ -298,9 +393,15 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                 else if (jv <= 4 && jg <= 4) sp_norm_row<4, 4>(row, st, lane, m, k_lo, k_hi, K, G, inv_K, eps, s_gamma, s_beta, b_tiles, B_BYTES);
                 else sp_norm_row<SP_LN_MAX_KB / 2, SP_STAT_SEGS / 32>(row, st, lane, m, k_lo, k_hi, K, G, inv_K, eps, s_gamma, s_beta, b_tiles, B_BYTES);
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the MMA reads these through the async proxy
-            __syncwarp();
-            if (lane == 0) tbar_arrive(x_ready);
+            if (SYNC) {
+                // the four finishing warps read all rows: they wait for the eight that normed them
+                if (warp < 4) asm volatile("bar.sync 3, 256;" ::: "memory");
+                else asm volatile("bar.arrive 3, 256;" ::: "memory");
+            } else {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the MMA reads these through the async proxy
+                __syncwarp();
+                if (lane == 0) tbar_arrive(x_ready);
+            }
         }
         if (warp < 4) {
             if (kv.Kc != nullptr && (int)threadIdx.x < 64) {
@@ -340,7 +441,17 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                 }
             }
         }
-        if (warp < 4) {
+        if (SYNC && warp < 4) {
+            if (warp * 32 < bm && !*(volatile int*)s_abort) {
+                bool ok;
+                if (M > 8) ok = sp_sync_product<2, LN>(warp, lane, M, n_kb, stages, a_tiles, a_bytes, b_tiles, B_BYTES, full, empty, s_abort,
+                                                       recv, recv_bar, s_piece, segs, split, n_j);
+                else ok = sp_sync_product<1, LN>(warp, lane, M, n_kb, stages, a_tiles, a_bytes, b_tiles, B_BYTES, full, empty, s_abort,
+                                                 recv, recv_bar, s_piece, segs, split, n_j);
+                if (!ok) atomicExch(s_abort, 1);
+            }
+        }
+        if (!SYNC && warp < 4) {
             const bool have = !*(volatile int*)s_abort && tbar_wait_or_abort(acc_full, 0, s_abort);
             if (!have) atomicExch(s_abort, 1);
             float r[BN];
@@ -528,7 +639,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (warp == 4) {
+    if (!SYNC && warp == 4) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
     }
     if (threadIdx.x == 0 && *s_abort) atomicOr(dev_err, VLRF_DEVERR_WAIT_TIMEOUT);
@@ -545,13 +656,26 @@ int sp_sm_count() {
     return sms;
 }
 
+// Which tensor-core path a product of M ≤ 16 rows takes: `mma.sync` up to 8 rows (measured inside whole decode
+// steps of GPT-2 small: 0.262 against 0.302 ms at batch 1, 0.307 against 0.315 at batch 8, 0.383 against 0.373 at
+// batch 16), else `tcgen05.mma` as the products of more rows do.  VLRF_B200_SPLITK_MMA=tcgen05 or =sync in the
+// environment sends all of them one way (for measurements).
+bool sp_use_mma_sync(int M) {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("VLRF_B200_SPLITK_MMA");
+        v = e == nullptr ? 8 : strcmp(e, "tcgen05") == 0 ? 0 : strcmp(e, "sync") == 0 ? 16 : 8;
+    }
+    return M <= v;
+}
+
 struct SpPlan { int bm, tiles, splits, kb_cap, stages; size_t smem; };
 
 size_t sp_smem(int bm, int bn, bool ln, int stages, int kb_cap, int M, int splits) {
     const size_t ring = (size_t)stages * bm * 128;
     const size_t part = (bn == 16 ? (size_t)sp_recv_floats(M, bm, splits) : (size_t)M * bm) * sizeof(float);
     return 1024 + ring + part + (bm == 64 ? 8192 : 0) + (size_t)(ln ? kb_cap : stages) * bn * 128 +
-           (ln ? (size_t)kb_cap * SP_BK * 8 : 0) + (2 * SP_MAX_STAGES + 3) * 8 + 16 + 128 * sizeof(int);
+           (ln ? (size_t)kb_cap * SP_BK * 8 : 0) + (2 * SP_MAX_STAGES + 3) * 8 + 16 + 192 * sizeof(int);
 }
 
 // Tile height, number of parts and ring depth: about one CTA per SM (so that the next product's CTAs find
@@ -585,7 +709,7 @@ SpPlan sp_plan(int M, int N, int K, int bn, bool ln) {
     return best;
 }
 
-template <int BN, typename OT, bool LN, bool WIDE>
+template <int BN, typename OT, bool LN, bool WIDE, bool SYNC>
 int launch_sp_as(const void* X, const void* W, const float* gamma, const float* beta, float eps, const float* bias,
               const float* residual, void* Y, int M, int N, int K, int ldx, int ldy, int act, const SpKvScatter& kv,
               const float* stats_in, float* stats_out, const void* ahead, long long ahead_bytes, int* dev_err, cudaStream_t stream) {
@@ -600,7 +724,7 @@ int launch_sp_as(const void* X, const void* W, const float* gamma, const float* 
     } else {
         tx = tw;   // unused
     }
-    auto kern = gemm_splitk_kernel<BN, OT, LN, WIDE>;
+    auto kern = gemm_splitk_kernel<BN, OT, LN, WIDE, SYNC>;
     static bool clusters_allowed = false;
     if (!clusters_allowed) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
@@ -626,10 +750,13 @@ int launch_sp(const void* X, const void* W, const float* gamma, const float* bet
               const float* residual, void* Y, int M, int N, int K, int ldx, int ldy, int act, const SpKvScatter& kv,
               const float* stats_in, float* stats_out, const void* ahead, long long ahead_bytes, int* dev_err, cudaStream_t stream) {
     const SpPlan plan = sp_plan(M, N, K, BN, LN);
+    if (BN == 16 && sp_use_mma_sync(M))
+        return launch_sp_as<BN, OT, LN, false, BN == 16>(X, W, gamma, beta, eps, bias, residual, Y, M, N, K, ldx, ldy, act, kv, stats_in,
+                                                        stats_out, ahead, ahead_bytes, dev_err, stream);
     if (BN > 16 && sp_is_wide(M, plan.bm, plan.splits, LN))
-        return launch_sp_as<BN, OT, LN, (BN > 16 && !LN)>(X, W, gamma, beta, eps, bias, residual, Y, M, N, K, ldx, ldy, act, kv, stats_in,
+        return launch_sp_as<BN, OT, LN, (BN > 16 && !LN), false>(X, W, gamma, beta, eps, bias, residual, Y, M, N, K, ldx, ldy, act, kv, stats_in,
                                              stats_out, ahead, ahead_bytes, dev_err, stream);
-    return launch_sp_as<BN, OT, LN, false>(X, W, gamma, beta, eps, bias, residual, Y, M, N, K, ldx, ldy, act, kv, stats_in,
+    return launch_sp_as<BN, OT, LN, false, false>(X, W, gamma, beta, eps, bias, residual, Y, M, N, K, ldx, ldy, act, kv, stats_in,
                                            stats_out, ahead, ahead_bytes, dev_err, stream);
 }
 }  // namespace
