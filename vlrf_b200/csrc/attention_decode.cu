@@ -211,6 +211,68 @@ __device__ void finish_cluster(const float* wpart, float* cpart, int dh, int row
     cluster_sync_relaxed();                        // nobody leaves while its shared memory is being read
 }
 
+// The same end without a cluster barrier: every CTA of the cluster sends the merge of its warps (maximum, sum,
+// outputs: dh + 2 floats) into the shared memory of the CTA of part 0, `crecv` [n_split][dh + 2], as stores that
+// count down the barrier `cbar` there (`st.async`); that CTA waits for all the bytes it is due and merges the parts
+// in their order.  The others leave as soon as they have sent.  Before anyone sends, every CTA has initialised its
+// barrier (the CTA of part 0 expecting n_split · (dh + 2) floats) and met the others at a cluster barrier.
+template <typename ET, int DH>
+__device__ __forceinline__ void finish_cluster_push(const float* wpart, float* crecv, uint64_t* cbar, int row, int h, int split,
+                                                    int n_split, ET* __restrict__ out, int ld_out, int* __restrict__ dev_err) {
+    constexpr int ND = DH / 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp != 0) return;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, wpart[w * (DH + 2)]);
+    float L = 0.f;
+    float o[ND];
+#pragma unroll
+    for (int i = 0; i < ND; ++i) o[i] = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) {
+        const float* pw = wpart + w * (DH + 2);
+        const float f = (pw[0] == -INFINITY) ? 0.f : expf(pw[0] - M);
+        L += pw[1] * f;
+#pragma unroll
+        for (int i = 0; i < ND; ++i) o[i] += pw[2 + i * 32 + lane] * f;
+    }
+    {
+        uint32_t dst, bar;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(dst) : "r"(dsmem_u32(crecv + (size_t)split * (DH + 2))), "r"(0));
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(bar) : "r"(dsmem_u32(cbar)), "r"(0));
+        if (lane == 0) {
+            asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(dst), "r"(__float_as_uint(M)), "r"(bar) : "memory");
+            asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(dst + 4u), "r"(__float_as_uint(L)), "r"(bar) : "memory");
+        }
+#pragma unroll
+        for (int i = 0; i < ND; ++i)
+            asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(dst + 4u * (uint32_t)(2 + i * 32 + lane)), "r"(__float_as_uint(o[i])), "r"(bar) : "memory");
+    }
+    if (split != 0) return;
+    uint32_t polls = 0;
+    while (!dmbar_try_wait(cbar, 0)) {
+        if (++polls > DEC_WAIT_LIMIT) { if (lane == 0) atomicOr(dev_err, VLRF_DEVERR_WAIT_TIMEOUT); return; }
+    }
+    // all parts are here: merge them in their order (four at a time, so that the reads do not wait for one another)
+    float Mx = -INFINITY;
+    for (int s = 0; s < n_split; ++s) Mx = fmaxf(Mx, crecv[(size_t)s * (DH + 2)]);
+    float Lx = 0.f;
+#pragma unroll
+    for (int i = 0; i < ND; ++i) o[i] = 0.f;
+    for (int s = 0; s < n_split; ++s) {
+        const float* ps = crecv + (size_t)s * (DH + 2);
+        const float f = (ps[0] == -INFINITY) ? 0.f : expf(ps[0] - Mx);
+        Lx += ps[1] * f;
+#pragma unroll
+        for (int i = 0; i < ND; ++i) o[i] += ps[2 + i * 32 + lane] * f;
+    }
+    const float inv = (Lx > 0.f) ? 1.f / Lx : 0.f;
+    ET* dst = out + (size_t)row * ld_out + (size_t)h * DH;
+#pragma unroll
+    for (int i = 0; i < ND; ++i) ElemIO<ET>::store(dst + i * 32 + lane, o[i] * inv);
+}
+
 template <typename ET>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attn_decode_generic_kernel(const ET* __restrict__ qkv, int ld, int q_off, const ET* __restrict__ Kc,
@@ -553,8 +615,9 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     unsigned char* kbuf = dsm;                                                // [CH_MAX][32][128 B]
     unsigned char* vbuf = kbuf + (size_t)CH_MAX * CHUNK_BYTES;
     float* wpart = reinterpret_cast<float*>(vbuf + (size_t)CH_MAX * CHUNK_BYTES);   // [DEC_WARPS][DH + 2]
-    float* cpart = wpart + DEC_WARPS * (DH + 2);                              // [DH + 2] (CLUSTER)
-    uint64_t* bars = reinterpret_cast<uint64_t*>(cpart + DH + 2);            // CH_MAX barriers
+    float* crecv = wpart + DEC_WARPS * (DH + 2);                              // [DEC_MAX_CLUSTER][DH + 2] (CLUSTER, the CTA of part 0)
+    uint64_t* bars = reinterpret_cast<uint64_t*>(crecv + DEC_MAX_CLUSTER * (DH + 2));   // CH_MAX barriers and the one of the merge
+    uint64_t* cbar = bars + CH_MAX;
     __shared__ int s_last;
     static_assert(CH_MAX == DEC_WARPS, "a buffer and a barrier for every warp");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -577,9 +640,12 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < CH_MAX; ++i) dmbar_init(&bars[i], 1);
+        if (CLUSTER) dmbar_init(cbar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (CLUSTER && split == 0) dmbar_expect_tx(cbar, (uint32_t)(n_split * (DH + 2) * sizeof(float)));
     }
     __syncthreads();
+    if (CLUSTER) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");   // (waited for before anyone sends)
     // Warp w streams the chunks c_begin + w, + 8, + 16, … through buffer w on barrier w, on its own: it asks for
     // its next chunk as soon as it has read the one before, and waits for no other warp until the merge.
     unsigned char* my_k = kbuf + (size_t)warp * CHUNK_BYTES;
@@ -600,6 +666,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     const int my_first = c_begin + warp;
     int ok_first = 1;
     if (lane == 0 && my_first < c_end && my_first != c_new) ok_first = request(my_first, table[my_first * 32 / BT]) ? 1 : 0;
+    if (CLUSTER) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     pdl_wait();                                    // the new key and value and the query are written
     pdl_launch_dependents();
     // the query as rows 0 of the MMA's 16-row operand: only lanes 0-3 hold anything but zeros
@@ -722,7 +789,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
         for (int j = 0; j < 8; ++j) { mine[2 + 8 * j + 2 * t] = o[j][0]; mine[2 + 8 * j + 2 * t + 1] = o[j][1]; }
     }
     __syncthreads();
-    if (CLUSTER) finish_cluster<__nv_bfloat16>(wpart, cpart, DH, row, h, split, n_split, out, ld_out);
+    if (CLUSTER) finish_cluster_push<__nv_bfloat16, DH>(wpart, crecv, cbar, row, h, split, n_split, out, ld_out, dev_err);
     else finish_cta<__nv_bfloat16>(wpart, DH, row, h, H, split, n_split, partials, counters, out, ld_out, &s_last);
 }
 
@@ -735,7 +802,7 @@ int launch_mma(dim3 grid, const void* qkv, int ld, int q_off, const void* Kc, co
     if (st != VLRF_OK) return st;
     st = vlrf_make_tmap_bf16(Vc, kv_rows, 64, 64, 32, 64, &tv);
     if (st != VLRF_OK) return st;
-    const size_t smem = 1024 + (size_t)2 * 8 * 4096 + (size_t)(DEC_WARPS + 1) * (64 + 2) * sizeof(float) + 8 * 8;
+    const size_t smem = 1024 + (size_t)2 * 8 * 4096 + (size_t)(DEC_WARPS + DEC_MAX_CLUSTER) * (64 + 2) * sizeof(float) + 9 * 8;
     const bool cluster = n_split > 1 && n_split <= DEC_MAX_CLUSTER && partials == nullptr;
     auto kern = cluster ? attn_decode_mma_kernel<true> : attn_decode_mma_kernel<false>;
     static bool raised[2] = {false, false};
