@@ -341,6 +341,9 @@ def decode_splits(n_rows: int, n_heads: int, max_context: int) -> int:
     """Into how many parts a decode step cuts each context.  Measured inside whole steps of GPT-2 small,
     medium and XL: up to about 1.75 CTAs an SM in all, parts of at least 256 keys; more CTAs than that cost
     more (shared memory that the next kernel's CTAs would use, clusters to place) than they hide."""
+    forced = os.environ.get("VLRF_B200_DECODE_SPLITS")
+    if forced:
+        return max(1, min(16, int(forced)))
     pairs = max(1, n_rows * n_heads)
     want = (7 * sm_count()) // (4 * pairs)
     return max(1, min(16, want, -(-max_context // 256)))
