@@ -21,7 +21,7 @@ class KernelError(RuntimeError):
 _lib = None
 _lock = threading.Lock()
 
-_c_int, _c_float, _c_void_p, _c_longlong = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
+_c_int, _c_float, _c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
 
 #: name -> argument types; every function returns int (0 = ok) unless noted
 _SIGNATURES = {
@@ -47,7 +47,7 @@ _SIGNATURES = {
     "vlrf_gemm_splitk": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
                          _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_float,
                          _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
-                         _c_int, _c_void_p, _c_void_p, _c_void_p, _c_longlong, _c_void_p, _c_void_p],
+                         _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "vlrf_gemm_tcgen05_takes": [_c_int, _c_int, _c_int, _c_int],
     "vlrf_gemm_tcgen05": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
                           _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int,

@@ -220,8 +220,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                    const float* __restrict__ Xf, int ldx, const float* __restrict__ gamma,
                    const float* __restrict__ beta, float eps, const float* __restrict__ bias, const float* residual,
                    OT* Y, int M, int N, int K, int ldy, int act, int bm, int stages, int kb_cap, SpKvScatter kv,
-                   const float* stats_in, float* stats_out, const unsigned char* __restrict__ ahead, long long ahead_bytes,
-                   int* __restrict__ dev_err) {
+                   const float* stats_in, float* stats_out, int* __restrict__ dev_err) {
     extern __shared__ unsigned char sp_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(sp_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int B_BYTES = BN * SP_BK * 2;
@@ -316,17 +315,6 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         for (int i = 0; i < first; ++i) {
             tbar_expect_tx(&full[i], a_bytes + (LN ? 0 : B_BYTES));
             tma_load_2d(a_tiles + (size_t)i * a_bytes, &tmap_w, (kb0 + i) * SP_BK, n0, &full[i]);
-        }
-    }
-    // The weights that the step streams after these are pulled toward L2 meanwhile, every CTA asking for its share:
-    // the next product's CTAs, which can only begin to fetch once an SM has room for them, then find them there.
-    if (warp == 5 && lane == 0 && ahead_bytes > 0) {
-        const long long ctas = (long long)gridDim.x * gridDim.y, me = (long long)tile * gridDim.y + split;
-        const long long share = ((ahead_bytes + ctas - 1) / ctas + 15) & ~15ll;
-        const long long lo = me * share, hi = lo + share < ahead_bytes ? lo + share : ahead_bytes & ~15ll;
-        for (long long off = lo; off < hi; off += 8192) {
-            const uint32_t n = (uint32_t)(hi - off < 8192 ? hi - off : 8192);
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ahead + off), "r"(n) : "memory");
         }
     }
     const bool ln_warp = LN && warp != 4 && warp != 5;
@@ -712,7 +700,7 @@ SpPlan sp_plan(int M, int N, int K, int bn, bool ln) {
 template <int BN, typename OT, bool LN, bool WIDE, bool SYNC>
 int launch_sp_as(const void* X, const void* W, const float* gamma, const float* beta, float eps, const float* bias,
               const float* residual, void* Y, int M, int N, int K, int ldx, int ldy, int act, const SpKvScatter& kv,
-              const float* stats_in, float* stats_out, const void* ahead, long long ahead_bytes, int* dev_err, cudaStream_t stream) {
+              const float* stats_in, float* stats_out, int* dev_err, cudaStream_t stream) {
     const SpPlan plan = sp_plan(M, N, K, BN, LN);
     VLRF_REQUIRE(plan.smem <= 200 * 1024, "gemm_splitk: %zu bytes of shared memory", plan.smem);
     CUtensorMap tw, tx;
@@ -740,7 +728,7 @@ int launch_sp_as(const void* X, const void* W, const float* gamma, const float* 
     cudaError_t e = launch_chained_cluster(kern, dim3(plan.tiles, plan.splits), dim3(LN ? SP_THREADS_LN : SP_THREADS), plan.smem,
                                            dim3(1, plan.splits, 1), stream, tw, tx, (const float*)X, ldx, gamma, beta, eps, bias, residual,
                                            (OT*)Y, M, N, K, ldy, act, plan.bm, plan.stages, plan.kb_cap, kv, stats_in, stats_out,
-                                           (const unsigned char*)ahead, ahead_bytes, dev_err);
+                                           dev_err);
     if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "gemm_splitk: %s", cudaGetErrorString(e));
     return vlrf_check_launch("gemm_splitk");
 }
@@ -748,16 +736,16 @@ int launch_sp_as(const void* X, const void* W, const float* gamma, const float* 
 template <int BN, typename OT, bool LN>
 int launch_sp(const void* X, const void* W, const float* gamma, const float* beta, float eps, const float* bias,
               const float* residual, void* Y, int M, int N, int K, int ldx, int ldy, int act, const SpKvScatter& kv,
-              const float* stats_in, float* stats_out, const void* ahead, long long ahead_bytes, int* dev_err, cudaStream_t stream) {
+              const float* stats_in, float* stats_out, int* dev_err, cudaStream_t stream) {
     const SpPlan plan = sp_plan(M, N, K, BN, LN);
     if (BN == 16 && sp_use_mma_sync(M))
         return launch_sp_as<BN, OT, LN, false, BN == 16>(X, W, gamma, beta, eps, bias, residual, Y, M, N, K, ldx, ldy, act, kv, stats_in,
-                                                        stats_out, ahead, ahead_bytes, dev_err, stream);
+                                                        stats_out, dev_err, stream);
     if (BN > 16 && sp_is_wide(M, plan.bm, plan.splits, LN))
         return launch_sp_as<BN, OT, LN, (BN > 16 && !LN), false>(X, W, gamma, beta, eps, bias, residual, Y, M, N, K, ldx, ldy, act, kv, stats_in,
-                                             stats_out, ahead, ahead_bytes, dev_err, stream);
+                                             stats_out, dev_err, stream);
     return launch_sp_as<BN, OT, LN, false, false>(X, W, gamma, beta, eps, bias, residual, Y, M, N, K, ldx, ldy, act, kv, stats_in,
-                                           stats_out, ahead, ahead_bytes, dev_err, stream);
+                                           stats_out, dev_err, stream);
 }
 }  // namespace
 
@@ -782,9 +770,7 @@ extern "C" int vlrf_gemm_splitk(const void* X, int x_is_f32_ln, const void* W, c
                                 const int* tok_pos, int k_off, int v_off, int Hkv, int dh, int BT,
                                 // x_is_f32_ln: the row statistics of X, [M][ceil(K/32)][2]; stats_out (or null):
                                 // the same for the rows of Y, [M][ceil(N/32)][2], for a later product to use
-                                const float* stats_in, float* stats_out,
-                                // weights that the step reads next (or null): pulled toward L2 while this product runs
-                                const void* ahead, long long ahead_bytes, int* dev_err, cudaStream_t stream) {
+                                const float* stats_in, float* stats_out, int* dev_err, cudaStream_t stream) {
     VLRF_REQUIRE(vlrf_gemm_splitk_takes(M, N, K, ldx, x_is_f32_ln), "gemm_splitk: does not take M=%d N=%d K=%d ldx=%d", M, N, K, ldx);
     VLRF_REQUIRE(ldx >= K && ldy >= N && act >= 0 && act <= 2, "gemm_splitk: bad arguments");
     VLRF_REQUIRE(dev_err != nullptr, "gemm_splitk: needs the device error word");
@@ -792,9 +778,6 @@ extern "C" int vlrf_gemm_splitk(const void* X, int x_is_f32_ln, const void* W, c
     VLRF_REQUIRE(stats_out == nullptr || ((N + 31) / 32 <= SP_STAT_SEGS && out_dtype == VLRF_F32),
                  "gemm_splitk: statistics are kept of float32 rows of at most %d columns", SP_STAT_SEGS * 32);
     VLRF_REQUIRE(out_dtype == VLRF_BF16 || out_dtype == VLRF_F32, "gemm_splitk: unknown output dtype %d", out_dtype);
-    VLRF_REQUIRE(ahead_bytes >= 0 && (ahead_bytes == 0 || ahead == nullptr || (reinterpret_cast<uintptr_t>(ahead) & 15) == 0),
-                 "gemm_splitk: the weights to fetch ahead must start on a 16-byte boundary");
-    if (ahead == nullptr) ahead_bytes = 0;
     SpKvScatter kv{};
     if (Kc != nullptr) {
         VLRF_REQUIRE(Vc && block_table && tok_slot && tok_pos && Hkv > 0 && dh > 0 && BT > 0 && max_blocks > 0,
@@ -804,8 +787,8 @@ extern "C" int vlrf_gemm_splitk(const void* X, int x_is_f32_ln, const void* W, c
     }
 #define SP_GO(BNV, LNV)                                                                                                  \
     return out_dtype == VLRF_BF16                                                                                        \
-               ? launch_sp<BNV, __nv_bfloat16, LNV>(X, W, gamma, beta, eps, bias, residual, Y, M, N, K, ldx, ldy, act, kv, stats_in, stats_out, ahead, ahead_bytes, dev_err, stream) \
-               : launch_sp<BNV, float, LNV>(X, W, gamma, beta, eps, bias, residual, Y, M, N, K, ldx, ldy, act, kv, stats_in, stats_out, ahead, ahead_bytes, dev_err, stream)
+               ? launch_sp<BNV, __nv_bfloat16, LNV>(X, W, gamma, beta, eps, bias, residual, Y, M, N, K, ldx, ldy, act, kv, stats_in, stats_out, dev_err, stream) \
+               : launch_sp<BNV, float, LNV>(X, W, gamma, beta, eps, bias, residual, Y, M, N, K, ldx, ldy, act, kv, stats_in, stats_out, dev_err, stream)
     if (x_is_f32_ln) { SP_GO(16, true); }
     if (M <= 16) { SP_GO(16, false); }
     if (M <= 32) { SP_GO(32, false); }

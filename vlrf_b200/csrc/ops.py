@@ -88,14 +88,12 @@ def layernorm(x, gamma, beta, eps: float, out, rows=None) -> None:
 
 
 def linear(x, w, bias, out, *, act=None, residual=None, rows: int | None = None, kv_scatter=None,
-           stats: "RowStats | None" = None, ahead: "torch.Tensor | None" = None) -> bool:
+           stats: "RowStats | None" = None) -> bool:
     """out = act(x · wᵀ + bias) (+ residual).  x [M,K], w [N,K] (same dtype), bias/residual float32,
     out [M,N] float32 or bfloat16.  `rows` limits M to the first rows of x/out/residual.  `kv_scatter`
     (see linear_layernorm) asks the kernel to write K/V columns into a cache as well; the return value
     says whether it did (only the tensor-core kernels can).  `stats`: where the statistics of float32 result rows
-    are left when the kernel that takes the shape computes them (and where stale ones of `out` are forgotten).
-    `ahead`: the weights that the step reads after this product; a few-row kernel asks for them to be brought to L2
-    while it runs (a hint: other kernels ignore it)."""
+    are left when the kernel that takes the shape computes them (and where stale ones of `out` are forgotten)."""
     _dev(x, "x"); _dev(w, "w", x.dtype); _dev(out, "out")
     M = x.shape[0] if rows is None else rows
     K = x.shape[1]
@@ -114,7 +112,7 @@ def linear(x, w, bias, out, *, act=None, residual=None, rows: int | None = None,
         raise KernelError("linear: float32 input gives float32 output")
     if stats is not None:
         stats.written(out)
-    return _linear_dispatch(x, w, bias, out, ACT[act], residual, M, N, K, kv_scatter, stats, ahead)
+    return _linear_dispatch(x, w, bias, out, ACT[act], residual, M, N, K, kv_scatter, stats)
 
 
 #: head sizes that the attention kernels take (each checks it again; parts refuse others when they are built)
@@ -131,8 +129,6 @@ SWAPPED_MIN_COLUMNS = 16384
 #: wins at every size of GPT-2's: its CTAs leave room on an SM for the next kernel's to begin ahead, and it
 #: passes on the row statistics that the next LayerNorm needs.  The `mma.sync` kernel remains for the shapes
 #: the split-k kernel refuses and for a LayerNorm of rows whose statistics nobody left.
-#: Whether few-row products ask for the weights that follow theirs to be brought to L2 (`ahead=`).
-FETCH_WEIGHTS_AHEAD = os.environ.get("VLRF_B200_FETCH_AHEAD", "1") != "0"
 SPLITK_MIN_WEIGHT_BYTES = 0
 SPLITK_NORM_MIN_WEIGHT_BYTES = 0
 _DEV_ERR = None
@@ -257,13 +253,7 @@ def _kv_args(kv_scatter, N: int) -> list:
             kc.shape[2]]
 
 
-def _ahead_args(ahead) -> list:
-    if ahead is None or not FETCH_WEIGHTS_AHEAD or not ahead.is_cuda or not ahead.is_contiguous() or ahead.data_ptr() % 16:
-        return [0, 0]
-    return [ahead.data_ptr(), ahead.numel() * ahead.element_size()]
-
-
-def _linear_dispatch(x, w, bias, out, act, residual, M, N, K, kv_scatter=None, stats=None, ahead=None) -> bool:
+def _linear_dispatch(x, w, bias, out, act, residual, M, N, K, kv_scatter=None, stats=None) -> bool:
     bf16_out = out.dtype == torch.bfloat16
     if (x.dtype == torch.bfloat16 and M <= SKINNY_MAX_ROWS and K % 8 == 0 and USE_TCGEN05 and kv_scatter is None
             and N >= SWAPPED_MIN_COLUMNS):
@@ -278,7 +268,7 @@ def _linear_dispatch(x, w, bias, out, act, residual, M, N, K, kv_scatter=None, s
         keep = stats is not None and not bf16_out and stats.takes(M, N)
         call("vlrf_gemm_splitk", _ptr(x), 0, _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), dtype_code(out.dtype),
              M, N, K, K, N, act, 0, 0, 0.0, *_kv_args(kv_scatter if scatter else None, N), 0,
-             _ptr(stats.buffer()) if keep else 0, *_ahead_args(ahead), _ptr(_dev_err()), _stream())
+             _ptr(stats.buffer()) if keep else 0, _ptr(_dev_err()), _stream())
         if keep:
             stats.keep(out, M, N)
         return scatter
@@ -310,7 +300,7 @@ def can_fuse_layernorm(n_rows: int, width: int, w_dtype: torch.dtype) -> bool:
 
 
 def linear_layernorm(x, gamma, beta, eps: float, w, bias, out, *, act=None, rows: int | None = None,
-                     kv_scatter=None, stats: "RowStats | None" = None, ahead: "torch.Tensor | None" = None) -> None:
+                     kv_scatter=None, stats: "RowStats | None" = None) -> None:
     """out = act(LayerNorm(x) · wᵀ + bias) for few rows, the norm fused into the product's prologue.
     x float32 [M,K]; w bfloat16 [N,K]; out bfloat16 or float32.  `kv_scatter` = (k_cache, v_cache,
     block_table, tok_slot, tok_pos, k_off, v_off, n_kv_heads, head_dim) also writes those columns of the
@@ -330,8 +320,7 @@ def linear_layernorm(x, gamma, beta, eps: float, w, bias, out, *, act=None, rows
     if known is not None and _splitk_takes(M, N, K, K, True):
         # the rows' statistics are at hand: each CTA normalises only the columns it multiplies
         call("vlrf_gemm_splitk", _ptr(x), 1, _ptr(w), _ptr(bias), 0, _ptr(out), dtype_code(out.dtype), M, N, K, K, N,
-             ACT[act], _ptr(gamma), _ptr(beta), float(eps), *kv, _ptr(known), 0, *_ahead_args(ahead), _ptr(_dev_err()),
-             _stream())
+             ACT[act], _ptr(gamma), _ptr(beta), float(eps), *kv, _ptr(known), 0, _ptr(_dev_err()), _stream())
         return
     call("vlrf_gemm_skinny", _ptr(x), 1, _ptr(w), _ptr(bias), 0, _ptr(out), dtype_code(out.dtype), M, N, K, K, N,
          ACT[act], _ptr(gamma), _ptr(beta), float(eps), *kv, sm_count(), _ptr(_dev_err()), _stream())

@@ -83,15 +83,14 @@ int vlrf_gemm_tcgen05_force_width(int bn);
 // Few rows (M ≤ 64), the sum over k cut into parts whose CTAs form a cluster and add through distributed shared
 // memory.  x_is_f32_ln: X is the float32 residual stream and LayerNorm (gamma, beta, eps) is applied first, from
 // the rows' statistics `stats_in` ([M][ceil(K/32)][2], see vlrf_embed; M ≤ 16).  stats_out (or null): the same
-// statistics of the float32 rows of Y.  ahead (or null): `ahead_bytes` bytes, from a 16-byte boundary, that the step
-// reads after this product (the next product's weights); the CTAs ask for them to be brought to L2 meanwhile.
+// statistics of the float32 rows of Y.
 long long vlrf_row_stats_floats(int rows, int width);
 int vlrf_gemm_splitk_takes(int M, int N, int K, int ldx, int x_is_f32_ln);
 int vlrf_gemm_splitk(const void* X, int x_is_f32_ln, const void* W, const float* bias, const float* residual, void* Y,
                      int out_dtype, int M, int N, int K, int ldx, int ldy, int act, const float* gamma, const float* beta,
                      float eps, void* Kc, void* Vc, const int* block_table, int max_blocks, const int* tok_slot,
                      const int* tok_pos, int k_off, int v_off, int Hkv, int dh, int BT, const float* stats_in,
-                     float* stats_out, const void* ahead, long long ahead_bytes, int* dev_err, cudaStream_t stream);
+                     float* stats_out, int* dev_err, cudaStream_t stream);
 
 // Few rows, weights streamed once through persistent CTAs (`mma.sync`); x_is_f32_ln: the norm of whole rows in
 // the prologue (vlrf_gemm_skinny_ln_fits says whether M rows of K columns fit).  sm_count: CTAs to launch.

@@ -128,12 +128,9 @@ class DecoderModel:
         for i, call in enumerate(self.schedule):
             owner = i if call.reads_cache_of is None else call.reads_cache_of
             view = cache.view(owner) if cache.needs[owner] is not None else None
-            nxt = self.layers[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else None
-            ctx.ws.weights_ahead = getattr(nxt, "first_weight", None)     # a hint for this layer's last kernel
             self.layers[call.layer].forward(x, ctx, view, writes_cache=call.reads_cache_of is None)
             if not getattr(self.layers[call.layer], "leaves_row_stats", False):
                 ctx.ws.row_stats.forget()              # a block of another kind that does not vouch for them
-        ctx.ws.weights_ahead = None
         n = ctx.n_logit_rows
         logits = ctx.ws.get("logits", max(n, 1), self.vocab_size, torch.float32)
         if n == 0:

@@ -33,14 +33,7 @@ class PreNormBlock:
         self.mixer.emit_decode(program, x, self.norm1, view, writes_cache)
         self.feed_forward.emit_decode(program, x, self.norm2)
 
-    @property
-    def first_weight(self):
-        """The weight matrix this block streams first, if its mixer says."""
-        return getattr(self.mixer, "first_weight", None)
-
     def forward(self, x: torch.Tensor, ctx: StepContext, view, writes_cache: bool = True) -> None:
-        after = ctx.ws.weights_ahead                     # what the step reads after this block (the model says)
-        ctx.ws.weights_ahead = getattr(self.feed_forward, "first_weight", None)
         if getattr(self.mixer, "fuses_norm", False):
             self.mixer.forward(None, x, ctx, view, writes_cache, norm=self.norm1)
         else:
@@ -50,7 +43,6 @@ class PreNormBlock:
         # that just rewrote them says so; a part with kernels of its own need not know that such a thing exists.
         if not getattr(self.mixer, "leaves_row_stats", False):
             ctx.ws.row_stats.forget()
-        ctx.ws.weights_ahead = after
         if getattr(self.feed_forward, "fuses_norm", False):
             self.feed_forward.forward(None, x, ctx, norm=self.norm2)
         else:

@@ -27,10 +27,6 @@ class Workspace:
         #: statistics of the residual rows that the step's last product wrote (see csrc.ops.RowStats); parts hand
         #: this to the products that may leave or use them, the block forgets them after parts it cannot vouch for
         self.row_stats = RowStats(self.device)
-        #: the weight matrix that the step reads first after the part now running (the block and the model set it from
-        #: the parts' `first_weight`); a part may hand it to its last product (`ahead=`), whose kernel asks for it to
-        #: be brought to L2 meanwhile.  A hint only: None, or ignoring it, changes no result.
-        self.weights_ahead = None
 
     def get(self, name: str, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
         key = (name, rows, cols, dtype)

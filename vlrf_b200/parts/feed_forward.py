@@ -27,7 +27,6 @@ class DenseMLP:
         if w_out.shape[1] != w_in.shape[0] or w_out.shape[0] != w_in.shape[1]:
             raise ValueError("DenseMLP: the two matrices do not chain")
         self.w_in, self.b_in, self.w_out, self.b_out = w_in, b_in, w_out, b_out
-        self.first_weight = w_in             # what this part streams first (a hint for the kernel ahead of it)
         self.activation = activation
         self.inner = w_in.shape[0]
 
@@ -48,9 +47,9 @@ class DenseMLP:
         u = ctx.ws.get("ffn_inner", T, self.inner, ctx.act_dtype)
         if h is None and getattr(norm, "fusable_as", None) == "layernorm" and ops.can_fuse_layernorm(T, x.shape[1], self.w_in.dtype):
             ops.linear_layernorm(x, norm.weight, norm.bias, norm.eps, self.w_in, self.b_in, u, act=self.activation,
-                                 stats=ctx.ws.row_stats, ahead=self.w_out)
+                                 stats=ctx.ws.row_stats)
         else:
             if h is None:
                 h = norm(x, ctx.ws.get("block_normed", T, x.shape[1], ctx.act_dtype))
-            ops.linear(h, self.w_in, self.b_in, u, act=self.activation, ahead=self.w_out)
-        ops.linear(u, self.w_out, self.b_out, x, residual=x, stats=ctx.ws.row_stats, ahead=ctx.ws.weights_ahead)
+            ops.linear(h, self.w_in, self.b_in, u, act=self.activation)
+        ops.linear(u, self.w_out, self.b_out, x, residual=x, stats=ctx.ws.row_stats)

@@ -52,7 +52,6 @@ class CausalSelfAttention:
         if position is not None and getattr(position, "where", None) == "qk":
             raise NotImplementedError("attention: no position encoding acting on q/k is built into this mixer")
         self.w_qkv, self.b_qkv, self.w_out, self.b_out = w_qkv, b_qkv, w_out, b_out
-        self.first_weight = w_qkv            # what this part streams first (a hint for the kernel ahead of it)
         self.n_heads, self.n_kv_heads, self.head_dim = n_heads, n_kv_heads, head_dim
         self.scale, self.window = float(scale), int(window)
         self.q_off, self.k_off, self.v_off = 0, width_q, width_q + width_kv
@@ -81,7 +80,7 @@ class CausalSelfAttention:
                            self.n_kv_heads, self.head_dim)
                 appended = True
             ops.linear_layernorm(x, norm.weight, norm.bias, norm.eps, self.w_qkv, self.b_qkv, qkv, kv_scatter=scatter,
-                                 stats=ctx.ws.row_stats, ahead=self.w_out)
+                                 stats=ctx.ws.row_stats)
         else:
             if h is None:
                 h = norm(x, ctx.ws.get("block_normed", T, x.shape[1], ctx.act_dtype))
@@ -89,13 +88,13 @@ class CausalSelfAttention:
             if writes_cache:
                 scatter = (view.k, view.v, view.block_table, ctx.tok_slot, ctx.tok_pos, self.k_off, self.v_off,
                            self.n_kv_heads, self.head_dim)
-            appended = ops.linear(h, self.w_qkv, self.b_qkv, qkv, kv_scatter=scatter, ahead=self.w_out)   # the epilogue writes the cache if it can
+            appended = ops.linear(h, self.w_qkv, self.b_qkv, qkv, kv_scatter=scatter)   # the epilogue writes the cache if it can
         if writes_cache and not appended:
             ops.kv_append(qkv, self.k_off, self.v_off, view.k, view.v, view.block_table, ctx.tok_slot,
                           ctx.tok_pos, T, self.n_kv_heads, self.head_dim, ctx.dev_err)
         merged = ctx.ws.get("attn_out", T, self.n_heads * self.head_dim, ctx.act_dtype)
         self._attend(qkv, view, merged, ctx)
-        ops.linear(merged, self.w_out, self.b_out, x, residual=x, stats=ctx.ws.row_stats, ahead=ctx.ws.weights_ahead)
+        ops.linear(merged, self.w_out, self.b_out, x, residual=x, stats=ctx.ws.row_stats)
 
     def emit_decode(self, program, x: torch.Tensor, norm, view, writes_cache: bool = True) -> None:
         """The decode step of this mixer as operations of a decode program: norm + q/k/v projection (+ cache
