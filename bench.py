@@ -370,6 +370,12 @@ def main() -> int:
         if not args.skip_points:
             for b in (1, 64):
                 points[f"decode_b{b}"] = round(decode_device(model_dir, b, min(args.steps, 128), warmup)["tok_s"], 1)
+    if not args.skip_points and args.preset == "gpt2" and args.layers is None:
+        # the largest size of the family at its full depth, where a step is bound by bytes rather than by latencies
+        with tempfile.TemporaryDirectory(prefix="vlrf_b200_bench_") as tmp:
+            xl = decode_device(make_model_dir("gpt2-xl", None, tmp), 8, 64, warmup)
+        points["xl_decode_b8"] = round(xl["tok_s"], 1)
+        points["xl_decode_b8_hbm_frac"] = round(xl["bytes_per_step"] / (xl["ms_per_step"] / 1e3) / 1e9 / hbm_gbs, 4)
     cfg = load_preset(args.preset)
     achieved = dec["bytes_per_step"] / (dec["ms_per_step"] / 1e3) / 1e9
     pre_tflops = pre["flops"] / (pre["ms"] / 1e3) / 1e12
