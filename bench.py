@@ -336,6 +336,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the preset (named in config)")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--timeline", action="store_true",
+                    help="with --only decode and VLRF_B200_KERNEL_TRACE=1: print where the last step's kernels spent their time")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="measure one part only and print a short line (for profiling runs); the full line needs 'all'")
     args = ap.parse_args()
@@ -357,6 +359,9 @@ def main() -> int:
             dec = decode_device(model_dir, args.batch, args.steps, warmup)
             print(json.dumps({"only": "decode", "batch": args.batch, "tok_s": round(dec["tok_s"], 1),
                               "ms_per_step": round(dec["ms_per_step"], 4), "kernels_per_step": dec["kernels_per_step"]}))
+            if args.timeline:
+                from vlrf_b200 import log
+                print(log.timeline_table(log.kernel_timeline(), last=5 * dec["n_layer"]))
             return 0
         if args.only == "prefill":
             pre = prefill_device(model_dir, reps=max(1, args.steps))

@@ -38,6 +38,8 @@ _SIGNATURES = {
                           _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
                           _c_void_p, _c_void_p],
     "vlrf_set_chained_launch": [_c_int],
+    "vlrf_trace_dims": [ctypes.POINTER(_c_int)] * 3,
+    "vlrf_trace_read": [_c_void_p],
     "vlrf_gemm_skinny_ln_fits": [_c_int, _c_int],
     "vlrf_gemm_skinny": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
                          _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_float,

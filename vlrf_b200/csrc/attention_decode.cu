@@ -608,8 +608,13 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
                        const __nv_bfloat16* __restrict__ qkv, int ld, int q_off, const int* __restrict__ block_table,
                        int max_blocks, const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
                        __nv_bfloat16* __restrict__ out, int ld_out, int H, int Hkv, int BT, float scale, int window,
-                       int n_split, float* __restrict__ partials, int* __restrict__ counters, int* __restrict__ dev_err) {
+                       int n_split, float* __restrict__ partials, int* __restrict__ counters, int* __restrict__ dev_err,
+                       long long* trace) {
     constexpr int DH = 64, CHUNK_BYTES = 32 * DH * 2, CH_MAX = 8;
+    // (stations of the time stamps, kind 2: 0 the CTA begins, 1 the kernel ahead has finished, 2 warp 0's first chunk
+    // is here, 3 warp 0 has worked through its chunks, 4 all warps have, 6 the merge is sent or, part 0, the row stored)
+    const int tcta = (blockIdx.x * gridDim.y + blockIdx.y) * gridDim.z + blockIdx.z;
+    if (threadIdx.x == 0) VLRF_TRACE(trace, 2, tcta, 0);
     extern __shared__ unsigned char dsm_raw[];
     unsigned char* dsm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(dsm_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* kbuf = dsm;                                                // [CH_MAX][32][128 B]
@@ -668,6 +673,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     if (lane == 0 && my_first < c_end && my_first != c_new) ok_first = request(my_first, table[my_first * 32 / BT]) ? 1 : 0;
     if (CLUSTER) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     pdl_wait();                                    // the new key and value and the query are written
+    if (threadIdx.x == 0) VLRF_TRACE(trace, 2, tcta, 1);
     pdl_launch_dependents();
     // the query as rows 0 of the MMA's 16-row operand: only lanes 0-3 hold anything but zeros
     uint32_t qa[4][2];
@@ -700,6 +706,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
                 if (++polls > DEC_WAIT_LIMIT) { gave_up = true; break; }
             }
             if (gave_up) break;
+            if (threadIdx.x == 0 && c == my_first) VLRF_TRACE(trace, 2, tcta, 2);
             const int i = warp;
             const int k0 = c * 32;
             const uint32_t kb = dsmem_u32(kbuf + (size_t)i * CHUNK_BYTES), vb = dsmem_u32(vbuf + (size_t)i * CHUNK_BYTES);
@@ -779,6 +786,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
         }
     }
     if (gave_up && lane == 0) atomicOr(dev_err, VLRF_DEVERR_WAIT_TIMEOUT);
+    if (threadIdx.x == 0) VLRF_TRACE(trace, 2, tcta, 3);
 
     // this warp's (maximum, sum, outputs): row 0 lies in lanes 0-3, dimensions 8j + 2t and + 1; the merge
     // works with natural logarithms
@@ -789,8 +797,10 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
         for (int j = 0; j < 8; ++j) { mine[2 + 8 * j + 2 * t] = o[j][0]; mine[2 + 8 * j + 2 * t + 1] = o[j][1]; }
     }
     __syncthreads();
+    if (threadIdx.x == 0) VLRF_TRACE(trace, 2, tcta, 4);
     if (CLUSTER) finish_cluster_push<__nv_bfloat16, DH>(wpart, crecv, cbar, row, h, split, n_split, out, ld_out, dev_err);
     else finish_cta<__nv_bfloat16>(wpart, DH, row, h, H, split, n_split, partials, counters, out, ld_out, &s_last);
+    if (threadIdx.x == 0) VLRF_TRACE(trace, 2, tcta, 6);
 }
 
 int launch_mma(dim3 grid, const void* qkv, int ld, int q_off, const void* Kc, const void* Vc, long long kv_rows,
@@ -816,11 +826,12 @@ int launch_mma(dim3 grid, const void* qkv, int ld, int q_off, const void* Kc, co
     if (cluster)
         e = launch_chained_cluster(kern, grid, dim3(DEC_WARPS * 32), smem, dim3(1, 1, n_split), stream, tk, tv,
                                    (const __nv_bfloat16*)qkv, ld, q_off, block_table, max_blocks, tok_slot, tok_pos,
-                                   (__nv_bfloat16*)out, ld_out, H, Hkv, BT, scale, window, n_split, partials, counters, dev_err);
+                                   (__nv_bfloat16*)out, ld_out, H, Hkv, BT, scale, window, n_split, partials, counters, dev_err,
+                                   vlrf_trace_buffer());
     else
         e = launch_chained(kern, grid, dim3(DEC_WARPS * 32), smem, stream, tk, tv, (const __nv_bfloat16*)qkv, ld, q_off,
                            block_table, max_blocks, tok_slot, tok_pos, (__nv_bfloat16*)out, ld_out, H, Hkv, BT, scale,
-                           window, n_split, partials, counters, dev_err);
+                           window, n_split, partials, counters, dev_err, vlrf_trace_buffer());
     if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "attn_decode: %s", cudaGetErrorString(e));
     return vlrf_check_launch("attn_decode");
 }

@@ -23,6 +23,11 @@ SRC_DIR = Path(__file__).parent
 LIB_NAME = "libvlrf_b200_kernels.so"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
+# VLRF_B200_KERNEL_TRACE=1: the decode step's kernels are compiled with time stamps at the stations of their critical
+# path (see common.cuh); such a build is a measuring instrument, not the product, and is kept in a folder of its own
+KERNEL_TRACE = os.environ.get("VLRF_B200_KERNEL_TRACE", "0") not in ("", "0")
+if KERNEL_TRACE:
+    NVCC_FLAGS = NVCC_FLAGS + ["-DVLRF_KERNEL_TRACE"]
 
 
 def sources() -> list[Path]:
@@ -59,7 +64,7 @@ def build_dir() -> Path:
         if _writable(d):
             return d
         raise RuntimeError(f"VLRF_B200_BUILD_DIR={env} is not writable")
-    d = SRC_DIR / "_build"
+    d = SRC_DIR / ("_build_trace" if KERNEL_TRACE else "_build")
     if _writable(d):
         return d
     d = Path(tempfile.gettempdir()) / f"vlrf_b200_build_{os.getuid()}"

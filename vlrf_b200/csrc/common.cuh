@@ -37,6 +37,29 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 extern "C" int vlrf_chained_launch_enabled();
 
+// Time stamps inside the kernels of a decode step, compiled in only with -DVLRF_KERNEL_TRACE (build.py:
+// VLRF_B200_KERNEL_TRACE=1).  One thread of a CTA calls VLRF_TRACE(buf, kind, cta, station) at the stations of the
+// kernel's critical path; the record of a launch is found by the launch's number (%gridid), so a replayed graph
+// leaves the stamps of its last replay.  buf: [VLRF_TRACE_SLOTS][VLRF_TRACE_CTAS][2 + VLRF_TRACE_STATIONS] int64:
+// launch number, kind of kernel, then nanoseconds of the global timer (coarse: steps of a quarter microsecond).
+constexpr int VLRF_TRACE_SLOTS = 512, VLRF_TRACE_CTAS = 320, VLRF_TRACE_STATIONS = 8;
+extern "C" long long* vlrf_trace_buffer();     // device memory, or null in a build without stamps
+#ifdef VLRF_KERNEL_TRACE
+__device__ __forceinline__ void vlrf_trace_stamp(long long* buf, int kind, int cta, int station) {
+    unsigned long long gid;
+    long long t;
+    asm volatile("mov.u64 %0, %%gridid;" : "=l"(gid));
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    if (buf != nullptr && cta < VLRF_TRACE_CTAS) {
+        long long* r = buf + ((size_t)(gid % VLRF_TRACE_SLOTS) * VLRF_TRACE_CTAS + cta) * (2 + VLRF_TRACE_STATIONS);
+        r[0] = (long long)gid; r[1] = kind; r[2 + station] = t;
+    }
+}
+#define VLRF_TRACE(buf, kind, cta, station) vlrf_trace_stamp(buf, kind, cta, station)
+#else
+#define VLRF_TRACE(buf, kind, cta, station) ((void)0)
+#endif
+
 template <typename... KArgs, typename... Args>
 cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                            Args... args) {

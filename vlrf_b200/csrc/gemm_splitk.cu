@@ -220,8 +220,13 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                    const float* __restrict__ Xf, int ldx, const float* __restrict__ gamma,
                    const float* __restrict__ beta, float eps, const float* __restrict__ bias, const float* residual,
                    OT* Y, int M, int N, int K, int ldy, int act, int bm, int stages, int kb_cap, SpKvScatter kv,
-                   const float* stats_in, float* stats_out, int* __restrict__ dev_err) {
+                   const float* stats_in, float* stats_out, int* __restrict__ dev_err, long long* trace) {
     extern __shared__ unsigned char sp_raw[];
+    // (stations of the time stamps, kind 1: 0 the CTA begins, 1 the kernel ahead has finished, 2 the rows of X are in
+    // shared memory (fused norm), 3 the products are done, 4 the partial tile is sent or in place, 5 all parts are
+    // here, 6 the pieces are stored; thread 0 stamps)
+    const int tcta = blockIdx.x * gridDim.y + blockIdx.y;
+    if (threadIdx.x == 0) VLRF_TRACE(trace, 1, tcta, 0);
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(sp_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int B_BYTES = BN * SP_BK * 2;
     constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
@@ -330,6 +335,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     if (PUSH) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     pdl_launch_dependents();
     pdl_wait();                                    // the rows of X, the residual and the positions are ready
+    if (threadIdx.x == 0) VLRF_TRACE(trace, 1, tcta, 1);
 
     // pieces of the tile that this warp will finish: (row m, 32-column segment), dealt to the 4·splits
     // epilogue warps of the cluster; what the first two need from global memory is fetched now
@@ -385,6 +391,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                 // the four finishing warps read all rows: they wait for the eight that normed them
                 if (warp < 4) asm volatile("bar.sync 3, 256;" ::: "memory");
                 else asm volatile("bar.arrive 3, 256;" ::: "memory");
+                if (threadIdx.x == 0) VLRF_TRACE(trace, 1, tcta, 2);
             } else {
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the MMA reads these through the async proxy
                 __syncwarp();
@@ -436,11 +443,13 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                                                        recv, recv_bar, s_piece, segs, split, n_j);
                 else ok = sp_sync_product<1, LN>(warp, lane, M, n_kb, stages, a_tiles, a_bytes, b_tiles, B_BYTES, full, empty, s_abort,
                                                  recv, recv_bar, s_piece, segs, split, n_j);
+                if (threadIdx.x == 0) VLRF_TRACE(trace, 1, tcta, 4);
                 if (!ok) atomicExch(s_abort, 1);
             }
         }
         if (!SYNC && warp < 4) {
             const bool have = !*(volatile int*)s_abort && tbar_wait_or_abort(acc_full, 0, s_abort);
+            if (threadIdx.x == 0) VLRF_TRACE(trace, 1, tcta, 3);
             if (!have) atomicExch(s_abort, 1);
             float r[BN];
 #pragma unroll
@@ -485,11 +494,13 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         }
     }
     __syncwarp();
+    if (!SYNC && threadIdx.x == 0) VLRF_TRACE(trace, 1, tcta, 4);
     if (PUSH) {
         if (warp < 4 && !*(volatile int*)s_abort && !tbar_wait_or_abort(recv_bar, 0, s_abort)) atomicExch(s_abort, 1);
     } else {
         cluster_sync_all();                                    // every part of the tile is in shared memory
     }
+    if (threadIdx.x == 0) VLRF_TRACE(trace, 1, tcta, 5);
     if (warp < 4 && wide && !*(volatile int*)s_abort) {
         int j = 0;
         for (int u = gw; u < units; u += ustride, ++j) {
@@ -623,6 +634,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         }
     }
     __syncwarp();
+    if (threadIdx.x == 0) VLRF_TRACE(trace, 1, tcta, 6);
     if (!PUSH) cluster_sync_relaxed();                         // nobody leaves while its shared memory is being read
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -728,7 +740,7 @@ int launch_sp_as(const void* X, const void* W, const float* gamma, const float* 
     cudaError_t e = launch_chained_cluster(kern, dim3(plan.tiles, plan.splits), dim3(LN ? SP_THREADS_LN : SP_THREADS), plan.smem,
                                            dim3(1, plan.splits, 1), stream, tw, tx, (const float*)X, ldx, gamma, beta, eps, bias, residual,
                                            (OT*)Y, M, N, K, ldy, act, plan.bm, plan.stages, plan.kb_cap, kv, stats_in, stats_out,
-                                           dev_err);
+                                           dev_err, vlrf_trace_buffer());
     if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "gemm_splitk: %s", cudaGetErrorString(e));
     return vlrf_check_launch("gemm_splitk");
 }

@@ -49,6 +49,13 @@ int vlrf_device_info(int* sm_count, int* cc_major, int* cc_minor, int* max_smem_
 // Whether kernels are launched chained (programmatic stream serialization); on by default.
 int vlrf_chained_launch_enabled();
 int vlrf_set_chained_launch(int on);
+// Time stamps that the decode step's kernels leave in a build with -DVLRF_KERNEL_TRACE: the buffer's sizes (0 slots
+// in a build without stamps), and a copy of it to host memory, [slots][ctas][2 + stations] int64 (launch number,
+// kind of kernel: 1 few-row product, 2 decode attention; then the global timer's nanoseconds at every station),
+// after which the buffer is cleared.
+long long* vlrf_trace_buffer();                 // the buffer on the device (what the kernels are handed), or null
+int vlrf_trace_dims(int* slots, int* ctas, int* stations);
+int vlrf_trace_read(long long* host);
 
 // ---- embedding and LayerNorm (embed_norm.cu) ----------------------------------------------------------------
 // x[t] = wte[tokens[t]] (+ wpe[positions[t]] if wpe is not null), float32 [T][d]; tables [V][d] and [P][d] of

@@ -106,3 +106,60 @@ class KernelTimers:
 
 
 timers = KernelTimers()
+
+
+#: what the stations of a kernel's time stamps mean, by kind of kernel (vlrf_b200/csrc: gemm_splitk.cu, attention_decode.cu)
+TRACE_KINDS = {1: ("product", ["begins", "waited", "x in smem", "products", "sent", "received", "stored"]),
+               2: ("attention", ["begins", "waited", "first chunk", "warp 0 done", "all warps", "", "stored"])}
+
+
+def kernel_timeline() -> list:
+    """The time stamps that the decode step's kernels left (a build with VLRF_B200_KERNEL_TRACE=1), one record per
+    launch in launch order: {"launch", "kind", "ctas", "first": [...], "last": [...]}: per station the earliest and
+    the latest CTA, in microseconds after the previous record's last stamp (the first record: after its own first).
+    Reading clears the buffer.  A replayed graph leaves the stamps of its last replays."""
+    import ctypes
+
+    import numpy as np
+
+    from .csrc import KernelError, call_host, library
+    lib = library()
+    dims = [ctypes.c_int(0) for _ in range(3)]
+    lib.vlrf_trace_dims(*[ctypes.byref(d) for d in dims])
+    slots, ctas, stations = (d.value for d in dims)
+    if slots == 0:
+        raise KernelError("this build of the kernels has no time stamps: set VLRF_B200_KERNEL_TRACE=1 before the first import")
+    buf = np.zeros((slots, ctas, 2 + stations), dtype=np.int64)
+    call_host("vlrf_trace_read", buf.ctypes.data_as(ctypes.c_void_p))
+    records = []
+    for s in range(slots):
+        live = buf[s, :, 0] > 0
+        if not live.any():
+            continue
+        launch = int(buf[s, live, 0].max())
+        rows = buf[s][live & (buf[s, :, 0] == launch)]
+        records.append((launch, int(rows[0, 1]), rows[:, 2:].astype(np.float64)))
+    records.sort(key=lambda r: r[0])
+    out, prev_end = [], None
+    for launch, kind, t in records:
+        seen = np.where(t > 0, t, np.nan)
+        base = prev_end if prev_end is not None else np.nanmin(seen)
+        first = [None if np.isnan(v) else round((v - base) / 1e3, 2) for v in np.nanmin(seen, axis=0)] if seen.size else []
+        last = [None if np.isnan(v) else round((v - base) / 1e3, 2) for v in np.nanmax(seen, axis=0)] if seen.size else []
+        out.append({"launch": launch, "kind": kind, "ctas": int(t.shape[0]), "first": first, "last": last})
+        prev_end = np.nanmax(seen)
+    return out
+
+
+def timeline_table(records: list, last: int | None = None) -> str:
+    """The records of `kernel_timeline` (the last `last` of them) as text: per launch and station, earliest…latest CTA
+    in microseconds after the launch before it ended."""
+    lines = []
+    for r in (records[-last:] if last else records):
+        name, stations = TRACE_KINDS.get(r["kind"], (f"kind {r['kind']}", [""] * 8))
+        cells = []
+        for i, label in enumerate(stations):
+            if label and i < len(r["first"]) and r["first"][i] is not None:
+                cells.append(f"{label} {r['first'][i]:6.2f}…{r['last'][i]:6.2f}")
+        lines.append(f"{name:9} {r['ctas']:3d} CTAs | " + " | ".join(cells))
+    return "\n".join(lines)
