@@ -143,30 +143,30 @@ __device__ __forceinline__ void sp_mma16816(float (&c)[4], uint32_t a0, uint32_t
 // (row m of X, this warp's 32 columns) it is in.  An `mma.sync` has a long latency here, and the MMAs of a k block
 // that add to one accumulator would wait for one another: the four 16-wide steps of a k block have accumulators of
 // their own, which are added at the end (in a fixed order).
-template <int NT, bool LN>
-__device__ __forceinline__ bool sp_sync_product(int warp, int lane, int M, int n_kb, int stages, unsigned char* a_tiles, int a_bytes,
+template <int NT, int MT, bool LN>
+__device__ __forceinline__ bool sp_sync_product(int row0, int lane, int M, int n_kb, int stages, unsigned char* a_tiles, int a_bytes,
                                                 unsigned char* b_tiles, int b_bytes, uint64_t* full, uint64_t* empty, int* s_abort,
                                                 float* recv, uint64_t* recv_bar, const int* s_piece, int segs, int split, int n_j) {
-    float acc[SP_BK / 16][2][NT][4];
+    float acc[SP_BK / 16][MT][NT][4];
 #pragma unroll
     for (int ks = 0; ks < SP_BK / 16; ++ks)
 #pragma unroll
-        for (int a = 0; a < 2; ++a)
+        for (int a = 0; a < MT; ++a)
 #pragma unroll
             for (int b = 0; b < NT; ++b)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) acc[ks][a][b][e] = 0.f;
-    const int a_row = warp * 32 + (lane & 15);                     // + 16 for the second tile
+    const int a_row = row0 + (lane & 15);                          // + 16 for a second tile
     const int b_row = (lane & 7) + ((lane >> 4) << 3);
     for (int i = 0; i < n_kb; ++i) {
         const int s = i % stages;
         if (!tbar_wait_or_abort(&full[s], (uint32_t)((i / stages) & 1), s_abort)) return false;
         const uint32_t a_base = tsm(a_tiles + (size_t)s * a_bytes), b_base = tsm(b_tiles + (size_t)(LN ? i : s) * b_bytes);
-        uint32_t a[SP_BK / 16][2][4], b[SP_BK / 16][4];
+        uint32_t a[SP_BK / 16][MT][4], b[SP_BK / 16][4];
 #pragma unroll
         for (int ks = 0; ks < SP_BK / 16; ++ks) {
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt) {
+            for (int mt = 0; mt < MT; ++mt) {
                 const int row = a_row + mt * 16, ch = ks * 2 + (lane >> 4);
                 sp_ldsm_x4(a_base + row * 128 + ((ch ^ (row & 7)) << 4), a[ks][mt][0], a[ks][mt][1], a[ks][mt][2], a[ks][mt][3]);
             }
@@ -177,7 +177,7 @@ __device__ __forceinline__ bool sp_sync_product(int warp, int lane, int M, int n
 #pragma unroll
         for (int ks = 0; ks < SP_BK / 16; ++ks)
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt) {
+            for (int mt = 0; mt < MT; ++mt) {
                 sp_mma16816(acc[ks][mt][0], a[ks][mt][0], a[ks][mt][1], a[ks][mt][2], a[ks][mt][3], b[ks][0], b[ks][1]);
                 if (NT == 2) sp_mma16816(acc[ks][mt][1], a[ks][mt][0], a[ks][mt][1], a[ks][mt][2], a[ks][mt][3], b[ks][2], b[ks][3]);
             }
@@ -193,10 +193,10 @@ __device__ __forceinline__ bool sp_sync_product(int warp, int lane, int M, int n
         for (int e1 = 0; e1 < 2; ++e1) {
             const int m = nt * 8 + (lane & 3) * 2 + e1;
             if (m < M) {
-                const int who = s_piece[m * segs + warp], g = who & 255, j = who >> 8;
-                const uint32_t base = recv0 + (uint32_t)(((split * n_j + j) * 4 + (g & 3)) * 32 + (lane >> 2)) * 4u;
+                const int who = s_piece[m * segs + (row0 >> 5)], g = who & 255, j = who >> 8;
+                const uint32_t base = recv0 + (uint32_t)(((split * n_j + j) * 4 + (g & 3)) * 32 + (row0 & 31) + (lane >> 2)) * 4u;
 #pragma unroll
-                for (int mt = 0; mt < 2; ++mt)
+                for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
                     for (int e2 = 0; e2 < 2; ++e2) {
                         const int e = e2 * 2 + e1;
@@ -209,8 +209,8 @@ __device__ __forceinline__ bool sp_sync_product(int warp, int lane, int M, int n
 }
 
 // bm: rows of W per tile (64 or 128); stages: depth of the ring; kb_cap: most k blocks of one part
-// SYNC (up to 16 rows only): the product on `mma.sync` by the four finishing warps, each on its 32 rows of the W
-// tile, straight from the ring (ldmatrix reads the 128-byte swizzle), the accumulators in registers: with so few
+// SYNC (up to 16 rows only): the product on `mma.sync` by the CTA's warps (the eight that normed the rows, each on
+// 16 rows of the W tile, or the four finishing warps, each on 32), straight from the ring (ldmatrix reads the 128-byte swizzle), the accumulators in registers: with so few
 // rows an MMA is a few cycles of work, and the one thread that issues `tcgen05.mma`, its commit, the barrier and
 // the read-back from tensor memory are a longer chain than eight warp-level MMAs a k block.
 // WIDE: the pieces of the finished tile are 32 lanes × 4 columns (many rows) instead of 32 lanes × 1 column
@@ -281,7 +281,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 
     if (threadIdx.x == 0) {
         // (a stage is given back by the commit of its MMAs, or by every warp that read it)
-        for (int s = 0; s < stages; ++s) { tbar_init(&full[s], 1); tbar_init(&empty[s], SYNC ? (uint32_t)min(4, bm >> 5) : 1u); }
+        for (int s = 0; s < stages; ++s) { tbar_init(&full[s], 1); tbar_init(&empty[s], SYNC ? (uint32_t)(LN ? min(8, bm >> 4) : min(4, bm >> 5)) : 1u); }
         tbar_init(acc_full, 1);
         tbar_init(x_ready, 8);
         tbar_init(recv_bar, 1);
@@ -294,6 +294,25 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                 for (int u = split * 4 + w; u < units_n; u += ustride) ++pieces;
             tbar_expect_tx(recv_bar, (uint32_t)(pieces * 32 * splits * 4));
         }
+    }
+    // The cache's block and row of every row's token.  Positions and block tables do not come from the kernel ahead:
+    // a product is let go by a product ahead of it at once, but the nearest kernel ahead that is no product (the
+    // attention, the embedding) let its successors go only after its own wait, and whatever wrote positions and tables
+    // (the step before's sampling kernel, copies from the host) lies before that kernel (common.cuh).
+    if (kv.Kc != nullptr && (int)threadIdx.x < 64) {
+        const int m = threadIdx.x;
+        int blk = -2, row = 0;                                  // −2: nothing to write for this row
+        if (m < M) {
+            const int slot = kv.tok_slot[m];
+            if (slot >= 0) {
+                const int pos = kv.tok_pos[m];
+                blk = kv.block_table[(size_t)slot * kv.max_blocks + pos / kv.BT];
+                row = pos % kv.BT;
+                if (blk < 0 && blockIdx.x == 0 && blockIdx.y == 0) atomicOr(dev_err, VLRF_DEVERR_NO_BLOCK);
+            }
+        }
+        s_kv_blk[m] = blk;
+        s_kv_row[m] = row;
     }
     if (SYNC && (int)threadIdx.x < units_n && threadIdx.x < 64) s_piece[threadIdx.x] = ((int)threadIdx.x % ustride) | (((int)threadIdx.x / ustride) << 8);
     if (warp == 4) {
@@ -388,10 +407,19 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                 else sp_norm_row<SP_LN_MAX_KB / 2, SP_STAT_SEGS / 32>(row, st, lane, m, k_lo, k_hi, K, G, inv_K, eps, s_gamma, s_beta, b_tiles, B_BYTES);
             }
             if (SYNC) {
-                // the four finishing warps read all rows: they wait for the eight that normed them
-                if (warp < 4) asm volatile("bar.sync 3, 256;" ::: "memory");
-                else asm volatile("bar.arrive 3, 256;" ::: "memory");
+                // every warp reads all rows: it waits for the others that normed them; then each multiplies 16 rows
+                // of the W tile (an `mma.sync` is slow here, so the more warps share them the better)
+                asm volatile("bar.sync 3, 256;" ::: "memory");
                 if (threadIdx.x == 0) VLRF_TRACE(trace, 1, tcta, 2);
+                if (lw * 16 < bm && !*(volatile int*)s_abort) {
+                    bool ok;
+                    if (M > 8) ok = sp_sync_product<2, 1, LN>(lw * 16, lane, M, n_kb, stages, a_tiles, a_bytes, b_tiles, B_BYTES, full, empty,
+                                                              s_abort, recv, recv_bar, s_piece, segs, split, n_j);
+                    else ok = sp_sync_product<1, 1, LN>(lw * 16, lane, M, n_kb, stages, a_tiles, a_bytes, b_tiles, B_BYTES, full, empty,
+                                                        s_abort, recv, recv_bar, s_piece, segs, split, n_j);
+                    if (!ok) atomicExch(s_abort, 1);
+                }
+                if (threadIdx.x == 0) VLRF_TRACE(trace, 1, tcta, 4);
             } else {
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the MMA reads these through the async proxy
                 __syncwarp();
@@ -399,21 +427,6 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             }
         }
         if (warp < 4) {
-            if (kv.Kc != nullptr && (int)threadIdx.x < 64) {
-                const int m = threadIdx.x;
-                int blk = -2, row = 0;                          // −2: nothing to write for this row
-                if (m < M) {
-                    const int slot = kv.tok_slot[m];
-                    if (slot >= 0) {
-                        const int pos = kv.tok_pos[m];
-                        blk = kv.block_table[(size_t)slot * kv.max_blocks + pos / kv.BT];
-                        row = pos % kv.BT;
-                        if (blk < 0 && tile == 0 && split == 0) atomicOr(dev_err, VLRF_DEVERR_NO_BLOCK);
-                    }
-                }
-                s_kv_blk[m] = blk;
-                s_kv_row[m] = row;
-            }
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 const int u = gw + j * ustride;
@@ -436,13 +449,13 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                 }
             }
         }
-        if (SYNC && warp < 4) {
+        if (SYNC && !LN && warp < 4) {
             if (warp * 32 < bm && !*(volatile int*)s_abort) {
                 bool ok;
-                if (M > 8) ok = sp_sync_product<2, LN>(warp, lane, M, n_kb, stages, a_tiles, a_bytes, b_tiles, B_BYTES, full, empty, s_abort,
-                                                       recv, recv_bar, s_piece, segs, split, n_j);
-                else ok = sp_sync_product<1, LN>(warp, lane, M, n_kb, stages, a_tiles, a_bytes, b_tiles, B_BYTES, full, empty, s_abort,
-                                                 recv, recv_bar, s_piece, segs, split, n_j);
+                if (M > 8) ok = sp_sync_product<2, 2, LN>(warp * 32, lane, M, n_kb, stages, a_tiles, a_bytes, b_tiles, B_BYTES, full, empty, s_abort,
+                                                          recv, recv_bar, s_piece, segs, split, n_j);
+                else ok = sp_sync_product<1, 2, LN>(warp * 32, lane, M, n_kb, stages, a_tiles, a_bytes, b_tiles, B_BYTES, full, empty, s_abort,
+                                                    recv, recv_bar, s_piece, segs, split, n_j);
                 if (threadIdx.x == 0) VLRF_TRACE(trace, 1, tcta, 4);
                 if (!ok) atomicExch(s_abort, 1);
             }
