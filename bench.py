@@ -337,7 +337,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the preset (named in config)")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--timeline", action="store_true",
-                    help="with --only decode and VLRF_B200_KERNEL_TRACE=1: print where the last step's kernels spent their time")
+                    help="with --only decode or prefill and VLRF_B200_KERNEL_TRACE=1: print where the last step's kernels spent their time")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="measure one part only and print a short line (for profiling runs); the full line needs 'all'")
     args = ap.parse_args()
@@ -366,6 +366,9 @@ def main() -> int:
         if args.only == "prefill":
             pre = prefill_device(model_dir, reps=max(1, args.steps))
             print(json.dumps({"only": "prefill", "tokens": pre["tokens"], "ms": round(pre["ms"], 4)}))
+            if args.timeline:
+                from vlrf_b200 import log
+                print(log.timeline_table(log.kernel_timeline(), last=5 * full_layers if args.layers is None else 5 * args.layers))
             return 0
         dec = decode_device(model_dir, args.batch, args.steps, warmup)
         e2e = decode_e2e(model_dir, args.batch, dec["steps"], warmup)

@@ -74,8 +74,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
                        int max_blocks, const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
                        const int* __restrict__ seq_pos0, __nv_bfloat16* __restrict__ out, int ld_out, int H, int Hkv,
                        float scale, int window, int n_parts, float* __restrict__ partials, int* __restrict__ counters,
-                       int* __restrict__ dev_err) {
+                       int* __restrict__ dev_err, long long* trace) {
     extern __shared__ unsigned char ft_raw[];
+    // (stations of the time stamps, kind 4: 0 the CTA begins, 1 the kernel ahead has finished, 6 the CTA is done)
+    const int tcta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    if (threadIdx.x == 0) VLRF_TRACE(trace, 4, tcta, 0);
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(ft_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* q_tile = smem;                                    // [128][128 B]
     unsigned char* kv_tiles = smem + FT_TILE;                        // [3][128][128 B]: K_0, V_0, K_1, V_1, … in turn
@@ -115,6 +118,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     pdl_wait();
+    if (threadIdx.x == 0) VLRF_TRACE(trace, 4, tcta, 1);
     pdl_launch_dependents();
     const int row0 = seq_start[seq], row_end = seq_start[seq + 1], slot = seq_slot[seq], pos0 = seq_pos0[seq];
     const int n_new = row_end - row0;
@@ -396,6 +400,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     if (warp == 4) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_s), "r"((uint32_t)FT_TMEM_COLS) : "memory");
     }
+    if (threadIdx.x == 0) VLRF_TRACE(trace, 4, tcta, 6);
     if (threadIdx.x == 0 && *s_abort) atomicOr(dev_err, VLRF_DEVERR_WAIT_TIMEOUT);
 }
 }  // namespace
@@ -446,7 +451,7 @@ extern "C" int vlrf_attn_prefill_tc(const void* qkv, int ld, int q_off, const vo
     dim3 grid(H, n_seqs, (unsigned)(tiles * n_parts));
     cudaError_t e = launch_chained(attn_prefill_tc_kernel, grid, dim3(FT_THREADS), smem, stream, tq, tk, tv, q_off, block_table,
                                    max_blocks, seq_slot, seq_start, seq_pos0, (__nv_bfloat16*)out, ld_out, H, Hkv, scale,
-                                   window, n_parts, partials, counters, dev_err);
+                                   window, n_parts, partials, counters, dev_err, vlrf_trace_buffer());
     if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "attn_prefill_tc: %s", cudaGetErrorString(e));
     return vlrf_check_launch("attn_prefill_tc");
 }

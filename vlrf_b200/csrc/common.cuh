@@ -42,7 +42,7 @@ extern "C" int vlrf_chained_launch_enabled();
 // kernel's critical path; the record of a launch is found by the launch's number (%gridid), so a replayed graph
 // leaves the stamps of its last replay.  buf: [VLRF_TRACE_SLOTS][VLRF_TRACE_CTAS][2 + VLRF_TRACE_STATIONS] int64:
 // launch number, kind of kernel, then nanoseconds of the global timer (coarse: steps of a quarter microsecond).
-constexpr int VLRF_TRACE_SLOTS = 512, VLRF_TRACE_CTAS = 320, VLRF_TRACE_STATIONS = 8;
+constexpr int VLRF_TRACE_SLOTS = 512, VLRF_TRACE_CTAS = 512, VLRF_TRACE_STATIONS = 8;
 extern "C" long long* vlrf_trace_buffer();     // device memory, or null in a build without stamps
 #ifdef VLRF_KERNEL_TRACE
 __device__ __forceinline__ void vlrf_trace_stamp(long long* buf, int kind, int cta, int station) {

@@ -66,8 +66,11 @@ template <int BN, int STAGES, typename OT, bool SWAP>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                     const float* __restrict__ bias, const float* residual, OT* Y, int M, int N, int K, int ldy,
-                    int act, TcKvScatter kv, int* __restrict__ dev_err) {
+                    int act, TcKvScatter kv, int* __restrict__ dev_err, long long* trace) {
     extern __shared__ unsigned char tc_raw[];
+    // (stations of the time stamps, kind 3: 0 the CTA begins, 1 the kernel ahead has finished, 2 the first tile's
+    // accumulator is complete, 3 the last tile's, 6 the last tile is stored; thread 0 stamps)
+    if (threadIdx.x == 0) VLRF_TRACE(trace, 3, (int)blockIdx.x, 0);
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int KA = tc_atoms(BN);
     constexpr int A_ATOM = TC_BM * TC_BK * 2, B_ATOM = BN * TC_BK * 2;           // bytes of one atom of each operand
@@ -125,6 +128,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     }
     pdl_launch_dependents();
     pdl_wait();                                    // X (and the residual) come from the kernel before
+    if (threadIdx.x == 0) VLRF_TRACE(trace, 3, (int)blockIdx.x, 1);
 
     if (warp == 8) {
         if (lane == 0) {
@@ -202,6 +206,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                 }
             }
             if (*(volatile int*)s_abort || !tbar_wait_or_abort(&acc_full[b], (tc >> 1) & 1, s_abort)) { atomicExch(s_abort, 1); break; }
+            if (threadIdx.x == 0) { if (tc == 0) VLRF_TRACE(trace, 3, (int)blockIdx.x, 2); VLRF_TRACE(trace, 3, (int)blockIdx.x, 3); }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t tmem_d = tmem_base + b * ACC_STRIDE + ((uint32_t)(q * 32) << 16);
             if (SWAP) {
@@ -379,6 +384,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
             }
         }
     }
+    if (threadIdx.x == 0) VLRF_TRACE(trace, 3, (int)blockIdx.x, 6);
     // everyone meets here on every path; then the allocating warp gives the tensor memory back
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -409,7 +415,7 @@ int launch_tc(const void* X, const void* W, const float* bias, const float* resi
     const int sms = sm_count_cached();
     dim3 grid((unsigned)(tiles < sms ? tiles : sms));          // persistent: one CTA per SM at most
     cudaError_t e = launch_chained(kern, grid, dim3(TC_THREADS), smem, stream, tx, tw, bias, residual, (OT*)Y, M, N, K, ldy,
-                                   act, kv, dev_err);
+                                   act, kv, dev_err, vlrf_trace_buffer());
     if (e != cudaSuccess) return vlrf_fail(VLRF_ERR_CUDA, "gemm_tcgen05: %s", cudaGetErrorString(e));
     return vlrf_check_launch("gemm_tcgen05");
 }

@@ -51,7 +51,7 @@ int vlrf_chained_launch_enabled();
 int vlrf_set_chained_launch(int on);
 // Time stamps that the decode step's kernels leave in a build with -DVLRF_KERNEL_TRACE: the buffer's sizes (0 slots
 // in a build without stamps), and a copy of it to host memory, [slots][ctas][2 + stations] int64 (launch number,
-// kind of kernel: 1 few-row product, 2 decode attention; then the global timer's nanoseconds at every station),
+// kind of kernel: 1 few-row product, 2 decode attention, 3 many-row product, 4 prompt attention; then the global timer's nanoseconds at every station),
 // after which the buffer is cleared.
 long long* vlrf_trace_buffer();                 // the buffer on the device (what the kernels are handed), or null
 int vlrf_trace_dims(int* slots, int* ctas, int* stations);

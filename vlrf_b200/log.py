@@ -110,7 +110,9 @@ timers = KernelTimers()
 
 #: what the stations of a kernel's time stamps mean, by kind of kernel (vlrf_b200/csrc: gemm_splitk.cu, attention_decode.cu)
 TRACE_KINDS = {1: ("product", ["begins", "waited", "x in smem", "products", "sent", "received", "stored"]),
-               2: ("attention", ["begins", "waited", "first chunk", "warp 0 done", "all warps", "", "stored"])}
+               2: ("attention", ["begins", "waited", "first chunk", "warp 0 done", "all warps", "", "stored"]),
+               3: ("gemm", ["begins", "waited", "first tile", "last tile", "", "", "stored"]),
+               4: ("attn", ["begins", "waited", "", "", "", "", "done"])}
 
 
 def kernel_timeline() -> list:
