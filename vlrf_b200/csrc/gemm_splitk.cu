@@ -1,30 +1,42 @@
-// Y[M,N] = act(X[M,K] · W[N,K]^T + bias) (+ residual) for few rows (M ≤ 64) on the tcgen05 tensor cores,
-// with the sum over k cut into parts: the decode step's products for layers too wide for one CTA to
-// stream a whole group of weight rows.
+// Y[M,N] = act(X[M,K] · W[N,K]^T + bias) (+ residual) for few rows (M ≤ 64) on the tensor cores, with the
+// sum over k cut into parts: the decode step's products.
 //
-// The product is bound by reading W once.  W is the 128-row operand of the MMA (a tile of 128 output
-// columns), the few rows of X are its N (16, 32 or 64), so the accumulator in tensor memory holds Yᵀ.  A
-// layer's matrices have only N/128 such tiles, too few to keep HBM busy, so the grid is tiles × splits and
-// the `splits` CTAs of a tile form a thread-block cluster: CTA (tile, s) streams the 64-wide k blocks of
-// part s through a ring of shared-memory stages (TMA, 128-byte swizzle), one elected thread issues
-// `tcgen05.mma` per block.  The finished tile is dealt to the warps of all CTAs of the cluster in pieces (a row,
-// 32 columns); every CTA sends each piece of its partial tile into the shared memory of the CTA whose warp
-// finishes that piece, as stores that count down a barrier there (`st.async`), so a piece crosses the cluster
-// once and nobody waits at a cluster barrier or reads another CTA's memory on the way.  The receiving warp
-// adds the parts in the order of their CTAs, so the result does not depend on timing; it then applies bias, GELU
-// and the residual sum (reference include/model/feedforward.hpp:54-76,
-// include/model/transformer_block.hpp:153,158), stores the piece and, for a fused q/k/v projection, scatters K
-// and V columns into the paged cache (reference include/model/kv_cache.hpp:215-251).  A CTA leaves when it has
-// received all it is due, which is after everyone has stopped writing to it.
+// Such a product reads W once and is far too little work for either roofline: what it costs is the chain of
+// latencies between "the rows of X are there" and "the rows of Y are there".  A layer's matrices have only N/128
+// tiles of 128 output columns, too few to keep HBM busy, so the grid is tiles × splits and the `splits` CTAs of a
+// tile form a thread-block cluster: CTA (tile, s) asks for the 64-wide k blocks of part s (TMA, 128-byte swizzle; a
+// ring of shared-memory stages where a part is larger than the ring) before the kernel ahead has finished, since the
+// weights depend on nothing.
 //
-// A tile may also have 64 rows of W only (twice as many tiles for narrow matrices): the MMA still works on
-// 128 rows, the upper 64 being whatever follows in shared memory, and the upper 64 lanes of the accumulator
-// are never read.
+// The product itself, by the number of rows:
+//   up to 8 rows (SYNC)  `mma.sync` by the CTA's warps, each on 16 (or 32) rows of the W tile read from the ring with
+//       ldmatrix, times all rows of X, accumulators in registers.  One thread issuing `tcgen05.mma`, its commit, a
+//       barrier and the read-back from tensor memory are the longer chain for so little work.
+//   more rows  W is the 128-row operand of `tcgen05.mma`, the rows of X its N (16, 32 or 64), the accumulator in
+//       tensor memory holds Yᵀ; one elected thread issues the MMAs, four warps read the accumulator back.
 //
-// LN: the rows of X are the float32 residual stream; eight warps compute the LayerNorm (statistics in
-// float32 over the whole row, held in registers for both passes; reference include/model/ops.hpp:443-476)
-// and write this CTA's part of the normalised rows as bfloat16 into shared memory in the layout TMA would
-// have produced, while the weight copies are already in flight.
+// The sum over the parts: the finished tile is dealt to the warps of all CTAs of the cluster in pieces.
+//   up to 16 rows (PUSH)  a piece is a row of Y, 32 columns; every thread sends each value of its partial tile into
+//       the shared memory of the CTA whose warp finishes the piece, as a store that counts down a barrier there
+//       (`st.async`): a piece crosses the cluster once, nobody waits at a cluster barrier or reads another CTA's
+//       memory, and a CTA leaves when it has received all it is due (which is after everyone stopped writing to it).
+//   more rows  every CTA keeps its partial tile; after a cluster barrier the finishing warps read their pieces from
+//       every CTA through distributed shared memory, and a second barrier keeps every CTA's memory alive until then
+//       (a store per value costs more than it saves there).
+// Either way a warp adds the parts in the order of their CTAs, so the result does not depend on timing; it then
+// applies bias, GELU and the residual sum (reference include/model/feedforward.hpp:54-76,
+// include/model/transformer_block.hpp:153,158), stores the piece, leaves the row statistics a later LayerNorm needs
+// and, for a fused q/k/v projection, scatters K and V columns into the paged cache (reference
+// include/model/kv_cache.hpp:215-251; the cache row of every token is looked up before the wait).
+//
+// A tile may also have 64 rows of W only (twice as many tiles for narrow matrices); with `tcgen05.mma` the MMA still
+// works on 128 rows, the upper 64 being whatever follows in shared memory, and the upper 64 lanes of the
+// accumulator are never read.
+//
+// LN: the rows of X are the float32 residual stream; eight warps compute the LayerNorm of this CTA's k range (mean
+// and variance from the row statistics that the kernel which wrote the rows left; reference
+// include/model/ops.hpp:443-476) and write the normalised rows as bfloat16 into shared memory in the layout TMA
+// would have produced, while the weight copies are already in flight.
 //
 // Launched "chained": weights are requested before the kernel ahead has finished, activations only after.
 // Every wait on an mbarrier is bounded; a CTA that gives up sets the device error word, sends nothing (its
