@@ -9,7 +9,7 @@
 // weights depend on nothing.
 //
 // The product itself, by the number of rows:
-//   up to 8 rows (SYNC)  `mma.sync` by the CTA's warps, each on 16 (or 32) rows of the W tile read from the ring with
+//   up to 16 rows (SYNC)  `mma.sync` by the CTA's warps, each on 16 (or 32) rows of the W tile read from the ring with
 //       ldmatrix, times all rows of X, accumulators in registers.  One thread issuing `tcgen05.mma`, its commit, a
 //       barrier and the read-back from tensor memory are the longer chain for so little work.
 //   more rows  W is the 128-row operand of `tcgen05.mma`, the rows of X its N (16, 32 or 64), the accumulator in
@@ -681,15 +681,15 @@ int sp_sm_count() {
     return sms;
 }
 
-// Which tensor-core path a product of M ≤ 16 rows takes: `mma.sync` up to 8 rows (measured inside whole decode
-// steps of GPT-2 small: 0.262 against 0.302 ms at batch 1, 0.307 against 0.315 at batch 8, 0.383 against 0.373 at
-// batch 16), else `tcgen05.mma` as the products of more rows do.  VLRF_B200_SPLITK_MMA=tcgen05 or =sync in the
-// environment sends all of them one way (for measurements).
+// Which tensor-core path a product of M ≤ 16 rows takes: `mma.sync` (measured inside whole decode steps of GPT-2
+// small against `tcgen05.mma`: 0.262 against 0.302 ms at batch 1, 0.290 against 0.315 at batch 8, 0.354 against 0.369 at
+// batch 16).  VLRF_B200_SPLITK_MMA=tcgen05 in the environment sends them the way of the products of more rows, =8
+// those of more than 8 rows (for measurements).
 bool sp_use_mma_sync(int M) {
     static int v = -1;
     if (v < 0) {
         const char* e = getenv("VLRF_B200_SPLITK_MMA");
-        v = e == nullptr ? 8 : strcmp(e, "tcgen05") == 0 ? 0 : strcmp(e, "sync") == 0 ? 16 : 8;
+        v = e == nullptr ? 16 : strcmp(e, "tcgen05") == 0 ? 0 : strcmp(e, "8") == 0 ? 8 : 16;
     }
     return M <= v;
 }
