@@ -54,13 +54,18 @@ class DecoderModel:
         same work for the same shapes without asking the device anything.  A part whose control flow
         depends on device values (say, a feed-forward that gathers each expert's tokens on the host) says
         so with a class or instance attribute `replayable = False`; steps then launch plainly."""
+        cached = self.__dict__.get("_replayable")          # (asked at every step; the parts of a model do not change)
+        if cached is not None:
+            return cached
+
         def ok(obj):
             return getattr(obj, "replayable", True)
         parts = [self.embedding, self.final_norm, self.head]
         for layer in self.layers:
             parts.append(layer)
             parts.extend(v for v in vars(layer).values() if not isinstance(v, (int, float, str, torch.Tensor)))
-        return all(ok(p) for p in parts)
+        self.__dict__["_replayable"] = all(ok(p) for p in parts)
+        return self.__dict__["_replayable"]
 
     def describe_kernels(self, block_tokens: int = 64) -> list:
         """For every layer whose mixer can say, which attention kernels its sizes get (see the mixers' `kernels`)."""

@@ -97,7 +97,8 @@ class Engine:
             if self.cache.lengths[e.slot] + len(e.tokens) > self.model.max_seq_len:
                 raise StepError(f"slot {e.slot}: {self.cache.lengths[e.slot]} + {len(e.tokens)} tokens exceed the "
                                 f"{self.model.max_seq_len} positions of the model")
-            arr = np.asarray(e.tokens, dtype=np.int64)         # (a list is converted once: this is most of a long prompt's host time)
+            # (a list is converted once: this is most of a long prompt's host time; an integer array is taken as it is)
+            arr = e.tokens if isinstance(e.tokens, np.ndarray) and e.tokens.dtype.kind in "iu" else np.asarray(e.tokens, dtype=np.int64)
             if arr.min() < 0 or arr.max() >= vocab:
                 bad = int(arr[(arr < 0) | (arr >= vocab)][0])
                 raise StepError(f"slot {e.slot}: token id {bad} lies outside the vocabulary of {vocab}")
