@@ -172,7 +172,7 @@ def split_k_always(monkeypatch):
 
 # few and many tiles, one and many parts, 64- and 128-row tiles, tails in M, N and K
 SPLIT_K_SHAPES = [(1, 200, 72), (8, 512, 256), (16, 1600, 1600), (17, 1000, 320), (33, 136, 200), (64, 768, 3072),
-                  (5, 96, 64), (8, 6400, 1600), (40, 130, 8)]
+                  (5, 96, 64), (8, 6400, 1600), (40, 130, 8), (4, 1600, 6400), (12, 768, 3072), (16, 200, 4096)]
 
 
 @pytest.mark.parametrize("M,N,K", SPLIT_K_SHAPES)
