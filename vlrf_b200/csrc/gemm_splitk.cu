@@ -15,15 +15,13 @@
 //   more rows  W is the 128-row operand of `tcgen05.mma`, the rows of X its N (16, 32 or 64), the accumulator in
 //       tensor memory holds Yᵀ; one elected thread issues the MMAs, four warps read the accumulator back.
 //
-// The sum over the parts: the finished tile is dealt to the warps of all CTAs of the cluster in pieces.
-//   up to 16 rows (PUSH)  a piece is a row of Y, 32 columns; every thread sends each value of its partial tile into
-//       the shared memory of the CTA whose warp finishes the piece, as a store that counts down a barrier there
-//       (`st.async`): a piece crosses the cluster once, nobody waits at a cluster barrier or reads another CTA's
-//       memory, and a CTA leaves when it has received all it is due (which is after everyone stopped writing to it).
-//   more rows  every CTA keeps its partial tile; after a cluster barrier the finishing warps read their pieces from
-//       every CTA through distributed shared memory, and a second barrier keeps every CTA's memory alive until then
-//       (a store per value costs more than it saves there).
-// Either way a warp adds the parts in the order of their CTAs, so the result does not depend on timing; it then
+// The sum over the parts: the finished tile is dealt to the warps of all CTAs of the cluster in pieces: a row of Y by
+// 32 columns up to 16 rows, four rows by 32 columns beyond.  Every thread sends each value of its partial tile (four
+// rows of a column at once where pieces have four) into the shared memory of the CTA whose warp finishes the piece, as
+// a store that counts down a barrier there (`st.async`): a piece crosses the cluster once, nobody waits at a cluster
+// barrier or reads another CTA's memory, and a CTA leaves when it has received all it is due (which is after everyone
+// stopped writing to it).
+// A warp adds the parts in the order of their CTAs, so the result does not depend on timing; it then
 // applies bias, GELU and the residual sum (reference include/model/feedforward.hpp:54-76,
 // include/model/transformer_block.hpp:153,158), stores the piece, leaves the row statistics a later LayerNorm needs
 // and, for a fused q/k/v projection, scatters K and V columns into the paged cache (reference
@@ -123,12 +121,10 @@ __device__ __forceinline__ void sp_norm_row(const float* __restrict__ row, const
     }
 }
 
-// Whether the finished tile is dealt out in pieces of 32 lanes × 4 columns (many rows) or 32 lanes × 1 column.
-__host__ __device__ inline bool sp_is_wide(int M, int bm, int splits, bool ln) { return !ln && M > 16 && M * (bm / 32) > 4 * 4 * splits; }
-// Floats of the buffer in which a CTA receives its warps' pieces (a row, 32 columns) from every part.
-__host__ __device__ inline int sp_recv_floats(int M, int bm, int splits) {
-    const int n_j = (M * (bm >> 5) + 4 * splits - 1) / (4 * splits);
-    return splits * n_j * 4 * 32;
+// Floats of the buffer in which a CTA receives its warps' pieces (rp rows, 32 columns) from every part.
+__host__ __device__ inline int sp_recv_floats(int M, int bm, int splits, int rp) {
+    const int n_j = (((M + rp - 1) / rp) * (bm >> 5) + 4 * splits - 1) / (4 * splits);
+    return splits * n_j * 4 * 32 * rp;
 }
 // a float into the shared memory of CTA `rank` of the cluster (at the place `own_addr` has in this CTA), counted
 // down on the barrier at `own_bar`'s place there
@@ -220,13 +216,21 @@ __device__ __forceinline__ bool sp_sync_product(int row0, int lane, int M, int n
     return true;
 }
 
+// four floats at once
+__device__ __forceinline__ void sp_send_f32x4(uint32_t own_addr, uint32_t own_bar, uint32_t rank, float a, float b, float c, float d) {
+    uint32_t addr, bar;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(own_addr), "r"(rank));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(bar) : "r"(own_bar), "r"(rank));
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+                 ::"r"(addr), "r"(__float_as_uint(a)), "r"(__float_as_uint(b)), "r"(__float_as_uint(c)), "r"(__float_as_uint(d)), "r"(bar) : "memory");
+}
+
 // bm: rows of W per tile (64 or 128); stages: depth of the ring; kb_cap: most k blocks of one part
 // SYNC (up to 16 rows only): the product on `mma.sync` by the CTA's warps (the eight that normed the rows, each on
 // 16 rows of the W tile, or the four finishing warps, each on 32), straight from the ring (ldmatrix reads the 128-byte swizzle), the accumulators in registers: with so few
 // rows an MMA is a few cycles of work, and the one thread that issues `tcgen05.mma`, its commit, the barrier and
 // the read-back from tensor memory are a longer chain than eight warp-level MMAs a k block.
-// WIDE: the pieces of the finished tile are 32 lanes × 4 columns (many rows) instead of 32 lanes × 1 column
-template <int BN, typename OT, bool LN, bool WIDE, bool SYNC>
+template <int BN, typename OT, bool LN, bool SYNC>
 __global__ void __launch_bounds__(LN ? SP_THREADS_LN : SP_THREADS, 2)
 gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                    const float* __restrict__ Xf, int ldx, const float* __restrict__ gamma,
@@ -251,29 +255,20 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     unsigned char* after_b = b_tiles + (size_t)(LN ? kb_cap : stages) * B_BYTES;
     float* s_gamma = reinterpret_cast<float*>(after_b);              // LN: [kb_cap·64] this part's norm weights
     float* s_beta = s_gamma + (LN ? kb_cap * SP_BK : 0);
-    // up to 16 rows: what this CTA receives of the tile, the pieces its warps finish from every part of the sum
-    // (below); more rows: this CTA's part of the tile, [m][bm] float32, which the others read
+    // what this CTA receives of the tile: the pieces its warps finish, from every part of the sum
     float* recv = s_beta + (LN ? kb_cap * SP_BK : 0);
-    float* part = recv;
-    // The finished tile is dealt to the 4·splits epilogue warps of the cluster in pieces of 32 lanes × 4
-    // columns: one row of a 128-row tile, two rows of a 64-row tile.
-    const int lpr = bm >> 2, rpp = 32 / lpr;                         // lanes a row, rows a piece
-    const int units = (M + rpp - 1) / rpp, ustride = 4 * (int)gridDim.y;
-    // … unless that leaves most warps without a piece (few rows): then pieces of 32 lanes × 1 column
-    const int segs = bm >> 5, units_n = M * segs;
-    constexpr bool wide = WIDE;
-    // Up to 16 rows (PUSH): every CTA of the cluster sends each piece of its partial tile to the CTA whose warp
-    // finishes that piece, as stores into that CTA's shared memory that count down a barrier there (`st.async`):
-    // recv[source part][piece of the warp j][warp][32 lanes].  The receiver waits on its own barrier for all the
-    // bytes it is due and adds the parts in the order of their CTAs: one crossing of the cluster instead of a
-    // cluster barrier and a read of the others' memory, and nobody's shared memory is read by another CTA.
-    // More rows: a store per value would cost more than it saves; every CTA keeps its part, a cluster barrier
-    // says that all are complete, and the finishing warps read them through distributed shared memory.
-    constexpr bool PUSH = BN == 16;
-    static_assert(!(PUSH && WIDE), "pieces of up to 16 rows are 32 lanes × 1 column");
+    // The finished tile is dealt to the 4·splits finishing warps of the cluster in pieces of RP rows of Y by 32 columns
+    // (RP = 1 up to 16 rows, else 4): piece u = (row group)·segs + (32-column segment) is piece u / ustride of warp
+    // u % ustride of the cluster.  Every CTA sends each piece of its partial tile to the CTA whose warp finishes it, as
+    // stores into that CTA's shared memory that count down a barrier there (`st.async`; with RP = 4 a thread's four
+    // rows of a column in one store): recv[source part][piece of the warp j][warp][32 lanes][RP].  The receiver waits
+    // on its own barrier for all the bytes it is due and adds the parts in the order of their CTAs: one crossing of the
+    // cluster, no cluster barrier, and nobody's shared memory is read by another CTA.
+    constexpr int RP = BN == 16 ? 1 : 4;
+    const int segs = bm >> 5, units = ((M + RP - 1) / RP) * segs, ustride = 4 * (int)gridDim.y;
     static_assert(!SYNC || BN == 16, "the mma.sync variant is for up to 16 rows");
-    const int n_j = (units_n + ustride - 1) / ustride;                   // (PUSH) pieces a warp
-    uint64_t* full = reinterpret_cast<uint64_t*>(recv + (PUSH ? (size_t)sp_recv_floats(M, bm, (int)gridDim.y) : (size_t)M * bm));
+    const int n_j = (units + ustride - 1) / ustride;                     // pieces a warp
+    uint64_t* full = reinterpret_cast<uint64_t*>(recv + (size_t)sp_recv_floats(M, bm, (int)gridDim.y, RP));
     uint64_t* empty = full + SP_MAX_STAGES;
     uint64_t* acc_full = empty + SP_MAX_STAGES;
     uint64_t* x_ready = acc_full + 1;
@@ -299,13 +294,11 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         tbar_init(recv_bar, 1);
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        if (PUSH) {
-            // the bytes this CTA is due: its warps' pieces, once from every part
-            int pieces = 0;
-            for (int w = 0; w < 4; ++w)
-                for (int u = split * 4 + w; u < units_n; u += ustride) ++pieces;
-            tbar_expect_tx(recv_bar, (uint32_t)(pieces * 32 * splits * 4));
-        }
+        // the bytes this CTA is due: its warps' pieces, once from every part
+        int pieces = 0;
+        for (int w = 0; w < 4; ++w)
+            for (int u = split * 4 + w; u < units; u += ustride) ++pieces;
+        tbar_expect_tx(recv_bar, (uint32_t)(pieces * 32 * RP * splits * 4));
     }
     // The cache's block and row of every row's token.  Positions and block tables do not come from the kernel ahead:
     // a product is let go by a product ahead of it at once, but the nearest kernel ahead that is no product (the
@@ -326,7 +319,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         s_kv_blk[m] = blk;
         s_kv_row[m] = row;
     }
-    if (SYNC && (int)threadIdx.x < units_n && threadIdx.x < 64) s_piece[threadIdx.x] = ((int)threadIdx.x % ustride) | (((int)threadIdx.x / ustride) << 8);
+    if (SYNC && (int)threadIdx.x < units && threadIdx.x < 64) s_piece[threadIdx.x] = ((int)threadIdx.x % ustride) | (((int)threadIdx.x / ustride) << 8);
     if (warp == 4) {
         if (lane == 0) { tma_prefetch_descriptor(&tmap_w); if (!LN) tma_prefetch_descriptor(&tmap_x); }
         __syncwarp();
@@ -342,7 +335,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
     // every CTA of the cluster has set up its receiving barrier before anyone sends (waited for further down)
-    if (PUSH) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 
     // The weights do not depend on the kernel ahead: the first stages' tiles of W are requested at once, and
     // the norm's weights for this part's columns are copied to shared memory.
@@ -363,7 +356,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         }
     }
     const float inv_K = 1.f / (float)K;
-    if (PUSH) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     pdl_launch_dependents();
     pdl_wait();                                    // the rows of X, the residual and the positions are ready
     if (threadIdx.x == 0) VLRF_TRACE(trace, 1, tcta, 1);
@@ -371,7 +364,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     // pieces of the tile that this warp will finish: (row m, 32-column segment), dealt to the 4·splits
     // epilogue warps of the cluster; what the first two need from global memory is fetched now
     const int gw = split * 4 + warp;
-    float pre_res[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}}, pre_bias[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    float pre_res[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}}, pre_bias[2] = {0.f, 0.f};
 
     if (warp == 4) {
         if (lane == 0) {
@@ -439,24 +432,19 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             }
         }
         if (warp < 4) {
+            // bias and residual of the first two pieces this warp finishes: asked for now, used at the end
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 const int u = gw + j * ustride;
-                if (wide) {
-                    const int m = u * rpp + lane / lpr, n = n0 + (lane % lpr) * 4;
-                    if (u < units && m < M) {
-#pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            if (n + e < N) {
-                                if (residual) pre_res[j][e] = residual[(size_t)m * ldy + n + e];
-                                if (bias) pre_bias[j][e] = bias[n + e];
-                            }
-                    }
-                } else if (u < units_n) {
-                    const int m = u / segs, n = n0 + (u % segs) * 32 + lane;
+                if (u < units) {
+                    const int m0 = (u / segs) * RP, n = n0 + (u % segs) * 32 + lane;
                     if (n < N) {
-                        if (residual) pre_res[j][0] = residual[(size_t)m * ldy + n];
-                        if (bias) pre_bias[j][0] = bias[n];
+                        if (bias) pre_bias[j] = bias[n];
+                        if (residual) {
+#pragma unroll
+                            for (int e = 0; e < RP; ++e)
+                                if (m0 + e < M) pre_res[j][e] = residual[(size_t)(m0 + e) * ldy + n];
+                        }
                     }
                 }
             }
@@ -496,171 +484,85 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                 }
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             }
-            if (PUSH && have && warp * 32 < bm) {
-                // this thread's column of the partial tile, row after row, to whoever finishes the piece it is in
+            if (have && warp * 32 < bm) {
+                // this thread's column of the partial tile, RP rows at a time, to whoever finishes the piece they are in
                 const uint32_t recv0 = tsm(recv), bar0 = tsm(recv_bar);
-                // the piece of row 0: its owner (a warp of the cluster, g) and which of that warp's pieces it is (j)
+                // the piece of the first rows: its owner (a warp of the cluster, g) and which of that warp's pieces it is (j)
                 int g = warp, j = 0;                       // (segs ≤ 4 ≤ ustride: one subtraction wraps)
 #pragma unroll
-                for (int m = 0; m < BN; ++m) {
+                for (int m = 0; m < BN; m += RP) {
                     if (m < M) {
-                        const int off = ((split * n_j + j) * 4 + (g & 3)) * 32 + lane;
-                        sp_send_f32(recv0 + (uint32_t)off * 4u, bar0, (uint32_t)(g >> 2), r[m]);
+                        const int off = (((split * n_j + j) * 4 + (g & 3)) * 32 + lane) * RP;
+                        if (RP == 1) sp_send_f32(recv0 + (uint32_t)off * 4u, bar0, (uint32_t)(g >> 2), r[m]);
+                        else sp_send_f32x4(recv0 + (uint32_t)off * 4u, bar0, (uint32_t)(g >> 2), r[m], r[m + RP / 4], r[m + RP / 2], r[m + RP - 1]);
                         g += segs;
                         if (g >= ustride) { g -= ustride; ++j; }
                     }
                 }
             }
-            if (!PUSH && warp * 32 < bm) {
-#pragma unroll
-                for (int m = 0; m < BN; ++m)
-                    if (m < M) part[m * bm + warp * 32 + lane] = r[m];
-            }
         }
     }
     __syncwarp();
     if (!SYNC && threadIdx.x == 0) VLRF_TRACE(trace, 1, tcta, 4);
-    if (PUSH) {
-        if (warp < 4 && !*(volatile int*)s_abort && !tbar_wait_or_abort(recv_bar, 0, s_abort)) atomicExch(s_abort, 1);
-    } else {
-        cluster_sync_all();                                    // every part of the tile is in shared memory
-    }
+    if (warp < 4 && !*(volatile int*)s_abort && !tbar_wait_or_abort(recv_bar, 0, s_abort)) atomicExch(s_abort, 1);
     if (threadIdx.x == 0) VLRF_TRACE(trace, 1, tcta, 5);
-    if (warp < 4 && wide && !*(volatile int*)s_abort) {
+    if (warp < 4 && !*(volatile int*)s_abort) {
         int j = 0;
         for (int u = gw; u < units; u += ustride, ++j) {
-            const int m = u * rpp + lane / lpr, colw = (lane % lpr) * 4;
-            const int n = n0 + colw;
-            const bool row_ok = m < M;
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
-            if (row_ok) {
-                const uint32_t own = tsm(part + m * bm + colw);
-                float4 v[SP_MAX_SPLITS];
+            const int m0 = (u / segs) * RP, seg0 = n0 + (u % segs) * 32, n = seg0 + lane;
+            const float* mine = recv + ((size_t)(j * 4 + warp) * 32 + lane) * RP;
+            float acc[RP];
 #pragma unroll
-                for (int s = 0; s < SP_MAX_SPLITS; ++s)
-                    v[s] = s < splits ? ld_cluster_f32x4(own, (uint32_t)s) : make_float4(0.f, 0.f, 0.f, 0.f);
-                acc[0] = v[0].x; acc[1] = v[0].y; acc[2] = v[0].z; acc[3] = v[0].w;
+            for (int e = 0; e < RP; ++e) acc[e] = 0.f;
 #pragma unroll
-                for (int s = 1; s < SP_MAX_SPLITS; ++s) {               // always in the order of the parts
-                    acc[0] += v[s].x; acc[1] += v[s].y; acc[2] += v[s].z; acc[3] += v[s].w;
-                }
-            }
-            float y[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                float res = 0.f, bv = 0.f;
-                if (row_ok && n + e < N) {
-                    if (j < 2) { res = j == 0 ? pre_res[0][e] : pre_res[1][e]; bv = j == 0 ? pre_bias[0][e] : pre_bias[1][e]; }
-                    else { res = residual ? residual[(size_t)m * ldy + n + e] : 0.f; bv = bias ? bias[n + e] : 0.f; }
-                }
-                y[e] = apply_act_out<OT>(acc[e] + bv, act) + res;
-            }
-            const bool full = row_ok && n + 3 < N;
-            if (full && ((size_t)m * ldy + n) % 4 == 0) {
-                if (sizeof(OT) == 4) {
-                    *reinterpret_cast<float4*>(reinterpret_cast<float*>(Y) + (size_t)m * ldy + n) = make_float4(y[0], y[1], y[2], y[3]);
-                } else {
-                    uint2 pk;
-                    pk.x = pack2(y[0], y[1]); pk.y = pack2(y[2], y[3]);
-                    *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(Y) + (size_t)m * ldy + n) = pk;
-                }
-            } else if (row_ok) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    if (n + e < N) ElemIO<OT>::store(Y + (size_t)m * ldy + n + e, y[e]);
-            }
-            if (stats_out != nullptr) {
-                // What a LayerNorm of these rows will need, per 32-column segment (8 lanes): the sum and the
-                // squared deviation from the segment's own mean, of the values as stored (float32 rows only).
-                const int seg0 = n & ~31;
-                const int n_seg = min(32, N - seg0);
-                float sum = 0.f;
-#pragma unroll
-                for (int e = 0; e < 4; ++e) sum += (row_ok && n + e < N) ? y[e] : 0.f;
-#pragma unroll
-                for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-                const float mean = n_seg > 0 ? sum / (float)n_seg : 0.f;
-                float m2 = 0.f;
-#pragma unroll
-                for (int e = 0; e < 4; ++e) { const float d = (row_ok && n + e < N) ? y[e] - mean : 0.f; m2 += d * d; }
-#pragma unroll
-                for (int o = 1; o < 8; o <<= 1) m2 += __shfl_xor_sync(0xffffffffu, m2, o);
-                if ((lane & 7) == 0 && row_ok && seg0 < N) {
-                    float* so = stats_out + ((size_t)m * ((N + 31) >> 5) + (seg0 >> 5)) * 2;
-                    so[0] = sum; so[1] = m2;
-                }
-            }
-            if (kv.Kc != nullptr && row_ok) {
-                const int blk = s_kv_blk[m];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int ne = n + e;
-                    if (ne < N && ne >= kv.k_off && blk >= 0) {
-                        const bool is_v = ne >= kv.v_off;
-                        const int c = ne - (is_v ? kv.v_off : kv.k_off);
-                        if (c < kv.width) {
-                            const int hh = c / kv.dh, cc = c - hh * kv.dh;
-                            __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(is_v ? kv.Vc : kv.Kc);
-                            base[(((size_t)blk * kv.Hkv + hh) * kv.BT + s_kv_row[m]) * kv.dh + cc] = __float2bfloat16_rn(y[e]);
-                        }
+            for (int s = 0; s < SP_MAX_SPLITS; ++s) {               // always in the order of the parts
+                if (s < splits) {
+                    if (RP == 4) {
+                        const float4 v = *reinterpret_cast<const float4*>(mine + (size_t)s * n_j * 128 * RP);
+                        acc[0] += v.x; acc[RP / 4] += v.y; acc[RP / 2] += v.z; acc[RP - 1] += v.w;
+                    } else {
+                        acc[0] += mine[(size_t)s * n_j * 128 * RP];
                     }
                 }
             }
-        }
-    }
-    if (warp < 4 && !wide && !*(volatile int*)s_abort) {
-        // few pieces: 32 lanes × 1 column each, so that more warps share them
-        int j = 0;
-        for (int u = gw; u < units_n; u += ustride, ++j) {
-            const int m = u / segs, colw = (u % segs) * 32 + lane;
-            const int n = n0 + colw;
-            const float* mine = recv + (size_t)(j * 4 + warp) * 32 + lane;
-            const uint32_t own = tsm(part + m * bm + colw);
-            float v[SP_MAX_SPLITS];
+            const float bv = j < 2 ? (j == 0 ? pre_bias[0] : pre_bias[1]) : ((bias && n < N) ? bias[n] : 0.f);
+            const int n_seg = min(32, N - seg0);
 #pragma unroll
-            for (int s = 0; s < SP_MAX_SPLITS; ++s)
-                v[s] = s >= splits ? 0.f : PUSH ? mine[(size_t)s * n_j * 128] : ld_cluster_f32(own, (uint32_t)s);
-            float acc = v[0];
-#pragma unroll
-            for (int s = 1; s < SP_MAX_SPLITS; ++s) acc += v[s];    // always in the order of the parts
-            float res = 0.f, bv = 0.f;
-            if (n < N) {
-                if (j < 2) { res = j == 0 ? pre_res[0][0] : pre_res[1][0]; bv = j == 0 ? pre_bias[0][0] : pre_bias[1][0]; }
-                else { res = residual ? residual[(size_t)m * ldy + n] : 0.f; bv = bias ? bias[n] : 0.f; }
-            }
-            const float y = apply_act_out<OT>(acc + bv, act) + res;
-            if (n < N) ElemIO<OT>::store(Y + (size_t)m * ldy + n, y);
-            if (stats_out != nullptr) {
-                // what a LayerNorm of these rows will need: this segment's sum and squared deviation from its
-                // own mean (of the values as stored)
-                const int seg0 = n0 + (u % segs) * 32;
-                if (seg0 < N) {
-                    const float yv = n < N ? y : 0.f;          // (statistics are kept of float32 rows only)
+            for (int e = 0; e < RP; ++e) {
+                const int m = m0 + e;
+                if (m >= M) break;                                  // (uniform over the warp)
+                float res = 0.f;
+                if (j < 2) res = j == 0 ? pre_res[0][e] : pre_res[1][e];
+                else if (residual && n < N) res = residual[(size_t)m * ldy + n];
+                const float y = apply_act_out<OT>(acc[e] + bv, act) + res;
+                if (n < N) ElemIO<OT>::store(Y + (size_t)m * ldy + n, y);
+                if (stats_out != nullptr && seg0 < N) {
+                    // what a LayerNorm of these rows will need: this segment's sum and squared deviation from its
+                    // own mean (of the values as stored; statistics are kept of float32 rows only)
+                    const float yv = n < N ? y : 0.f;
                     const float sum = warp_sum(yv);
-                    const float d = n < N ? yv - sum / (float)min(32, N - seg0) : 0.f;
+                    const float d = n < N ? yv - sum / (float)n_seg : 0.f;
                     const float m2 = warp_sum(d * d);
                     if (lane == 0) {
                         float* so = stats_out + ((size_t)m * ((N + 31) >> 5) + (seg0 >> 5)) * 2;
                         so[0] = sum; so[1] = m2;
                     }
                 }
-            }
-            if (n >= N) continue;
-            if (kv.Kc != nullptr && n >= kv.k_off) {
-                const bool is_v = n >= kv.v_off;
-                const int c = n - (is_v ? kv.v_off : kv.k_off);
-                const int blk = s_kv_blk[m];
-                if (c < kv.width && blk >= 0) {
-                    const int hh = c / kv.dh, cc = c - hh * kv.dh;
-                    __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(is_v ? kv.Vc : kv.Kc);
-                    base[(((size_t)blk * kv.Hkv + hh) * kv.BT + s_kv_row[m]) * kv.dh + cc] = __float2bfloat16_rn(y);
+                if (n < N && kv.Kc != nullptr && n >= kv.k_off) {
+                    const bool is_v = n >= kv.v_off;
+                    const int c = n - (is_v ? kv.v_off : kv.k_off);
+                    const int blk = s_kv_blk[m];
+                    if (c < kv.width && blk >= 0) {
+                        const int hh = c / kv.dh, cc = c - hh * kv.dh;
+                        __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(is_v ? kv.Vc : kv.Kc);
+                        base[(((size_t)blk * kv.Hkv + hh) * kv.BT + s_kv_row[m]) * kv.dh + cc] = __float2bfloat16_rn(y);
+                    }
                 }
             }
         }
     }
     __syncwarp();
     if (threadIdx.x == 0) VLRF_TRACE(trace, 1, tcta, 6);
-    if (!PUSH) cluster_sync_relaxed();                         // nobody leaves while its shared memory is being read
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -698,7 +600,7 @@ struct SpPlan { int bm, tiles, splits, kb_cap, stages; size_t smem; };
 
 size_t sp_smem(int bm, int bn, bool ln, int stages, int kb_cap, int M, int splits) {
     const size_t ring = (size_t)stages * bm * 128;
-    const size_t part = (bn == 16 ? (size_t)sp_recv_floats(M, bm, splits) : (size_t)M * bm) * sizeof(float);
+    const size_t part = (size_t)sp_recv_floats(M, bm, splits, bn == 16 ? 1 : 4) * sizeof(float);
     return 1024 + ring + part + (bm == 64 ? 8192 : 0) + (size_t)(ln ? kb_cap : stages) * bn * 128 +
            (ln ? (size_t)kb_cap * SP_BK * 8 : 0) + (2 * SP_MAX_STAGES + 3) * 8 + 16 + 192 * sizeof(int);
 }
@@ -734,7 +636,7 @@ SpPlan sp_plan(int M, int N, int K, int bn, bool ln) {
     return best;
 }
 
-template <int BN, typename OT, bool LN, bool WIDE, bool SYNC>
+template <int BN, typename OT, bool LN, bool SYNC>
 int launch_sp_as(const void* X, const void* W, const float* gamma, const float* beta, float eps, const float* bias,
               const float* residual, void* Y, int M, int N, int K, int ldx, int ldy, int act, const SpKvScatter& kv,
               const float* stats_in, float* stats_out, int* dev_err, cudaStream_t stream) {
@@ -749,7 +651,7 @@ int launch_sp_as(const void* X, const void* W, const float* gamma, const float* 
     } else {
         tx = tw;   // unused
     }
-    auto kern = gemm_splitk_kernel<BN, OT, LN, WIDE, SYNC>;
+    auto kern = gemm_splitk_kernel<BN, OT, LN, SYNC>;
     static bool clusters_allowed = false;
     if (!clusters_allowed) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
@@ -776,12 +678,9 @@ int launch_sp(const void* X, const void* W, const float* gamma, const float* bet
               const float* stats_in, float* stats_out, int* dev_err, cudaStream_t stream) {
     const SpPlan plan = sp_plan(M, N, K, BN, LN);
     if (BN == 16 && sp_use_mma_sync(M))
-        return launch_sp_as<BN, OT, LN, false, BN == 16>(X, W, gamma, beta, eps, bias, residual, Y, M, N, K, ldx, ldy, act, kv, stats_in,
-                                                        stats_out, dev_err, stream);
-    if (BN > 16 && sp_is_wide(M, plan.bm, plan.splits, LN))
-        return launch_sp_as<BN, OT, LN, (BN > 16 && !LN), false>(X, W, gamma, beta, eps, bias, residual, Y, M, N, K, ldx, ldy, act, kv, stats_in,
-                                             stats_out, dev_err, stream);
-    return launch_sp_as<BN, OT, LN, false, false>(X, W, gamma, beta, eps, bias, residual, Y, M, N, K, ldx, ldy, act, kv, stats_in,
+        return launch_sp_as<BN, OT, LN, BN == 16>(X, W, gamma, beta, eps, bias, residual, Y, M, N, K, ldx, ldy, act, kv, stats_in,
+                                                 stats_out, dev_err, stream);
+    return launch_sp_as<BN, OT, LN, false>(X, W, gamma, beta, eps, bias, residual, Y, M, N, K, ldx, ldy, act, kv, stats_in,
                                            stats_out, dev_err, stream);
 }
 }  // namespace
