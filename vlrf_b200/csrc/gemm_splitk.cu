@@ -527,6 +527,16 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             }
             const float bv = j < 2 ? (j == 0 ? pre_bias[0] : pre_bias[1]) : ((bias && n < N) ? bias[n] : 0.f);
             const int n_seg = min(32, N - seg0);
+            // where this column lies in the cache, if it is a key's or a value's (the same for every row of the piece)
+            __nv_bfloat16* kv_col = nullptr;
+            if (n < N && kv.Kc != nullptr && n >= kv.k_off) {
+                const bool is_v = n >= kv.v_off;
+                const int c = n - (is_v ? kv.v_off : kv.k_off);
+                if (c < kv.width) {
+                    const int hh = c / kv.dh, cc = c - hh * kv.dh;
+                    kv_col = reinterpret_cast<__nv_bfloat16*>(is_v ? kv.Vc : kv.Kc) + (size_t)hh * kv.BT * kv.dh + cc;
+                }
+            }
 #pragma unroll
             for (int e = 0; e < RP; ++e) {
                 const int m = m0 + e;
@@ -548,15 +558,9 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                         so[0] = sum; so[1] = m2;
                     }
                 }
-                if (n < N && kv.Kc != nullptr && n >= kv.k_off) {
-                    const bool is_v = n >= kv.v_off;
-                    const int c = n - (is_v ? kv.v_off : kv.k_off);
+                if (kv_col != nullptr) {
                     const int blk = s_kv_blk[m];
-                    if (c < kv.width && blk >= 0) {
-                        const int hh = c / kv.dh, cc = c - hh * kv.dh;
-                        __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(is_v ? kv.Vc : kv.Kc);
-                        base[(((size_t)blk * kv.Hkv + hh) * kv.BT + s_kv_row[m]) * kv.dh + cc] = __float2bfloat16_rn(y);
-                    }
+                    if (blk >= 0) kv_col[((size_t)blk * kv.Hkv * kv.BT + s_kv_row[m]) * kv.dh] = __float2bfloat16_rn(y);
                 }
             }
         }
