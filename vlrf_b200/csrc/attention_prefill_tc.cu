@@ -36,7 +36,8 @@ constexpr int FT_THREADS = 192;
 constexpr int FT_TILE = FT_BK * FT_DH * 2;                         // bytes of a K or V tile (and of the Q tile)
 constexpr int FT_SLOTS = 3;
 constexpr int FT_TMEM_COLS = 256;                                  // S: columns 0-127, O_j: 128-191
-constexpr int FT_MIN_PART = 2;                                     // key blocks a part holds at least
+constexpr int FT_MIN_PART = 2;                                     // key blocks a part holds at least (what the host plans with)
+constexpr int FT_PART_BLOCKS = 3;                                  // key blocks a part holds at most, while the tile has parts left
 constexpr int FT_MAX_PARTS = 8;
 constexpr int FT_PART_FLOATS = FT_DH * FT_BQ + 2 * FT_BQ;          // a part's scratch: outputs [64][128], maxima, sums
 
@@ -95,9 +96,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     int* s_last = s_never + 1;                                       // whether this CTA merges its tile's parts
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // long tiles first: z is the slowest index of the order in which CTAs are started
+    // z is the slowest index of the order in which CTAs are started: first parts before second parts, so that the
+    // CTAs without work (short tiles have fewer parts) come last, and within a part long tiles first
     const int n_tiles = gridDim.z / n_parts;
-    const int qt = n_tiles - 1 - blockIdx.z / n_parts, part = blockIdx.z % n_parts, h = blockIdx.x, seq = blockIdx.y;
+    const int part = blockIdx.z / n_tiles, qt = n_tiles - 1 - blockIdx.z % n_tiles, h = blockIdx.x, seq = blockIdx.y;
 
     // set-up that reads nothing of the kernel ahead
     if (threadIdx.x == 0) {
@@ -129,7 +131,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     const int kb_first = (window > 0) ? max(0, q_first - window + 1) / FT_BK : 0;
     const int n_kb = kb_last - kb_first + 1;
     // the tile's key blocks are dealt to tile_parts CTAs; the others of its n_parts have nothing to do
-    const int tile_parts = max(1, min(n_parts, n_kb / FT_MIN_PART));
+    const int tile_parts = max(1, min(n_parts, (n_kb + FT_PART_BLOCKS - 1) / FT_PART_BLOCKS));
     const bool active = qt * FT_BQ < n_new && slot >= 0 && part < tile_parts;     // uniform over the CTA
     const int my_first = kb_first + part * n_kb / tile_parts;
     const int my_n = active ? kb_first + (part + 1) * n_kb / tile_parts - my_first : 0;
