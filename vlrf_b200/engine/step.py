@@ -47,6 +47,7 @@ class Engine:
         self.ws = Workspace(self.device)
         self.dev_err = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._meta_cap = 0
+        self._meta_views = {}
         self._meta_host = None
         self._meta_dev = None
         self._meta_copied = None   # event: the last copy out of the pinned staging buffer has finished
@@ -77,6 +78,7 @@ class Engine:
             self._meta_host = torch.empty(cap, dtype=torch.int32, pin_memory=True)
             self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
             self._meta_cap = cap
+            self._meta_views = {}
             self._graphs.clear()       # captured steps point into the old tables
         return self._meta_host, self._meta_dev
 
@@ -143,15 +145,27 @@ class Engine:
         parts = [p["tokens"], p["tok_slot"], p["tok_pos"], p["seq_slot"], p["seq_start"], p["seq_pos0"], p["rows"]]
         n_ints = sum(a.size for a in parts)
         host, dev = self._meta(n_ints)
-        views, at = [], 0
         if self._meta_copied is not None:
             self._meta_copied.synchronize()   # the staging buffer is free to overwrite
-        hnp = host.numpy()
+        # views of the tables' places in the staging buffers: the same for every step of the same sizes (making a
+        # view costs about 2 us, and a step has nine)
+        layout = (id(dev),) + tuple(a.size for a in parts)
+        cached = self._meta_views.get(layout)
+        if cached is None:
+            if len(self._meta_views) > 64:
+                self._meta_views.clear()
+            views, at = [], 0
+            for a in parts:
+                views.append(dev[at:at + a.size])
+                at += a.size
+            cached = (host.numpy(), views, dev[:n_ints], host[:n_ints])
+            self._meta_views[layout] = cached
+        hnp, views, dev_all, host_all = cached
+        at = 0
         for a in parts:
             hnp[at:at + a.size] = a
-            views.append(dev[at:at + a.size])
             at += a.size
-        dev[:n_ints].copy_(host[:n_ints], non_blocking=True)
+        dev_all.copy_(host_all, non_blocking=True)
         if self._meta_copied is None:
             self._meta_copied = torch.cuda.Event()
         self._meta_copied.record()
